@@ -1,0 +1,326 @@
+// Attention side of the decode path: split-sequence decode attention over the
+// KV cache (fp16, or the reference's fp32), the causal prefill form built on the
+// same inner loop, RoPE and the KV-cache write.
+//
+// Decode attention streams the cache once: HBM-bound.  A CTA owns one
+// (query, head, sequence split); eight lanes share a key (16 or 8 head dims
+// each, 128-bit loads), four keys per warp step, so one warp load instruction
+// covers four whole cache rows.  Each lane group keeps its own running maximum,
+// normaliser and output slice (online softmax); groups, warps and finally splits
+// are merged with the usual (max, sum, vector) rescaling.  Splits meet through a
+// scratch buffer: every CTA publishes its partial result, bumps a per-head
+// counter, and the CTA that sees the last ticket does the merge - no CTA ever
+// waits on another.
+#include <math.h>
+
+#include <algorithm>
+
+#include "greta_common.cuh"
+
+using namespace greta;
+
+namespace {
+
+constexpr int ATT_WARPS = 4;
+constexpr int ATT_THREADS = ATT_WARPS * 32;
+constexpr int MAX_SPLITS = 32;
+
+template <typename KV, int DPL>
+__device__ __forceinline__ void load_row(const KV *p, float (&f)[DPL]) {
+  if (sizeof(KV) == 2) {
+#pragma unroll
+    for (int v = 0; v < DPL / 8; ++v) {
+      uint4 u = ld_stream(reinterpret_cast<const uint8_t *>(p) + v * 16);
+      float2 a = h2_to_f2(u.x), b = h2_to_f2(u.y), c = h2_to_f2(u.z), d = h2_to_f2(u.w);
+      f[8 * v + 0] = a.x; f[8 * v + 1] = a.y; f[8 * v + 2] = b.x; f[8 * v + 3] = b.y;
+      f[8 * v + 4] = c.x; f[8 * v + 5] = c.y; f[8 * v + 6] = d.x; f[8 * v + 7] = d.y;
+    }
+  } else {
+#pragma unroll
+    for (int v = 0; v < DPL / 4; ++v) {
+      uint4 u = ld_stream(reinterpret_cast<const uint8_t *>(p) + v * 16);
+      f[4 * v + 0] = __uint_as_float(u.x); f[4 * v + 1] = __uint_as_float(u.y);
+      f[4 * v + 2] = __uint_as_float(u.z); f[4 * v + 3] = __uint_as_float(u.w);
+    }
+  }
+}
+
+struct AttnParams {
+  const float *q;        // [nq][H][Dh]
+  const void *kc, *vc;   // [Hkv][max_seq][Dh]
+  float *o;              // [nq][H][Dh]
+  const uint32_t *d_pos; // optional device position
+  uint32_t len0;         // keys visible to query 0 when d_pos == NULL (query z sees len0 + z)
+  uint32_t H, Hkv, max_seq;
+  float scale;
+  uint32_t splits;
+  uint32_t *counters;    // [H] zero on entry, left zero
+  float *partial;        // [H][splits][Dh + 2]
+};
+
+// Merge (m2, l2, o2) into (m, l, o).
+template <int DPL>
+__device__ __forceinline__ void merge(float &m, float &l, float (&o)[DPL], float m2, float l2, const float (&o2)[DPL]) {
+  float mn = fmaxf(m, m2);
+  float c1 = (m == -INFINITY) ? 0.f : expf(m - mn);
+  float c2 = (m2 == -INFINITY) ? 0.f : expf(m2 - mn);
+  l = l * c1 + l2 * c2;
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) o[i] = o[i] * c1 + o2[i] * c2;
+  m = mn;
+}
+
+template <typename KV, int DPL>
+__global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnParams p) {
+  constexpr int Dh = DPL * 8;
+  __shared__ float sm_m[ATT_WARPS], sm_l[ATT_WARPS];
+  __shared__ float sm_o[ATT_WARPS][Dh];
+  __shared__ uint32_t sm_last;
+
+  const uint32_t split = blockIdx.x, head = blockIdx.y, qi = blockIdx.z;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane & 7, grp = lane >> 3;  // 8 lanes per key, 4 keys per warp step
+  const uint32_t L = (p.d_pos ? *p.d_pos + 1 : p.len0) + qi;
+  const uint32_t kvh = head / (p.H / p.Hkv);
+  const uint32_t chunk = (L + p.splits - 1) / p.splits;
+  const uint32_t k0 = split * chunk, k1 = min(L, k0 + chunk);
+
+  const KV *kbase = reinterpret_cast<const KV *>(p.kc) + (size_t)kvh * p.max_seq * Dh + sub * DPL;
+  const KV *vbase = reinterpret_cast<const KV *>(p.vc) + (size_t)kvh * p.max_seq * Dh + sub * DPL;
+
+  float qv[DPL];
+  {
+    const float *qp = p.q + ((size_t)qi * p.H + head) * Dh + sub * DPL;
+#pragma unroll
+    for (int i = 0; i < DPL; i += 4) {
+      float4 t = *reinterpret_cast<const float4 *>(qp + i);
+      qv[i] = t.x * p.scale; qv[i + 1] = t.y * p.scale; qv[i + 2] = t.z * p.scale; qv[i + 3] = t.w * p.scale;
+    }
+  }
+
+  float m = -INFINITY, l = 0.f, o[DPL];
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) o[i] = 0.f;
+
+  // warp step j covers keys tw .. tw+3 and tw+16 .. tw+19 (two steps in flight), one key per lane group
+  for (uint32_t tw = k0 + 4 * warp; tw < k1; tw += 4 * ATT_WARPS * 2) {
+    const uint32_t ta = tw + grp, tb = tw + 4 * ATT_WARPS + grp;
+    const bool va = ta < k1, vb = tb < k1;
+    float ka[DPL], kb[DPL], xa[DPL], xb[DPL];
+    if (va) { load_row<KV, DPL>(kbase + (size_t)ta * Dh, ka); load_row<KV, DPL>(vbase + (size_t)ta * Dh, xa); }
+    if (vb) { load_row<KV, DPL>(kbase + (size_t)tb * Dh, kb); load_row<KV, DPL>(vbase + (size_t)tb * Dh, xb); }
+    float sa = 0.f, sb = 0.f;
+    if (va) {
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) sa = fmaf(qv[i], ka[i], sa);
+    }
+    if (vb) {
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) sb = fmaf(qv[i], kb[i], sb);
+    }
+    // reduce across the 8 lanes that share a key (all lanes take part in the shuffles)
+#pragma unroll
+    for (int off = 4; off > 0; off >>= 1) {
+      sa += __shfl_xor_sync(0xffffffffu, sa, off);
+      sb += __shfl_xor_sync(0xffffffffu, sb, off);
+    }
+    if (va) {
+      float mn = fmaxf(m, sa), c = expf(m - mn), pe = expf(sa - mn);
+      l = l * c + pe;
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) o[i] = fmaf(pe, xa[i], o[i] * c);
+      m = mn;
+    }
+    if (vb) {
+      float mn = fmaxf(m, sb), c = expf(m - mn), pe = expf(sb - mn);
+      l = l * c + pe;
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) o[i] = fmaf(pe, xb[i], o[i] * c);
+      m = mn;
+    }
+  }
+
+  // merge the four lane groups of the warp (same dims, different keys)
+#pragma unroll
+  for (int off = 8; off <= 16; off <<= 1) {
+    float m2 = __shfl_xor_sync(0xffffffffu, m, off), l2 = __shfl_xor_sync(0xffffffffu, l, off), o2[DPL];
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) o2[i] = __shfl_xor_sync(0xffffffffu, o[i], off);
+    merge<DPL>(m, l, o, m2, l2, o2);
+  }
+  // merge warps through shared memory
+  if (grp == 0) {
+    if (sub == 0) { sm_m[warp] = m; sm_l[warp] = l; }
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) sm_o[warp][sub * DPL + i] = o[i];
+  }
+  __syncthreads();
+  const int tid = threadIdx.x;
+  float fm = -INFINITY, fl = 0.f, fo = 0.f;  // thread tid < Dh owns output dim tid
+  if (tid < Dh) {
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; ++w) fm = fmaxf(fm, sm_m[w]);
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; ++w) {
+      float c = (sm_m[w] == -INFINITY) ? 0.f : expf(sm_m[w] - fm);
+      fl += sm_l[w] * c;
+      fo += sm_o[w][tid] * c;
+    }
+  }
+  float *out = p.o + ((size_t)qi * p.H + head) * Dh;
+  if (p.splits == 1) {
+    if (tid < Dh) out[tid] = fo / fl;
+    return;
+  }
+  // publish the partial result, take a ticket; the last CTA of this head merges all splits
+  float *mine = p.partial + ((size_t)head * p.splits + split) * (Dh + 2);
+  if (tid < Dh) mine[2 + tid] = fo;
+  if (tid == 0) { mine[0] = fm; mine[1] = fl; }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) sm_last = (atomicAdd(&p.counters[head], 1u) == p.splits - 1) ? 1u : 0u;
+  __syncthreads();
+  if (!sm_last) return;
+  __threadfence();
+  if (tid < Dh) {
+    const float *ph = p.partial + (size_t)head * p.splits * (Dh + 2);
+    float gm = -INFINITY;
+    for (uint32_t s = 0; s < p.splits; ++s) gm = fmaxf(gm, __ldcg(ph + (size_t)s * (Dh + 2)));
+    float gl = 0.f, go = 0.f;
+    for (uint32_t s = 0; s < p.splits; ++s) {
+      const float *ps = ph + (size_t)s * (Dh + 2);
+      float ms = __ldcg(ps);
+      float c = (ms == -INFINITY) ? 0.f : expf(ms - gm);
+      gl += __ldcg(ps + 1) * c;
+      go += __ldcg(ps + 2 + tid) * c;
+    }
+    out[tid] = go / gl;
+  }
+  if (tid == 0) p.counters[head] = 0;  // ready for the next call on this stream
+}
+
+__global__ void rope_kernel(float *x, uint32_t S, uint32_t H, uint32_t Dh, float base, uint32_t pos_offset,
+                            const uint32_t *d_pos) {
+  uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
+  uint32_t hd2 = Dh / 2, total = S * H * hd2;
+  if (idx >= total) return;
+  uint32_t i = idx % hd2, h = (idx / hd2) % H, s = idx / (hd2 * H);
+  uint32_t pos = (d_pos ? *d_pos : pos_offset) + s;
+  float theta = (float)pos * powf(base, -2.0f * (float)i / (float)Dh);
+  float c = cosf(theta), sn = sinf(theta);
+  size_t bi = (size_t)s * H * Dh + (size_t)h * Dh + i;
+  float v0 = x[bi], v1 = x[bi + hd2];
+  x[bi] = v0 * c - v1 * sn;
+  x[bi + hd2] = v0 * sn + v1 * c;
+}
+
+__global__ void kv_update_kernel(__half *kc, __half *vc, const float *nk, const float *nv, uint32_t S, uint32_t pos,
+                                 const uint32_t *d_pos, uint32_t max_seq, uint32_t Hkv, uint32_t Dh) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  size_t total = (size_t)S * Hkv * Dh;
+  if (idx >= total) return;
+  uint32_t d = idx % Dh, h = (idx / Dh) % Hkv, s = idx / ((size_t)Dh * Hkv);
+  uint32_t pp = (d_pos ? *d_pos : pos) + s;
+  if (pp >= max_seq) return;
+  size_t dst = ((size_t)h * max_seq + pp) * Dh + d;
+  kc[dst] = __float2half_rn(nk[idx]);
+  vc[dst] = __float2half_rn(nv[idx]);
+}
+
+size_t counters_bytes(uint32_t H) { return ((size_t)H * 4 + 255) / 256 * 256; }
+
+template <typename KV>
+int launch_attn(cudaStream_t stream, AttnParams p, uint32_t nq, uint32_t Dh) {
+  dim3 grid(p.splits, p.H, nq);
+  if (Dh == 128)
+    attn_kernel<KV, 16><<<grid, ATT_THREADS, 0, stream>>>(p);
+  else if (Dh == 64)
+    attn_kernel<KV, 8><<<grid, ATT_THREADS, 0, stream>>>(p);
+  else {
+    set_error("attention: head_dim=%u is not supported (64 or 128)", Dh);
+    return GRETA_ERR_NOT_IMPLEMENTED;
+  }
+  return launched("attn_kernel");
+}
+
+template <typename KV>
+int attn_decode_impl(greta_stream_t stream, const float *q, const void *kc, const void *vc, float *o,
+                     const uint32_t *d_pos, uint32_t seq_len, uint32_t H, uint32_t Hkv, uint32_t Dh, uint32_t max_seq,
+                     float scale, void *scratch, size_t scratch_bytes) {
+  GRETA_REQUIRE(H && Hkv && H % Hkv == 0, "attn_decode: num_heads=%u must be a positive multiple of num_heads_kv=%u", H, Hkv);
+  GRETA_REQUIRE(q && kc && vc && o, "attn_decode: null pointer");
+  GRETA_REQUIRE(aligned16(q) && aligned16(kc) && aligned16(vc), "attn_decode: pointers must be 16-byte aligned");
+  GRETA_REQUIRE(d_pos || (seq_len >= 1 && seq_len <= max_seq), "attn_decode: seq_len=%u outside 1..max_seq_len=%u", seq_len, max_seq);
+  // Splits are sized for the longest sequence this cache can hold, so that a captured launch stays valid as the position advances.
+  const uint32_t Lmax = d_pos ? max_seq : seq_len;
+  uint32_t want = (2u * (uint32_t)sm_count() + H - 1) / H;
+  uint32_t splits = std::max(1u, std::min({want, (uint32_t)MAX_SPLITS, (Lmax + 63) / 64}));
+  AttnParams p{};
+  p.q = q; p.kc = kc; p.vc = vc; p.o = o; p.d_pos = d_pos; p.len0 = seq_len;
+  p.H = H; p.Hkv = Hkv; p.max_seq = max_seq; p.scale = scale; p.splits = splits;
+  if (splits > 1) {
+    GRETA_REQUIRE(scratch && scratch_bytes >= greta_cuda_attn_decode_scratch_bytes(H, Dh),
+                  "attn_decode: scratch of %zu bytes needed, %zu given", greta_cuda_attn_decode_scratch_bytes(H, Dh), scratch_bytes);
+    p.counters = reinterpret_cast<uint32_t *>(scratch);
+    p.partial = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(scratch) + counters_bytes(H));
+  }
+  return launch_attn<KV>((cudaStream_t)stream, p, 1, Dh);
+}
+
+}  // namespace
+
+extern "C" {
+
+// Layout of the scratch: per-head tickets (zero before the first call; every call
+// leaves them zero), then [H][MAX_SPLITS][Dh + 2] floats of partial results.
+size_t greta_cuda_attn_decode_scratch_bytes(uint32_t H, uint32_t Dh) {
+  return counters_bytes(H) + (size_t)H * MAX_SPLITS * (Dh + 2) * sizeof(float);
+}
+
+int greta_cuda_attn_decode(greta_stream_t stream, const float *q, const void *kc, const void *vc, float *o,
+                           const uint32_t *d_pos, uint32_t seq_len, uint32_t H, uint32_t Hkv, uint32_t Dh,
+                           uint32_t max_seq, float scale, void *scratch, size_t scratch_bytes) {
+  return attn_decode_impl<__half>(stream, q, kc, vc, o, d_pos, seq_len, H, Hkv, Dh, max_seq, scale, scratch, scratch_bytes);
+}
+
+int greta_cuda_attn_decode_f32cache(greta_stream_t stream, const float *q, const float *kc, const float *vc, float *o,
+                                    const uint32_t *d_pos, uint32_t seq_len, uint32_t H, uint32_t Hkv, uint32_t Dh,
+                                    uint32_t max_seq, float scale, void *scratch, size_t scratch_bytes) {
+  return attn_decode_impl<float>(stream, q, kc, vc, o, d_pos, seq_len, H, Hkv, Dh, max_seq, scale, scratch, scratch_bytes);
+}
+
+int greta_cuda_attn_prefill(greta_stream_t stream, const float *q, const void *kc, const void *vc, float *o, uint32_t S,
+                            uint32_t pos0, uint32_t H, uint32_t Hkv, uint32_t Dh, uint32_t max_seq, float scale) {
+  if (S == 0) return GRETA_OK;
+  GRETA_REQUIRE(H && Hkv && H % Hkv == 0, "attn_prefill: num_heads=%u must be a positive multiple of num_heads_kv=%u", H, Hkv);
+  GRETA_REQUIRE(q && kc && vc && o, "attn_prefill: null pointer");
+  GRETA_REQUIRE(pos0 + S <= max_seq, "attn_prefill: positions %u..%u exceed max_seq_len=%u", pos0, pos0 + S, max_seq);
+  GRETA_REQUIRE(S <= 65535, "attn_prefill: S=%u exceeds 65535", S);
+  AttnParams p{};
+  p.q = q; p.kc = kc; p.vc = vc; p.o = o; p.d_pos = nullptr; p.len0 = pos0 + 1;
+  p.H = H; p.Hkv = Hkv; p.max_seq = max_seq; p.scale = scale; p.splits = 1;
+  return launch_attn<__half>((cudaStream_t)stream, p, S, Dh);
+}
+
+int greta_cuda_rope(greta_stream_t stream, float *x, uint32_t S, uint32_t H, uint32_t Dh, float base, uint32_t pos_offset,
+                    const uint32_t *d_pos) {
+  uint32_t total = S * H * (Dh / 2);
+  if (total == 0) return GRETA_OK;
+  GRETA_REQUIRE(x, "rope: null pointer");
+  GRETA_REQUIRE(Dh % 2 == 0, "rope: head_dim=%u must be even", Dh);
+  rope_kernel<<<(total + 255) / 256, 256, 0, (cudaStream_t)stream>>>(x, S, H, Dh, base, pos_offset, d_pos);
+  return launched("rope_kernel");
+}
+
+int greta_cuda_kv_update(greta_stream_t stream, void *kc, void *vc, const float *nk, const float *nv, uint32_t S,
+                         uint32_t pos, const uint32_t *d_pos, uint32_t max_seq, uint32_t Hkv, uint32_t Dh) {
+  size_t total = (size_t)S * Hkv * Dh;
+  if (total == 0) return GRETA_OK;
+  GRETA_REQUIRE(kc && vc && nk && nv, "kv_update: null pointer");
+  GRETA_REQUIRE(d_pos || pos + S <= max_seq, "kv_update: rows %u..%u exceed max_seq_len=%u", pos, pos + S, max_seq);
+  kv_update_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>((__half *)kc, (__half *)vc, nk, nv, S, pos,
+                                                                                    d_pos, max_seq, Hkv, Dh);
+  return launched("kv_update_kernel");
+}
+
+}  // extern "C"

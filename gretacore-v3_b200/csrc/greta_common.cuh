@@ -1,0 +1,79 @@
+// Shared helpers of the sm_100a kernels: error plumbing, format constants, load
+// and conversion primitives.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "greta_cuda.h"
+
+namespace greta {
+
+void set_error(const char *fmt, ...);
+int cuda_fail(cudaError_t e, const char *what);     // records the text, maps to a GRETA_ERR_* code
+void count_launch(unsigned n = 1);
+int sm_count();                                     // SMs of the current device (cached per device)
+
+#define GRETA_CUDA_TRY(expr)                                       \
+  do {                                                             \
+    cudaError_t _e = (expr);                                       \
+    if (_e != cudaSuccess) return ::greta::cuda_fail(_e, #expr);   \
+  } while (0)
+
+#define GRETA_REQUIRE(cond, ...)                                   \
+  do {                                                             \
+    if (!(cond)) {                                                 \
+      ::greta::set_error(__VA_ARGS__);                             \
+      return GRETA_ERR_INVALID_ARGS;                               \
+    }                                                              \
+  } while (0)
+
+// Checks the launch that was just issued.
+inline int launched(const char *kernel, unsigned n = 1) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    cuda_fail(e, kernel);
+    return GRETA_ERR_KERNEL_LAUNCH;
+  }
+  count_launch(n);
+  return GRETA_OK;
+}
+
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Payload bytes per block of 32 weights in the qs plane; 0 for unknown formats.
+__host__ __device__ constexpr int payload_bytes(int fmt) {
+  return fmt == GRETA_FMT_Q4_0 ? 16 : fmt == GRETA_FMT_Q8_0 ? 32 : fmt == GRETA_FMT_F16 ? 64
+       : fmt == GRETA_FMT_REF_INT4 ? 16 : fmt == GRETA_FMT_REF_INT8 ? 32 : 0;
+}
+
+// 128-bit streaming load of weights that are read once: bypass L1 allocation.
+__device__ __forceinline__ uint4 ld_stream(const void *p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint2 ld_stream8(const void *p) {
+  uint2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+__device__ __forceinline__ float2 h2_to_f2(uint32_t h2) {
+  return __half22float2(*reinterpret_cast<const __half2 *>(&h2));
+}
+
+}  // namespace greta

@@ -1,0 +1,239 @@
+/*
+ * greta_cuda.h - C ABI of the sm_100a (B200) quantized-matmul hot path for GRETA CORE.
+ *
+ * Every entry point is plain C: raw device pointers, sizes, a stream handle.  No
+ * exceptions, no hidden synchronisation, and (runtime/memory section apart) no
+ * allocation.  Return value: 0 on success, otherwise a gcore::rt::GretaResult
+ * value (src/rt/include/gcore/rt/greta_runtime.hpp:15-22 in the reference):
+ *   1 out of memory, 2 graph capture, 3 kernel launch, 4 invalid arguments,
+ *   5 not implemented.  greta_cuda_last_error() gives the text of the last failure
+ *   on the calling thread.
+ *
+ * Each function names the reference interface it stands in for (path:line inside
+ * the reference project).
+ *
+ * WEIGHT LAYOUT ("planar GGUF").  A weight W[N x K] (K contiguous, y = x * W^T)
+ * quantised in GGUF blocks of 32 along K is held as two planes:
+ *   qs plane: N * (K/32) quant payloads, row-major, 16 bytes each for Q4_0 (byte j
+ *             of a payload = element j in the low nibble, element j+16 in the
+ *             high nibble, q in 0..15, value (q-8)*d) and 32 bytes for Q8_0
+ *             (int8 q, value q*d) - i.e. the GGUF block with its scale removed;
+ *   d  plane: N * (K/32) fp16 scales, row-major.
+ * Bytes per weight are those of GGUF (18/32 and 34/32); the split makes every
+ * payload 16-byte aligned for 128-bit loads and TMA.  The pair (qs, d) plays
+ * the role of the reference's (weights, GretaQuantInfo::scales) pair with
+ * group_size 32 (greta_runtime.hpp:35-41).  K must be a multiple of 32 and both
+ * planes 16-byte aligned.
+ */
+#ifndef GRETA_CUDA_H
+#define GRETA_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GRETA_API __attribute__((visibility("default")))
+
+typedef void *greta_stream_t; /* a cudaStream_t; NULL = the legacy default stream */
+
+enum {
+  GRETA_OK = 0,
+  GRETA_ERR_OUT_OF_MEM = 1,
+  GRETA_ERR_GRAPH_CAPTURE = 2,
+  GRETA_ERR_KERNEL_LAUNCH = 3,
+  GRETA_ERR_INVALID_ARGS = 4,
+  GRETA_ERR_NOT_IMPLEMENTED = 5
+};
+
+/* Weight formats.  Values continue gcore::rt::GretaDataType (greta_runtime.hpp:24-33,
+ * FP32=0 .. FP8_E5M2=7) so that the C++ layer can pass data_type() straight through. */
+enum {
+  GRETA_FMT_F16 = 1,
+  GRETA_FMT_REF_INT8 = 3, /* reference storage: int8 w[N][K], fp32 scale per 32 along the flat index */
+  GRETA_FMT_REF_INT4 = 4, /* reference storage: uint8 w[N][K/2], elem 2j low nibble, two's complement, fp32 scales */
+  GRETA_FMT_Q4_0 = 8,
+  GRETA_FMT_Q8_0 = 9
+};
+
+/* ------------------------------------------------------------------ runtime
+ * Stand-ins for the hip* calls of the reference's L0 backend
+ * (src/rt/backend/hip/src/greta_runtime_hip.cpp:7-179, buffer.cpp:7-84,
+ * backend.cpp:11-87). */
+GRETA_API const char *greta_cuda_last_error(void);
+GRETA_API int greta_cuda_device_count(int *count);
+GRETA_API int greta_cuda_set_device(int device);
+GRETA_API int greta_cuda_get_device(int *device);
+/* name_cap bytes of name; any out pointer may be NULL. */
+GRETA_API int greta_cuda_device_info(int device, char *name, size_t name_cap, int *sm_count,
+                                     size_t *total_mem, int *cc_major, int *cc_minor);
+GRETA_API int greta_cuda_malloc(void **ptr, size_t bytes);
+GRETA_API int greta_cuda_free(void *ptr);
+GRETA_API int greta_cuda_malloc_host(void **ptr, size_t bytes); /* pinned host memory */
+GRETA_API int greta_cuda_free_host(void *ptr);
+/* Copies are asynchronous on `stream` when the host side is pinned; _sync variants block. */
+GRETA_API int greta_cuda_memcpy_h2d(void *dst, const void *src, size_t bytes, greta_stream_t stream);
+GRETA_API int greta_cuda_memcpy_d2h(void *dst, const void *src, size_t bytes, greta_stream_t stream);
+GRETA_API int greta_cuda_memcpy_d2d(void *dst, const void *src, size_t bytes, greta_stream_t stream);
+GRETA_API int greta_cuda_memcpy_h2d_sync(void *dst, const void *src, size_t bytes);
+GRETA_API int greta_cuda_memcpy_d2h_sync(void *dst, const void *src, size_t bytes);
+GRETA_API int greta_cuda_memset(void *dst, int value, size_t bytes, greta_stream_t stream);
+GRETA_API int greta_cuda_stream_create(greta_stream_t *stream);
+GRETA_API int greta_cuda_stream_destroy(greta_stream_t stream);
+GRETA_API int greta_cuda_stream_synchronize(greta_stream_t stream);
+GRETA_API int greta_cuda_device_synchronize(void);
+GRETA_API int greta_cuda_event_create(void **event);
+GRETA_API int greta_cuda_event_destroy(void *event);
+GRETA_API int greta_cuda_event_record(void *event, greta_stream_t stream);
+GRETA_API int greta_cuda_event_synchronize(void *event);
+GRETA_API int greta_cuda_event_elapsed_ms(void *start, void *end, float *ms);
+GRETA_API int greta_cuda_stream_wait_event(greta_stream_t stream, void *event);
+/* Graphs: GretaGraphHip capture_start/capture_end/instantiate/launch
+ * (greta_runtime_hip.cpp:84-141). */
+GRETA_API int greta_cuda_graph_capture_begin(greta_stream_t stream);
+GRETA_API int greta_cuda_graph_capture_end(greta_stream_t stream, void **graph);
+GRETA_API int greta_cuda_graph_instantiate(void *graph, void **exec);
+GRETA_API int greta_cuda_graph_launch(void *exec, greta_stream_t stream);
+GRETA_API int greta_cuda_graph_destroy(void *graph);
+GRETA_API int greta_cuda_graph_exec_destroy(void *exec);
+/* Number of kernel launches this library has issued on the calling process (all threads). */
+GRETA_API uint64_t greta_cuda_launch_count(void);
+
+/* ------------------------------------------------------------------ formats */
+/* Bytes of the qs plane and of the d plane of an [N x K] weight. */
+GRETA_API size_t greta_cuda_qs_bytes(int fmt, uint32_t N, uint32_t K);
+GRETA_API size_t greta_cuda_d_bytes(int fmt, uint32_t N, uint32_t K);
+/* Device-side split of raw GGUF blocks (18 B Q4_0 / 34 B Q8_0, as stored in a GGUF
+ * file: src/inference/src/weight_loader.cpp:60-75 sizes, :703-712 Q8_0 split) into
+ * the two planes. */
+GRETA_API int greta_cuda_repack_gguf(greta_stream_t stream, int fmt, const void *gguf_blocks, void *qs,
+                                     void *d, uint32_t N, uint32_t K);
+/* Dequantise to fp32, bit-exact (float)q * fp32(d)
+ * (read_weight_value, src/inference/src/block_scheduler.cpp:639-671). */
+GRETA_API int greta_cuda_dequant(greta_stream_t stream, int fmt, const void *qs, const void *d,
+                                 float *out, uint32_t N, uint32_t K);
+GRETA_API int greta_cuda_f32_to_f16(greta_stream_t stream, const float *in, void *out_f16, size_t n);
+GRETA_API int greta_cuda_f16_to_f32(greta_stream_t stream, const void *in_f16, float *out, size_t n);
+
+/* ------------------------------------------------------------------ decode GEMV
+ * y[M x N] = x[M x K] * dequant(W)^T, fp32 accumulation, fp32 output.
+ * Replaces the GEMV route (M <= 32) of launch_gemm_mfma_int4_wt_fp32_acc32 and
+ * launch_gemm_mfma_int8_wt_fp32_acc32 (src/rt/backend/hip/kernels/gemm_kernels.hip:
+ * 763-817, 594-634, launchers :742-760 and :910-942) and, for GRETA_FMT_F16
+ * (qs = fp16 W[N x K], d = NULL), launch_gemm_mixed_f16f32 / launch_lm_head_gemv
+ * (:466-507, :533-589).  x is fp32, or fp16 when x_is_f16 != 0 (the INT4 kernel's
+ * T_A = __half instantiation).  For the two GRETA_FMT_REF_* formats qs/d are the
+ * reference's own planes (d = fp32 scales). */
+GRETA_API int greta_cuda_gemv(greta_stream_t stream, int fmt, const void *x, int x_is_f16,
+                              const void *qs, const void *d, float *y, uint32_t M, uint32_t N,
+                              uint32_t K);
+
+/* y[N] = resid[N] + dequant(W)[N x K] * x[K]   (M = 1; y may alias resid).
+ * O-projection / down-projection followed by the residual add
+ * (block_scheduler.cpp:2769-2775 + launch_add :2896; :3003-3006 + :3032). */
+GRETA_API int greta_cuda_gemv_residual(greta_stream_t stream, int fmt, const float *x, const void *qs,
+                                       const void *d, const float *resid, float *y, uint32_t N,
+                                       uint32_t K);
+
+/* Fused decode QKV: xn = rmsnorm(x, gamma, eps); q = Wq xn; k = Wk xn; v = Wv xn;
+ * rotate-half RoPE at position *d_pos on q and k; q -> q_out fp32 [H*Dh];
+ * k, v -> fp16 caches [Hkv][max_seq][Dh] at row *d_pos.  gamma may be NULL (no
+ * norm).  k_out / v_out (fp32 [Hkv*Dh], post-RoPE k) are optional copies.
+ * Replaces launch_rmsnorm_naive + 3 x GretaCompute::gemm + 2 x launch_rope +
+ * launch_kv_update (block_scheduler.cpp:1814-1977) and is the Q4_0/Q8_0 form of
+ * launch_fused_rmsnorm_qkv_gemv_f16 (fused_compute_kernels.hip:22-157) and
+ * launch_fused_rope_kv_update_decode (fused_attention_kernels.hip:35-108); it is
+ * what GretaFused::rmsnorm_qkv (greta_compute.hpp:68-72) is declared for. */
+GRETA_API int greta_cuda_fused_rmsnorm_qkv_rope_kv(
+    greta_stream_t stream, int fmt, const float *x, const float *gamma, float eps, const void *wq_qs,
+    const void *wq_d, const void *wk_qs, const void *wk_d, const void *wv_qs, const void *wv_d,
+    float *q_out, float *k_out, float *v_out, void *k_cache_f16, void *v_cache_f16,
+    const uint32_t *d_pos, uint32_t num_heads, uint32_t num_heads_kv, uint32_t head_dim,
+    uint32_t max_seq_len, float rope_base, uint32_t D);
+
+/* Fused FFN front: xn = rmsnorm(x, gamma, eps); y[F] = silu(W1 xn) * (W3 xn).
+ * gamma may be NULL.  Replaces launch_rmsnorm_naive + 2 x gemm + launch_silu +
+ * launch_mul (block_scheduler.cpp:2913-2995); Q4_0/Q8_0 form of
+ * launch_fused_ffn_front_f16 (fused_compute_kernels.hip:167-243). */
+GRETA_API int greta_cuda_fused_ffn_front(greta_stream_t stream, int fmt, const float *x,
+                                         const float *gamma, float eps, const void *w1_qs,
+                                         const void *w1_d, const void *w3_qs, const void *w3_d,
+                                         float *y, uint32_t D, uint32_t F);
+
+/* ------------------------------------------------------------------ prefill GEMM
+ * C[M x N] = half(A[M x K]) * half(dequant(W))^T, fp32 accumulation on the
+ * tensor cores (tcgen05, TMEM accumulators); A fp32 or fp16, C fp32 or fp16.
+ * Replaces the M > 32 route: gemm_mfma_int4_wt_kernel / gemm_mfma_int8_wt_kernel
+ * (gemm_kernels.hip:820-908, 640-740) with the row-major contraction.
+ * workspace: device scratch of greta_cuda_gemm_workspace_bytes(M, K) bytes, used
+ * for the fp16 copy of A when A is fp32 (may be NULL when a_is_f16). */
+GRETA_API size_t greta_cuda_gemm_workspace_bytes(uint32_t M, uint32_t K);
+GRETA_API int greta_cuda_gemm(greta_stream_t stream, int fmt, const void *A, int a_is_f16,
+                              const void *qs, const void *d, void *C, int c_is_f16, uint32_t M,
+                              uint32_t N, uint32_t K, void *workspace);
+
+/* ------------------------------------------------------------------ attention
+ * Decode attention of one query per head over the fp16 KV cache
+ * [Hkv][max_seq][Dh], split over the sequence; seq_len = *d_pos + 1 when d_pos
+ * is non-NULL, else `seq_len`.  scratch: greta_cuda_attn_decode_scratch_bytes()
+ * bytes of device memory for the per-split partial results.
+ * Replaces launch_flash_attention_decode (attention_kernels.hip:167-380) behind
+ * GretaCompute::attention_decode (src/compute/src/greta_compute_hip.cpp:376-412). */
+GRETA_API size_t greta_cuda_attn_decode_scratch_bytes(uint32_t num_heads, uint32_t head_dim);
+GRETA_API int greta_cuda_attn_decode(greta_stream_t stream, const float *q, const void *k_cache_f16,
+                                     const void *v_cache_f16, float *o, const uint32_t *d_pos,
+                                     uint32_t seq_len, uint32_t num_heads, uint32_t num_heads_kv,
+                                     uint32_t head_dim, uint32_t max_seq_len, float scale,
+                                     void *scratch, size_t scratch_bytes);
+/* Same with an fp32 cache, the reference's own cache type (block_scheduler.cpp:1490-1494). */
+GRETA_API int greta_cuda_attn_decode_f32cache(greta_stream_t stream, const float *q,
+                                              const float *k_cache, const float *v_cache, float *o,
+                                              const uint32_t *d_pos, uint32_t seq_len,
+                                              uint32_t num_heads, uint32_t num_heads_kv,
+                                              uint32_t head_dim, uint32_t max_seq_len, float scale,
+                                              void *scratch, size_t scratch_bytes);
+/* Causal prefill attention: q [S][H][Dh] fp32 against rows [pos0, pos0+S) of the
+ * fp16 cache (keys 0 .. pos0+s for query s), o [S][H][Dh] fp32.
+ * Replaces launch_flash_attention_prefill (attention_kernels.hip:543-618). */
+GRETA_API int greta_cuda_attn_prefill(greta_stream_t stream, const float *q, const void *k_cache_f16,
+                                      const void *v_cache_f16, float *o, uint32_t S, uint32_t pos0,
+                                      uint32_t num_heads, uint32_t num_heads_kv, uint32_t head_dim,
+                                      uint32_t max_seq_len, float scale);
+/* RoPE in place on x [S][H][Dh]; position pos_offset + s, or *d_pos + s when
+ * d_pos != NULL.  launch_rope, both overloads (attention_kernels.hip:28-84). */
+GRETA_API int greta_cuda_rope(greta_stream_t stream, float *x, uint32_t S, uint32_t num_heads,
+                              uint32_t head_dim, float base, uint32_t pos_offset,
+                              const uint32_t *d_pos);
+/* Write S new K/V rows (fp32 [S][Hkv][Dh]) into the fp16 caches at rows pos.. .
+ * launch_kv_update, both overloads (attention_kernels.hip:103-158), without the
+ * reference's one-launch-per-token loop in prefill (block_scheduler.cpp:1970-1976). */
+GRETA_API int greta_cuda_kv_update(greta_stream_t stream, void *k_cache_f16, void *v_cache_f16,
+                                   const float *new_k, const float *new_v, uint32_t S,
+                                   uint32_t pos, const uint32_t *d_pos, uint32_t max_seq_len,
+                                   uint32_t num_heads_kv, uint32_t head_dim);
+
+/* ------------------------------------------------------------------ small operators */
+/* launch_rmsnorm_naive (basic_kernels.hip:21-64); also what GretaCompute::rmsnorm
+ * (greta_compute_hip.cpp:414-419, an empty placeholder in the reference) calls. */
+GRETA_API int greta_cuda_rmsnorm(greta_stream_t stream, const float *x, const float *gamma, float *y,
+                                 uint32_t rows, uint32_t cols, float eps);
+/* launch_add (basic_kernels.hip:127-140). */
+GRETA_API int greta_cuda_add(greta_stream_t stream, const float *a, const float *b, float *c, size_t n);
+/* launch_silu then launch_mul in one pass (basic_kernels.hip:141-167): y = silu(gate) * up. */
+GRETA_API int greta_cuda_silu_mul(greta_stream_t stream, const float *gate, const float *up, float *y,
+                                  size_t n);
+/* launch_embedding_lookup, row-major table (basic_kernels.hip:169-206); table fp16
+ * (table_is_f16) or fp32; ids outside [0, vocab) give zeros. */
+GRETA_API int greta_cuda_embedding(greta_stream_t stream, const int32_t *tokens, const void *table,
+                                   int table_is_f16, float *out, uint32_t S, uint32_t dim,
+                                   uint32_t vocab);
+/* launch_argmax (basic_kernels.hip:330-373) without its per-call allocation and
+ * synchronisation: writes the index of the first maximum to *d_out (device). */
+GRETA_API int greta_cuda_argmax(greta_stream_t stream, const float *logits, uint32_t n, int32_t *d_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GRETA_CUDA_H */

@@ -1,0 +1,53 @@
+"""Shared helpers of the test-suite: package loading, seeded GGUF block makers, error metric."""
+import importlib.util
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PKG_DIR = os.path.join(ROOT, "gretacore-v3_b200")
+
+
+def load_package():
+    """Imports the package directory `gretacore-v3_b200` under the importable name gretacore_v3_b200."""
+    name = "gretacore_v3_b200"
+    if name in sys.modules:
+        return sys.modules[name]
+    spec = importlib.util.spec_from_file_location(name, os.path.join(PKG_DIR, "__init__.py"),
+                                                  submodule_search_locations=[PKG_DIR])
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def q4_0_blocks(rng, N, K, sigma=0.02):
+    """GGUF Q4_0 blocks of W[N,K]: q uniform in 0..15, d = |N(0,sigma)|/8 as fp16 (BASELINE config 2)."""
+    nb = N * (K // 32)
+    blk = np.empty((nb, 18), np.uint8)
+    blk[:, :2] = (np.abs(rng.normal(0, sigma, nb)) / 8).astype(np.float16).view(np.uint8).reshape(nb, 2)
+    blk[:, 2:] = rng.integers(0, 256, (nb, 16), dtype=np.uint8)
+    return blk.reshape(-1)
+
+
+def q8_0_blocks(rng, N, K, sigma=0.02):
+    """GGUF Q8_0 blocks: q uniform in [-127,127], d = |N(0,sigma)|/127 as fp16 (BASELINE config 1)."""
+    nb = N * (K // 32)
+    blk = np.empty((nb, 34), np.uint8)
+    blk[:, :2] = (np.abs(rng.normal(0, sigma, nb)) / 127).astype(np.float16).view(np.uint8).reshape(nb, 2)
+    blk[:, 2:] = rng.integers(-127, 128, (nb, 32), dtype=np.int8).view(np.uint8)
+    return blk.reshape(-1)
+
+
+def make_blocks(rng, fmt, N, K):
+    from oracle import oracle as O
+    return q4_0_blocks(rng, N, K) if fmt == O.FMT_Q4_0 else q8_0_blocks(rng, N, K)
+
+
+def max_abs_rel(got, want):
+    """max |got - want| / max |want|: the acceptance metric (<= 2e-3 for matmul and attention)."""
+    got = np.asarray(got, np.float64)
+    want = np.asarray(want, np.float64)
+    denom = np.abs(want).max()
+    return float(np.abs(got - want).max() / (denom if denom > 0 else 1.0))

@@ -1,0 +1,365 @@
+"""Parity of the CUDA kernels with the CPU oracle, through the C ABI, on seeded inputs.
+
+Bars: dequantised values bit-exact; matmul and attention within max-abs-rel 2e-3 of the
+double-accumulating oracle (fp32 accumulation on the device).  The observed errors are far
+smaller; tighter internal bars are asserted where the arithmetic allows it.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from _support import load_package, make_blocks, max_abs_rel, q4_0_blocks
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3          # north-star tolerance (max-abs-rel, fp32 accumulation)
+TIGHT = 2e-5        # what fp32 accumulation against a double oracle actually gives
+
+FMTS = {"q4_0": (O.FMT_Q4_0, 8), "q8_0": (O.FMT_Q8_0, 9)}
+
+
+@pytest.fixture(scope="module")
+def g():
+    pkg = load_package()
+    pkg.build()
+    pkg.ffi.require_device()
+    return pkg.ffi
+
+
+_KEEP = []
+
+
+@pytest.fixture(autouse=True)
+def _release_device_buffers():
+    yield
+    for b in _KEEP:
+        b.free()
+    _KEEP.clear()
+
+
+def _dev(g, arr):
+    """Uploads arr; the buffer stays alive until the end of the test (a temporary would be freed,
+    and its address reused, before the kernel that reads it has run)."""
+    b = g.DeviceBuffer.from_numpy(arr)
+    _KEEP.append(b)
+    return b
+
+
+def _nan_buffer(g, n_floats):
+    b = g.DeviceBuffer(n_floats * 4)
+    b.fill(0xFF)            # NaN pattern: unwritten outputs are caught
+    return b
+
+
+# ----------------------------------------------------------------------------- formats
+@pytest.mark.parametrize("name", ["q4_0", "q8_0"])
+def test_repack_and_dequant_bit_exact(g, name):
+    ofmt, gfmt = FMTS[name]
+    rng = np.random.default_rng(11)
+    N, K = 37, 352
+    blk = make_blocks(rng, ofmt, N, K)
+    w = g.Weight(blk, gfmt, N, K)
+    out = g.DeviceBuffer(N * K * 4)
+    g.check(g.cuda().greta_cuda_dequant(None, gfmt, w.qs.ptr, w.d.ptr, out.ptr, N, K))
+    got = out.download(np.float32)
+    want = O.dequant(blk, ofmt)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    # the planes hold exactly GGUF's bytes: scales first two bytes of each block, payload the rest
+    bb = g.GGUF_BLOCK_BYTES[gfmt]
+    b2 = blk.reshape(-1, bb)
+    assert np.array_equal(w.d.download(np.uint8, N * (K // 32) * 2), b2[:, :2].reshape(-1))
+    assert np.array_equal(w.qs.download(np.uint8, b2[:, 2:].size), b2[:, 2:].reshape(-1))
+
+
+def test_dequant_reference_storage_bit_exact(g):
+    rng = np.random.default_rng(12)
+    n = 64 * 96
+    src = rng.normal(0, 0.02, n).astype(np.float32)
+    pk, sc = O.quantize_ref_int4(src)
+    out = g.DeviceBuffer(n * 4)
+    g.check(g.cuda().greta_cuda_dequant(None, g.FMT_REF_INT4, _dev(g, pk).ptr, _dev(g, sc).ptr, out.ptr, 64, 96))
+    assert np.array_equal(out.download(np.float32).view(np.uint32), O.dequant_ref_int4(pk, sc).view(np.uint32))
+    w8, s8 = O.quantize_ref_int8(src)
+    g.check(g.cuda().greta_cuda_dequant(None, g.FMT_REF_INT8, _dev(g, w8).ptr, _dev(g, s8).ptr, out.ptr, 64, 96))
+    assert np.array_equal(out.download(np.float32).view(np.uint32), O.dequant_ref_int8(w8, s8).view(np.uint32))
+
+
+def test_f16_conversions_bit_exact(g):
+    rng = np.random.default_rng(13)
+    f = np.concatenate([rng.normal(0, 1, 4099), rng.normal(0, 1e-5, 4096), rng.normal(0, 1e-7, 1024),
+                        [0.0, -0.0, 65504.0, 65520.0, 1e9, -1e9]]).astype(np.float32)
+    src = _dev(g, f)
+    dst = g.DeviceBuffer(f.size * 2)
+    g.check(g.cuda().greta_cuda_f32_to_f16(None, src.ptr, dst.ptr, f.size))
+    bits = dst.download(np.uint16)
+    assert np.array_equal(bits, O.f32_to_f16_bits(f))
+    back = g.DeviceBuffer(f.size * 4)
+    g.check(g.cuda().greta_cuda_f16_to_f32(None, dst.ptr, back.ptr, f.size))
+    assert np.array_equal(back.download(np.float32).view(np.uint32), O.f16_bits_to_f32(bits).view(np.uint32))
+
+
+# ----------------------------------------------------------------------------- GEMV
+GEMV_SHAPES = [(1, 1, 32), (1, 3, 64), (1, 17, 96), (2, 5, 1056), (1, 257, 4096), (3, 130, 2048), (1, 64, 11008),
+               (1, 4100, 512)]
+
+
+@pytest.mark.parametrize("name", ["q4_0", "q8_0"])
+@pytest.mark.parametrize("M,N,K", GEMV_SHAPES)
+def test_gemv_matches_oracle(g, name, M, N, K):
+    ofmt, gfmt = FMTS[name]
+    rng = np.random.default_rng(100 + N + K)
+    blk = make_blocks(rng, ofmt, N, K)
+    x = rng.normal(0, 1, (M, K)).astype(np.float32)
+    w = g.Weight(blk, gfmt, N, K)
+    y = _nan_buffer(g, M * N)
+    g.check(g.cuda().greta_cuda_gemv(None, gfmt, _dev(g, x).ptr, 0, w.qs.ptr, w.d.ptr, y.ptr, M, N, K))
+    got = y.download(np.float32).reshape(M, N)
+    want = O.gemv(x, blk, ofmt, N, K, O.ACC_F64)
+    assert np.isfinite(got).all()
+    err = max_abs_rel(got, want)
+    assert err < TOL and err < TIGHT, err
+
+
+def test_gemv_fp16_activations(g):
+    """The reference instantiates its INT4 GEMV for fp16 activations too (gemm_kernels.hip:921-925)."""
+    rng = np.random.default_rng(5)
+    N, K = 96, 1024
+    blk = q4_0_blocks(rng, N, K)
+    xh = rng.normal(0, 1, K).astype(np.float16)
+    w = g.Weight(blk, g.FMT_Q4_0, N, K)
+    y = _nan_buffer(g, N)
+    g.check(g.cuda().greta_cuda_gemv(None, g.FMT_Q4_0, _dev(g, xh.view(np.uint16)).ptr, 1, w.qs.ptr, w.d.ptr, y.ptr, 1, N, K))
+    want = O.gemv(xh.view(np.uint16).reshape(1, K), blk, O.FMT_Q4_0, N, K)
+    assert max_abs_rel(y.download(np.float32), want[0]) < TIGHT
+
+
+def test_gemv_reference_int4_int8_storage(g):
+    """The reference's own INT4 / INT8 planes (fp32 scales, adjacent-nibble packing) give the same
+    products as the oracle's dequantised weights."""
+    rng = np.random.default_rng(6)
+    N, K = 70, 1312
+    src = rng.normal(0, 0.02, N * K).astype(np.float32)
+    x = rng.normal(0, 1, K).astype(np.float32)
+    for gfmt, (planes, deq) in {g.FMT_REF_INT4: (O.quantize_ref_int4(src), O.dequant_ref_int4),
+                                g.FMT_REF_INT8: (O.quantize_ref_int8(src), O.dequant_ref_int8)}.items():
+        wq, sc = planes
+        W = deq(wq, sc).reshape(N, K).astype(np.float64)
+        y = _nan_buffer(g, N)
+        g.check(g.cuda().greta_cuda_gemv(None, gfmt, _dev(g, x).ptr, 0, _dev(g, wq).ptr, _dev(g, sc).ptr, y.ptr, 1, N, K))
+        assert max_abs_rel(y.download(np.float32), W @ x.astype(np.float64)) < TIGHT
+
+
+def test_gemv_f16_weights_lm_head_form(g):
+    rng = np.random.default_rng(7)
+    N, K = 1003, 512
+    W = rng.normal(0, 0.02, (N, K)).astype(np.float16)
+    x = rng.normal(0, 1, (2, K)).astype(np.float32)
+    y = _nan_buffer(g, 2 * N)
+    g.check(g.cuda().greta_cuda_gemv(None, g.FMT_F16, _dev(g, x).ptr, 0, _dev(g, W.view(np.uint16)).ptr, None, y.ptr, 2, N, K))
+    want = O.gemm_f16w(x, W.view(np.uint16), N, K)
+    assert max_abs_rel(y.download(np.float32).reshape(2, N), want) < TIGHT
+
+
+def test_gemv_linearity_at_full_size(g):
+    """Size-independent property at a BASELINE shape (11008 x 4096, Q4_0): W(a x1 + b x2) = a W x1 + b W x2,
+    and a sampled row check against the oracle."""
+    rng = np.random.default_rng(8)
+    N, K = 11008, 4096
+    blk = q4_0_blocks(rng, N, K)
+    w = g.Weight(blk, g.FMT_Q4_0, N, K)
+    x1 = rng.normal(0, 1, K).astype(np.float32)
+    x2 = rng.normal(0, 1, K).astype(np.float32)
+    xs = np.stack([x1, x2, (0.5 * x1.astype(np.float64) - 2.0 * x2.astype(np.float64)).astype(np.float32)])
+    y = _nan_buffer(g, 3 * N)
+    g.check(g.cuda().greta_cuda_gemv(None, g.FMT_Q4_0, _dev(g, xs).ptr, 0, w.qs.ptr, w.d.ptr, y.ptr, 3, N, K))
+    got = y.download(np.float32).reshape(3, N).astype(np.float64)
+    assert np.abs(got[2] - (0.5 * got[0] - 2.0 * got[1])).max() / np.abs(got[2]).max() < 1e-5
+    rows = rng.choice(N, 64, replace=False)
+    bb = 18 * (K // 32)
+    sub = np.concatenate([blk[r * bb:(r + 1) * bb] for r in rows])
+    want = O.gemv(x1, sub, O.FMT_Q4_0, 64, K)
+    assert max_abs_rel(got[0][rows], want[0]) < TIGHT
+
+
+@pytest.mark.parametrize("name", ["q4_0", "q8_0"])
+def test_gemv_residual(g, name):
+    ofmt, gfmt = FMTS[name]
+    rng = np.random.default_rng(9)
+    N, K = 515, 1408
+    blk = make_blocks(rng, ofmt, N, K)
+    x = rng.normal(0, 1, K).astype(np.float32)
+    r = rng.normal(0, 1, N).astype(np.float32)
+    w = g.Weight(blk, gfmt, N, K)
+    rb = _dev(g, r)
+    g.check(g.cuda().greta_cuda_gemv_residual(None, gfmt, _dev(g, x).ptr, w.qs.ptr, w.d.ptr, rb.ptr, rb.ptr, N, K))  # in place
+    want = r.astype(np.float64) + O.gemv(x, blk, ofmt, N, K)[0]
+    assert max_abs_rel(rb.download(np.float32), want) < TIGHT
+
+
+# ----------------------------------------------------------------------------- fused decode operators
+@pytest.mark.parametrize("name", ["q4_0", "q8_0"])
+@pytest.mark.parametrize("H,Hkv,Dh,D,pos", [(4, 4, 128, 512, 0), (8, 2, 64, 256, 37), (32, 32, 128, 4096, 2047)])
+def test_fused_rmsnorm_qkv_rope_kv(g, name, H, Hkv, Dh, D, pos):
+    if name == "q8_0" and D == 4096:
+        pytest.skip("large case covered by q4_0")
+    ofmt, gfmt = FMTS[name]
+    rng = np.random.default_rng(20 + H + pos)
+    max_seq = pos + 3
+    x = rng.normal(0, 1, D).astype(np.float32)
+    gamma = rng.normal(1, 0.1, D).astype(np.float32)
+    bq, bk, bv = (make_blocks(rng, ofmt, n, D) for n in (H * Dh, Hkv * Dh, Hkv * Dh))
+    wq, wk, wv = g.Weight(bq, gfmt, H * Dh, D), g.Weight(bk, gfmt, Hkv * Dh, D), g.Weight(bv, gfmt, Hkv * Dh, D)
+    q_out, k_out, v_out = _nan_buffer(g, H * Dh), _nan_buffer(g, Hkv * Dh), _nan_buffer(g, Hkv * Dh)
+    kc = g.DeviceBuffer(Hkv * max_seq * Dh * 2, zero=True)
+    vc = g.DeviceBuffer(Hkv * max_seq * Dh * 2, zero=True)
+    dpos = _dev(g, np.array([pos], np.uint32))
+    g.check(g.cuda().greta_cuda_fused_rmsnorm_qkv_rope_kv(
+        None, gfmt, _dev(g, x).ptr, _dev(g, gamma).ptr, 1e-5, wq.qs.ptr, wq.d.ptr, wk.qs.ptr, wk.d.ptr, wv.qs.ptr, wv.d.ptr,
+        q_out.ptr, k_out.ptr, v_out.ptr, kc.ptr, vc.ptr, dpos.ptr, H, Hkv, Dh, max_seq, 10000.0, D))
+    xn = O.rmsnorm(x.reshape(1, D), gamma, 1e-5)
+    q = O.rope(O.gemv(xn, bq, ofmt, H * Dh, D), 1, H, Dh, 10000.0, pos).ravel()
+    k = O.rope(O.gemv(xn, bk, ofmt, Hkv * Dh, D), 1, Hkv, Dh, 10000.0, pos).ravel()
+    v = O.gemv(xn, bv, ofmt, Hkv * Dh, D).ravel()
+    # RoPE at large positions amplifies the 1-ulp differences of powf/cosf/sinf between libm and the device
+    bar = 5e-4
+    assert max_abs_rel(q_out.download(np.float32), q) < bar
+    assert max_abs_rel(k_out.download(np.float32), k) < bar
+    assert max_abs_rel(v_out.download(np.float32), v) < TIGHT
+    kc_h = kc.download(np.uint16).reshape(Hkv, max_seq, Dh)
+    vc_h = vc.download(np.uint16).reshape(Hkv, max_seq, Dh)
+    # the cache row holds the fp16 rounding of exactly what was returned in fp32
+    assert np.array_equal(kc_h[:, pos, :].ravel(), O.f32_to_f16_bits(k_out.download(np.float32)))
+    assert np.array_equal(vc_h[:, pos, :].ravel(), O.f32_to_f16_bits(v_out.download(np.float32)))
+    other = np.ones(max_seq, bool)
+    other[pos] = False
+    assert not kc_h[:, other, :].any() and not vc_h[:, other, :].any()      # no other row touched
+
+
+@pytest.mark.parametrize("name", ["q4_0", "q8_0"])
+@pytest.mark.parametrize("D,F", [(256, 34), (512, 1377), (4096, 11008)])
+def test_fused_ffn_front(g, name, D, F):
+    if name == "q8_0" and D == 4096:
+        pytest.skip("large case covered by q4_0")
+    ofmt, gfmt = FMTS[name]
+    rng = np.random.default_rng(30 + F)
+    x = rng.normal(0, 1, D).astype(np.float32)
+    gamma = rng.normal(1, 0.1, D).astype(np.float32)
+    b1, b3 = make_blocks(rng, ofmt, F, D), make_blocks(rng, ofmt, F, D)
+    w1, w3 = g.Weight(b1, gfmt, F, D), g.Weight(b3, gfmt, F, D)
+    y = _nan_buffer(g, F)
+    g.check(g.cuda().greta_cuda_fused_ffn_front(None, gfmt, _dev(g, x).ptr, _dev(g, gamma).ptr, 1e-5, w1.qs.ptr, w1.d.ptr,
+                                                w3.qs.ptr, w3.d.ptr, y.ptr, D, F))
+    xn = O.rmsnorm(x.reshape(1, D), gamma, 1e-5)
+    want = O.silu_mul(O.gemv(xn, b1, ofmt, F, D), O.gemv(xn, b3, ofmt, F, D)).ravel()
+    assert max_abs_rel(y.download(np.float32), want) < TIGHT
+
+
+# ----------------------------------------------------------------------------- attention
+@pytest.mark.parametrize("H,Hkv,Dh,L,max_seq", [(4, 4, 128, 1, 8), (4, 4, 128, 63, 64), (8, 2, 64, 200, 256),
+                                                (32, 32, 128, 2049, 2304), (64, 8, 128, 777, 1024)])
+@pytest.mark.parametrize("use_dpos", [False, True])
+def test_attn_decode_matches_oracle(g, H, Hkv, Dh, L, max_seq, use_dpos):
+    rng = np.random.default_rng(40 + L)
+    q = rng.normal(0, 1, H * Dh).astype(np.float32)
+    kc = rng.normal(0, 1, (Hkv, max_seq, Dh)).astype(np.float16)
+    vc = rng.normal(0, 1, (Hkv, max_seq, Dh)).astype(np.float16)
+    scale = 1.0 / np.sqrt(Dh)
+    nbytes = g.cuda().greta_cuda_attn_decode_scratch_bytes(H, Dh)
+    scratch = g.DeviceBuffer(nbytes, zero=True)
+    o = _nan_buffer(g, H * Dh)
+    dpos = _dev(g, np.array([L - 1], np.uint32))
+    qd, kd, vd = _dev(g, q), _dev(g, kc.view(np.uint16)), _dev(g, vc.view(np.uint16))
+    want = O.attention_decode(q, kc.view(np.uint16), vc.view(np.uint16), H, Hkv, Dh, L, max_seq, scale)
+    for _ in range(2):       # twice: the split tickets must be left clean
+        o.fill(0xFF)
+        g.check(g.cuda().greta_cuda_attn_decode(None, qd.ptr, kd.ptr, vd.ptr, o.ptr, dpos.ptr if use_dpos else None,
+                                                0 if use_dpos else L, H, Hkv, Dh, max_seq, scale, scratch.ptr, nbytes))
+        got = o.download(np.float32)
+        assert np.isfinite(got).all()
+        assert max_abs_rel(got, want) < 1e-5
+    assert not scratch.download(np.uint32, H).any()
+
+
+def test_attn_decode_fp32_cache_as_in_the_reference(g):
+    rng = np.random.default_rng(41)
+    H, Hkv, Dh, L, max_seq = 8, 4, 128, 300, 320
+    q = rng.normal(0, 1, H * Dh).astype(np.float32)
+    kc = rng.normal(0, 1, (Hkv, max_seq, Dh)).astype(np.float32)
+    vc = rng.normal(0, 1, (Hkv, max_seq, Dh)).astype(np.float32)
+    nbytes = g.cuda().greta_cuda_attn_decode_scratch_bytes(H, Dh)
+    scratch = g.DeviceBuffer(nbytes, zero=True)
+    o = _nan_buffer(g, H * Dh)
+    g.check(g.cuda().greta_cuda_attn_decode_f32cache(None, _dev(g, q).ptr, _dev(g, kc).ptr, _dev(g, vc).ptr, o.ptr, None, L,
+                                                     H, Hkv, Dh, max_seq, 0.0883883, scratch.ptr, nbytes))
+    want = O.attention_decode(q, kc, vc, H, Hkv, Dh, L, max_seq, 0.0883883)
+    assert max_abs_rel(o.download(np.float32), want) < 1e-5
+
+
+def test_attn_prefill_causal(g):
+    rng = np.random.default_rng(42)
+    S, H, Hkv, Dh, max_seq = 70, 8, 4, 64, 96
+    q = rng.normal(0, 1, (S, H * Dh)).astype(np.float32)
+    k = rng.normal(0, 1, (S, Hkv * Dh)).astype(np.float32)
+    v = rng.normal(0, 1, (S, Hkv * Dh)).astype(np.float32)
+    kc = g.DeviceBuffer(Hkv * max_seq * Dh * 2, zero=True)
+    vc = g.DeviceBuffer(Hkv * max_seq * Dh * 2, zero=True)
+    g.check(g.cuda().greta_cuda_kv_update(None, kc.ptr, vc.ptr, _dev(g, k).ptr, _dev(g, v).ptr, S, 0, None, max_seq, Hkv, Dh))
+    kc_h = kc.download(np.uint16).reshape(Hkv, max_seq, Dh)
+    want_rows = O.f32_to_f16_bits(k).reshape(S, Hkv, Dh).transpose(1, 0, 2)
+    assert np.array_equal(kc_h[:, :S, :], want_rows) and not kc_h[:, S:, :].any()
+    o = _nan_buffer(g, S * H * Dh)
+    scale = 1.0 / np.sqrt(Dh)
+    g.check(g.cuda().greta_cuda_attn_prefill(None, _dev(g, q).ptr, kc.ptr, vc.ptr, o.ptr, S, 0, H, Hkv, Dh, max_seq, scale))
+    want = O.attention_prefill(q, k, v, S, H, Hkv, Dh, scale, causal=True, kv_round_f16=True)
+    assert max_abs_rel(o.download(np.float32).reshape(S, H * Dh), want) < 1e-5
+
+
+@pytest.mark.parametrize("use_dpos", [False, True])
+def test_rope_matches_oracle(g, use_dpos):
+    rng = np.random.default_rng(43)
+    S, H, Dh, pos = 5, 6, 128, 1234
+    x = rng.normal(0, 1, (S, H * Dh)).astype(np.float32)
+    xb = _dev(g, x)
+    dpos = _dev(g, np.array([pos], np.uint32))
+    g.check(g.cuda().greta_cuda_rope(None, xb.ptr, S, H, Dh, 10000.0, 0 if use_dpos else pos, dpos.ptr if use_dpos else None))
+    want = O.rope(x, S, H, Dh, 10000.0, pos)
+    assert max_abs_rel(xb.download(np.float32), want.ravel()) < 5e-4
+
+
+# ----------------------------------------------------------------------------- small operators
+def test_rmsnorm_add_silu_mul(g):
+    rng = np.random.default_rng(44)
+    rows, cols = 3, 4096
+    x = rng.uniform(-1, 1, (rows, cols)).astype(np.float32)     # the reference bench's distribution
+    gamma = rng.normal(1, 0.1, cols).astype(np.float32)
+    y = _nan_buffer(g, rows * cols)
+    g.check(g.cuda().greta_cuda_rmsnorm(None, _dev(g, x).ptr, _dev(g, gamma).ptr, y.ptr, rows, cols, 1e-5))
+    assert np.allclose(y.download(np.float32).reshape(rows, cols), O.rmsnorm(x, gamma, 1e-5), rtol=1e-5, atol=1e-6)
+    a = rng.normal(0, 1, 1000).astype(np.float32)
+    b = rng.normal(0, 1, 1000).astype(np.float32)
+    c = _nan_buffer(g, 1000)
+    g.check(g.cuda().greta_cuda_add(None, _dev(g, a).ptr, _dev(g, b).ptr, c.ptr, 1000))
+    assert np.array_equal(c.download(np.float32), a + b)
+    g.check(g.cuda().greta_cuda_silu_mul(None, _dev(g, a).ptr, _dev(g, b).ptr, c.ptr, 1000))
+    assert np.allclose(c.download(np.float32), O.silu_mul(a, b), rtol=1e-6, atol=1e-7)
+
+
+def test_embedding_and_argmax(g):
+    rng = np.random.default_rng(45)
+    vocab, dim = 300, 96
+    table = rng.normal(0, 0.02, (vocab, dim)).astype(np.float16)
+    toks = np.array([0, 299, 17, -1, 300, 5], np.int32)
+    out = _nan_buffer(g, toks.size * dim)
+    g.check(g.cuda().greta_cuda_embedding(None, _dev(g, toks).ptr, _dev(g, table.view(np.uint16)).ptr, 1, out.ptr,
+                                          toks.size, dim, vocab))
+    want = O.embedding(toks, table.view(np.uint16), dim, vocab)
+    assert np.array_equal(out.download(np.float32).reshape(toks.size, dim), want)
+    assert not want[3].any() and not want[4].any()      # out-of-range ids give zeros
+    res = g.DeviceBuffer(4)
+    for n in (1, 31, 1024, 32000, 128256):
+        logits = rng.normal(0, 1, n).astype(np.float32)
+        if n > 100:
+            logits[[n // 3, n // 3 + 57 if n // 3 + 57 < n else n - 1]] = 9.5     # an exact tie: first index wins
+        g.check(g.cuda().greta_cuda_argmax(None, _dev(g, logits).ptr, n, res.ptr))
+        assert int(res.download(np.int32)[0]) == O.argmax(logits)[0] == int(np.argmax(logits))
