@@ -1,0 +1,390 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-matmul decode path: Llama-2-7B-shaped model, Q4_0 weights, batch 1.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+One "step" is one greedy decode step (one token through all 32 layers, the LM head and the
+arg-max) after a 512-token random prompt.  The headline numbers printed in one JSON line:
+  value      tokens/s with every input resident in HBM (the step is one CUDA-graph launch with the
+             next token fed back on the device), timed with CUDA events on the model's stream;
+  e2e        the same through the reference-shaped host loop: per step the previous token id goes up
+             from pinned host memory and the sampled id comes back before the next step starts;
+  roofline   achieved HBM GB/s of the dominant kernel (the fused RMSNorm -> gate/up Q4_0 GEMV ->
+             SwiGLU), timed live over the 32 layers' distinct weights (3.6 GB touched per pass, far
+             beyond the 126 MB L2), against the measured copy bandwidth of this pool's B200s;
+  cpu_baseline  the CPU port of the reference's kernel math (oracle/, OpenMP) on a bounded sample.
+With --gpus N > 1 (launched under torchrun, one rank per GPU) the same model runs tensor-parallel
+over NCCL: the weights are sharded Megatron-style and each layer all-reduces twice.  Total work is
+fixed, so scaling is "strong".
+
+--impl reference times the CPU port itself (the reference ships no CPU implementation of this
+path and its GPU kernels are HIP/gfx942 only) on the host cores.
+"""
+import argparse
+import json
+import os
+import socket
+import struct
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+PROMPT_LEN = 512
+SEED = 3
+METRIC = "decode_tokens_per_s_llama2_7b_shape_q4_0_batch1"
+
+
+def load_pkg():
+    from _support import load_package
+    return load_package()
+
+
+def measured_peak_gbs():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device):
+        self.device, self.rows, self.proc = device, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.device)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        rows = [r for t, r in self.rows if t0 - 0.05 <= t <= t1 + 0.15 and len(r) >= 9] or [r for _, r in self.rows if len(r) >= 9]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        sm = sorted(float(r[1]) for r in rows)
+        reasons = set()
+        for r in rows:
+            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7), ("sw_power_cap", 8)):
+                if r[col].lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(rows[0][2]), "reasons": sorted(reasons), "samples": len(rows)}
+
+
+# ----------------------------------------------------------------------------- rendezvous (N > 1)
+class Ranks:
+    """Tiny TCP star on MASTER_ADDR for the NCCL id hand-out and for gathering per-rank timings."""
+
+    def __init__(self):
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.local = int(os.environ.get("LOCAL_RANK", str(self.rank)))
+        self.addr = os.environ.get("MASTER_ADDR", "127.0.0.1")
+        self.port = int(os.environ.get("MASTER_PORT", "29500")) + 1000
+        self.peers = []
+        if self.world > 1:
+            if self.rank == 0:
+                srv = socket.socket()
+                srv.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
+                srv.bind((self.addr, self.port))
+                srv.listen(self.world)
+                conns = {}
+                while len(conns) < self.world - 1:
+                    c, _ = srv.accept()
+                    r = struct.unpack("<i", self._recv(c, 4))[0]
+                    conns[r] = c
+                self.peers = [conns[r] for r in sorted(conns)]
+                srv.close()
+            else:
+                for _ in range(600):
+                    try:
+                        self.sock = socket.create_connection((self.addr, self.port), timeout=5)
+                        break
+                    except OSError:
+                        time.sleep(0.1)
+                else:
+                    raise RuntimeError("rank 0 not reachable")
+                self.sock.settimeout(None)
+                self.sock.sendall(struct.pack("<i", self.rank))
+
+    @staticmethod
+    def _recv(c, n):
+        buf = b""
+        while len(buf) < n:
+            chunk = c.recv(n - len(buf))
+            if not chunk:
+                raise RuntimeError("peer closed")
+            buf += chunk
+        return buf
+
+    def bcast(self, data, n):
+        if self.world == 1:
+            return data
+        if self.rank == 0:
+            for c in self.peers:
+                c.sendall(data)
+            return data
+        return self._recv(self.sock, n)
+
+    def gather_max(self, value):
+        if self.world == 1:
+            return value
+        if self.rank == 0:
+            vals = [value] + [struct.unpack("<d", self._recv(c, 8))[0] for c in self.peers]
+            return max(vals)
+        self.sock.sendall(struct.pack("<d", value))
+        return value
+
+    def barrier(self):
+        self.gather_max(0.0)
+        self.bcast(b"go!!", 4)
+
+
+# ----------------------------------------------------------------------------- CPU baseline (oracle port)
+def cpu_decode_layer_seconds(cfg, n_layers, reps):
+    """Times the CPU port on `n_layers` decoder layers of the 7B shape at batch 1 (fp32 accumulation, OpenMP over
+    output rows) and returns seconds per layer.  Weights are random GGUF Q4_0 blocks (values do not affect time)."""
+    from oracle import oracle as O
+    rng = np.random.default_rng(0)
+    D, F = cfg["dim"], cfg["hidden_dim"]
+    shapes = [(D, D)] * 4 + [(F, D), (F, D), (D, F)]
+
+    def blocks(n, k):
+        b = rng.integers(0, 256, (n * (k // 32), 18), dtype=np.uint8)
+        b[:, :2] = np.array([0.002], np.float16).view(np.uint8)
+        return b.reshape(-1)
+
+    layers = [[blocks(n, k) for n, k in shapes] for _ in range(n_layers)]
+    x = rng.normal(0, 1, D).astype(np.float32)
+    xf = rng.normal(0, 1, F).astype(np.float32)
+    O.gemv(x, layers[0][0], O.FMT_Q4_0, D, D, O.ACC_FAST_F32)      # warm-up (thread pool, page faults)
+    best = 1e30
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        for lw in layers:
+            for w, (n, k) in zip(lw, shapes):
+                O.gemv(x if k == D else xf, w, O.FMT_Q4_0, n, k, O.ACC_FAST_F32)
+        best = min(best, (time.perf_counter() - t0) / n_layers)
+    return best, O.num_threads()
+
+
+def cpu_baseline(cfg, n_layers=2, reps=3):
+    sec_per_layer, cores = cpu_decode_layer_seconds(cfg, n_layers, reps)
+    tok_s = 1.0 / (sec_per_layer * cfg["num_layers"])
+    return {"value": tok_s, "unit": "tok/s", "cores": cores, "kind": "port",
+            "sample": f"{n_layers} decoder layers of the 7B shape (7 Q4_0 GEMVs each, batch 1, fp32 accumulate), best of {reps}, "
+                      f"scaled to {cfg['num_layers']} layers; attention, LM head and element-wise work not included"}
+
+
+def run_reference(args, ranks, cfg):
+    """--impl reference: the CPU port of the reference's kernel math on the host cores."""
+    if ranks.rank != 0:
+        return
+    n_layers = 2
+    for _ in range(max(args.warmup, 1) if args.warmup < 2 else 1):
+        cpu_decode_layer_seconds(cfg, 1, 1)
+    times = []
+    for _ in range(args.steps):
+        sec, cores = cpu_decode_layer_seconds(cfg, n_layers, 1)
+        times.append(sec * cfg["num_layers"])
+    ms = 1e3 * float(np.mean(times))
+    val = 1e3 / ms
+    sample = (f"each step = {n_layers} decoder layers of the 7B shape on the CPU port (oracle/greta_oracle.cpp, fp32 accumulate, "
+              f"OpenMP), scaled to {cfg['num_layers']} layers")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "q4_0 weights, fp32 activations/accumulation", "data": "synthetic",
+        "config": {"workload": "Llama-2-7B-shaped decode, batch 1, Q4_0 (BASELINE config 4 shape), CPU port of the reference kernel math",
+                   "note": "the reference has no CPU implementation of this path and its GPU kernels are HIP/gfx942 only"},
+        "cpu_baseline": {"value": val, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ----------------------------------------------------------------------------- roofline of the dominant kernel
+def time_dominant_kernel(pkg, cfg, tp, reps=4):
+    """Fused RMSNorm -> gate/up GEMV -> SwiGLU over 32 distinct weight sets, captured in one graph, CUDA events."""
+    import ctypes as C
+    g = pkg.ffi
+    lib = g.cuda()
+    D, F = cfg["dim"], cfg["hidden_dim"] // tp
+    L = cfg["num_layers"]
+    rng = np.random.default_rng(0)
+    nb = F * (D // 32)
+    qs_h = rng.integers(0, 256, nb * 16, dtype=np.uint8)
+    d_h = (np.abs(rng.normal(0, 0.02, nb)) / 8).astype(np.float16).view(np.uint16)
+    sets = [(g.DeviceBuffer.from_numpy(qs_h), g.DeviceBuffer.from_numpy(d_h), g.DeviceBuffer.from_numpy(qs_h),
+             g.DeviceBuffer.from_numpy(d_h)) for _ in range(L)]
+    x = g.DeviceBuffer.from_numpy(rng.normal(0, 1, D).astype(np.float32))
+    gam = g.DeviceBuffer.from_numpy(np.ones(D, np.float32))
+    y = g.DeviceBuffer(F * 4)
+    stream = C.c_void_p()
+    g.check(lib.greta_cuda_stream_create(C.byref(stream)))
+
+    def one_pass():
+        for a, b, c, d in sets:
+            g.check(lib.greta_cuda_fused_ffn_front(stream, g.FMT_Q4_0, x.ptr, gam.ptr, 1e-5, a.ptr, b.ptr, c.ptr, d.ptr, y.ptr, D, F))
+
+    one_pass()
+    g.check(lib.greta_cuda_stream_synchronize(stream))
+    graph, ex, e0, e1 = C.c_void_p(), C.c_void_p(), C.c_void_p(), C.c_void_p()
+    g.check(lib.greta_cuda_graph_capture_begin(stream))
+    one_pass()
+    g.check(lib.greta_cuda_graph_capture_end(stream, C.byref(graph)))
+    g.check(lib.greta_cuda_graph_instantiate(graph, C.byref(ex)))
+    lib.greta_cuda_event_create(C.byref(e0))
+    lib.greta_cuda_event_create(C.byref(e1))
+    for _ in range(3):
+        lib.greta_cuda_graph_launch(ex, stream)
+    lib.greta_cuda_stream_synchronize(stream)
+    lib.greta_cuda_event_record(e0, stream)
+    for _ in range(reps):
+        lib.greta_cuda_graph_launch(ex, stream)
+    lib.greta_cuda_event_record(e1, stream)
+    lib.greta_cuda_event_synchronize(e1)
+    ms = C.c_float()
+    lib.greta_cuda_event_elapsed_ms(e0, e1, C.byref(ms))
+    us = ms.value * 1e3 / (reps * L)
+    alg_bytes = 2 * nb * 18 + 2 * D * 4 + F * 4          # both weight matrices + x + gamma in, y out
+    for s in sets:
+        for b in s:
+            b.free()
+    return us, alg_bytes
+
+
+# ----------------------------------------------------------------------------- main
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
+    ap.add_argument("--prefill-chunk", type=int, default=32, help="tokens per prefill call (0 = the whole prompt at once)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    ranks = Ranks()
+    if ranks.world != args.gpus and ranks.world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={ranks.world}")
+
+    pkg = load_pkg()
+    from gretacore_v3_b200.model import LLAMA2_7B
+    cfg = dict(LLAMA2_7B)
+    if args.impl == "reference":
+        run_reference(args, ranks, cfg)
+        return
+
+    import ctypes as C
+    g = pkg.ffi
+    g.require_device()                       # raises when the CUDA library or a device is missing: no CPU fallback
+    lib = g.cuda()
+    g.check(lib.greta_cuda_set_device(ranks.local))
+    tp = ranks.world
+    model = pkg.model.Model(cfg, tp_rank=ranks.rank, tp_size=tp)
+    if tp > 1:
+        uid = (C.c_char * 128)()
+        if ranks.rank == 0:
+            g.check(lib.greta_cuda_comm_unique_id(uid))
+        raw = ranks.bcast(bytes(uid.raw), 128)
+        comm = C.c_void_p()
+        idbuf = C.create_string_buffer(raw, 128)
+        g.check(lib.greta_cuda_comm_init(C.byref(comm), idbuf, tp, ranks.rank), "comm_init")
+        model.set_comm(comm)
+    model.load_synthetic(SEED)
+    prompt = pkg.model.synth_tokens(SEED, args.prompt_len, cfg["vocab"])
+    chunk = args.prefill_chunk or args.prompt_len           # prefill (not timed); chunks <= 32 take the GEMV route
+    for c0 in range(0, args.prompt_len, chunk):
+        logits = model.forward(prompt[c0:c0 + chunk], c0)
+    first = int(np.argmax(logits))
+    pos = args.prompt_len
+
+    # ---- value: device-resident decode loop, CUDA events, max over ranks
+    model.begin_decode(first, pos)
+    model.decode_timed(max(args.warmup, 3))
+    sampler = ClockSampler(ranks.local)
+    if ranks.rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    ranks.barrier()
+    g.check(lib.greta_cuda_device_synchronize())
+    launches0 = lib.greta_cuda_launch_count()
+    t0 = time.time()
+    ms = model.decode_timed(args.steps)
+    g.check(lib.greta_cuda_device_synchronize())
+    t1 = time.time()
+    launches = lib.greta_cuda_launch_count() - launches0
+    ms = ranks.gather_max(float(ms))
+    clocks = sampler.stop(t0, t1) if ranks.rank == 0 else None
+    ids_dev = model.read_generated(max(args.warmup, 3) + args.steps)
+
+    # ---- e2e: host-driven loop (token id up, sampled id down, every step), restarted from the same state
+    ranks.barrier()
+    ids_e2e, ms_e2e = model.decode_e2e(first, pos, max(args.warmup, 3))      # warm-up of this loop
+    ids_e2e, ms_e2e = model.decode_e2e(first, pos, args.steps)
+    ms_e2e = ranks.gather_max(float(ms_e2e))
+    same = ids_e2e == ids_dev[:args.steps]
+
+    if ranks.rank != 0:
+        return
+    # ---- roofline of the dominant kernel and the CPU baseline (rank 0)
+    model.close()
+    us, alg = time_dominant_kernel(pkg, cfg, tp)
+    peak, peak_src = measured_peak_gbs()
+    achieved = alg / us / 1e3
+    roofline = {"bound": "hbm", "kernel": "gemv_pipe_kernel<Q4_0, SwiGLU> (fused RMSNorm -> gate/up GEMV -> SwiGLU)",
+                "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": f"of {peak_src}",
+                "us_per_launch": us, "algorithmic_bytes_per_launch": alg, "traffic": None}
+    tok_s = 1e3 * args.steps / ms
+    # whole-step view of the same bound: bytes one decode step must read
+    step_bytes = model_step_bytes(cfg, pos + args.steps // 2)
+    out = {
+        "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "q4_0 weights (int8 dot products on 23-bit fixed-point activations), fp32 accumulation, fp16 KV cache",
+        "data": "synthetic",
+        "config": {"workload": "Llama-2-7B-shaped model (32 layers, hidden 4096, 32 heads x 128, FFN 11008, vocab 32000), random-init "
+                               "Q4_0 weights, fp16 LM head, 512-token random prompt then greedy decode at batch 1 (BASELINE config 4)",
+                   "prompt_len": args.prompt_len, "parallelism": f"tp{tp}" if tp > 1 else "single GPU",
+                   "l2_defeat": "every step streams 3.9 GB of distinct weights (L2 is 126 MB)", "seed": SEED},
+        "clocks": clocks, "gpu_launches": int(launches),
+        "e2e": {"value": 1e3 * args.steps / ms_e2e, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4,
+                "ids_match_device_loop": bool(same)},
+        "roofline": roofline,
+        "step_hbm": {"bytes_per_step": step_bytes, "achieved_gbs": step_bytes / (ms / args.steps) / 1e6,
+                     "frac_of_peak": step_bytes / (ms / args.steps) / 1e6 / peak},
+    }
+    if not args.no_cpu_baseline:
+        out["cpu_baseline"] = cpu_baseline(cfg)
+    print(json.dumps(out))
+
+
+def model_step_bytes(cfg, pos):
+    D, F, L, V = cfg["dim"], cfg["hidden_dim"], cfg["num_layers"], cfg["vocab"]
+    kv = cfg["num_heads_kv"] * cfg["head_dim"]
+    w = L * ((2 * D * D + 2 * D * kv + 3 * D * F) * 18 // 32)
+    return w + V * D * 2 + L * 2 * kv * 2 * (pos + 1)
+
+
+if __name__ == "__main__":
+    main()

@@ -106,6 +106,17 @@ __global__ void add_kernel(const float *a, const float *b, float *c, size_t n) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) c[i] = a[i] + b[i];
 }
+__global__ void silu_kernel(const float *x, float *y, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) {
+    float v = x[i];
+    y[i] = v / (1.0f + expf(-v));
+  }
+}
+__global__ void mul_kernel(const float *a, const float *b, float *c, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) c[i] = a[i] * b[i];
+}
 __global__ void silu_mul_kernel(const float *g, const float *u, float *y, size_t n) {
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) {
@@ -131,7 +142,8 @@ __global__ void embedding_kernel(const int32_t *__restrict__ tokens, const void 
 
 // Single CTA, 1024 threads: first maximum (lowest index among equal values).
 __global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ logits, uint32_t n,
-                                                      int32_t *__restrict__ out) {
+                                                      int32_t *__restrict__ out, uint32_t *d_pos, int32_t *out_tokens,
+                                                      uint32_t *d_count, uint32_t out_capacity) {
   __shared__ float sv[32];
   __shared__ uint32_t si[32];
   float best = -INFINITY;
@@ -139,10 +151,8 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ 
   for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
     float v = logits[i];
     if (v > best || bi == 0xffffffffu) {   // strided scan keeps the lowest index of this thread's maximum
-      if (v > best || bi == 0xffffffffu) {
-        best = v;
-        bi = i;
-      }
+      best = v;
+      bi = i;
     }
   }
   auto better = [](float v, uint32_t i, float bv, uint32_t bidx) { return v > bv || (v == bv && i < bidx); };
@@ -173,7 +183,15 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ 
         bi = oi;
       }
     }
-    if (l == 0) *out = (int32_t)bi;
+    if (l == 0) {
+      *out = (int32_t)bi;
+      if (d_count) {
+        uint32_t c = *d_count;
+        if (out_tokens && c < out_capacity) out_tokens[c] = (int32_t)bi;
+        *d_count = c + 1;
+      }
+      if (d_pos) *d_pos = *d_pos + 1;
+    }
   }
 }
 
@@ -268,8 +286,27 @@ int greta_cuda_embedding(greta_stream_t stream, const int32_t *tokens, const voi
 int greta_cuda_argmax(greta_stream_t stream, const float *logits, uint32_t n, int32_t *d_out) {
   GRETA_REQUIRE(n > 0, "argmax: empty input");
   GRETA_REQUIRE(logits && d_out, "argmax: null pointer");
-  argmax_kernel<<<1, 1024, 0, S(stream)>>>(logits, n, d_out);
+  argmax_kernel<<<1, 1024, 0, S(stream)>>>(logits, n, d_out, nullptr, nullptr, nullptr, 0);
   return launched("argmax_kernel");
+}
+int greta_cuda_argmax_advance(greta_stream_t stream, const float *logits, uint32_t n, int32_t *d_next, uint32_t *d_pos,
+                              int32_t *d_out_tokens, uint32_t *d_count, uint32_t out_capacity) {
+  GRETA_REQUIRE(n > 0, "argmax_advance: empty input");
+  GRETA_REQUIRE(logits && d_next, "argmax_advance: null pointer");
+  argmax_kernel<<<1, 1024, 0, S(stream)>>>(logits, n, d_next, d_pos, d_out_tokens, d_count, out_capacity);
+  return launched("argmax_kernel");
+}
+int greta_cuda_silu(greta_stream_t stream, const float *x, float *y, size_t n) {
+  if (n == 0) return GRETA_OK;
+  GRETA_REQUIRE(x && y, "silu: null pointer");
+  silu_kernel<<<blocks_for(n, 256), 256, 0, S(stream)>>>(x, y, n);
+  return launched("silu_kernel");
+}
+int greta_cuda_mul(greta_stream_t stream, const float *a, const float *b, float *c, size_t n) {
+  if (n == 0) return GRETA_OK;
+  GRETA_REQUIRE(a && b && c, "mul: null pointer");
+  mul_kernel<<<blocks_for(n, 256), 256, 0, S(stream)>>>(a, b, c, n);
+  return launched("mul_kernel");
 }
 
 }  // extern "C"

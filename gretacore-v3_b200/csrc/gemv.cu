@@ -166,9 +166,13 @@ __device__ __forceinline__ void epilogue(const GemvParams &p, uint32_t grp, uint
 #pragma unroll
       for (int j = 0; j < PAIRS; ++j) {
         uint32_t i = (g % gph) * PAIRS + j;
-        float theta = (float)pos * powf(p.rope_base, -2.0f * (float)i / (float)p.Dh);
-        float c = cosf(theta), s = sinf(theta);
-        float o0 = v[j] * c - v[j + PAIRS] * s, o1 = v[j] * s + v[j + PAIRS] * c;
+        float o0 = v[j], o1 = v[j + PAIRS];
+        if (p.d_pos) {
+          float theta = (float)pos * powf(p.rope_base, -2.0f * (float)i / (float)p.Dh);
+          float c = cosf(theta), s = sinf(theta);
+          o0 = v[j] * c - v[j + PAIRS] * s;
+          o1 = v[j] * s + v[j + PAIRS] * c;
+        }
         if (is_q) {
           p.q_out[head * p.Dh + i] = o0;
           p.q_out[head * p.Dh + i + p.Dh / 2] = o1;
@@ -177,9 +181,11 @@ __device__ __forceinline__ void epilogue(const GemvParams &p, uint32_t grp, uint
             p.k_out[head * p.Dh + i] = o0;
             p.k_out[head * p.Dh + i + p.Dh / 2] = o1;
           }
-          size_t dst = ((size_t)head * p.max_seq + pos) * p.Dh + i;
-          p.k_cache[dst] = __float2half_rn(o0);
-          p.k_cache[dst + p.Dh / 2] = __float2half_rn(o1);
+          if (p.k_cache) {
+            size_t dst = ((size_t)head * p.max_seq + pos) * p.Dh + i;
+            p.k_cache[dst] = __float2half_rn(o0);
+            p.k_cache[dst + p.Dh / 2] = __float2half_rn(o1);
+          }
         }
       }
     } else {
@@ -189,7 +195,7 @@ __device__ __forceinline__ void epilogue(const GemvParams &p, uint32_t grp, uint
         if (row < p.Hkv * p.Dh) {
           if (p.v_out) p.v_out[row] = v[r];
           uint32_t head = row / p.Dh, dd = row % p.Dh;
-          p.v_cache[((size_t)head * p.max_seq + pos) * p.Dh + dd] = __float2half_rn(v[r]);
+          if (p.v_cache) p.v_cache[((size_t)head * p.max_seq + pos) * p.Dh + dd] = __float2half_rn(v[r]);
         }
       }
     }
@@ -376,7 +382,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_simple_kernel(const GemvParam
   }
   __syncthreads();
 
-  const uint32_t pos = (EPI == EPI_QKV) ? *p.d_pos : 0u;
+  const uint32_t pos = (EPI == EPI_QKV && p.d_pos) ? *p.d_pos : 0u;
 
   for (uint32_t it = 0; it < p.iters; ++it) {
     float acc[R];
@@ -750,7 +756,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pipe_kernel(const GemvParams 
   __syncthreads();
 
   // ---- epilogue: one thread per row group, contributions summed in warp order ----
-  const uint32_t pos = (EPI == EPI_QKV) ? *p.d_pos : 0u;
+  const uint32_t pos = (EPI == EPI_QKV && p.d_pos) ? *p.d_pos : 0u;
   for (uint32_t g = g0 + threadIdx.x; g < g1; g += THREADS) {
     const uint32_t lo = (g - g0) * C, hi = lo + C;  // this group's cells
     float v[R];
@@ -860,6 +866,7 @@ int dispatch_quant(cudaStream_t stream, int fmt, const GemvParams &p, uint64_t t
   switch (fmt) {
     case GRETA_FMT_Q4_0: return launch_quant<GRETA_FMT_Q4_0, EPI>(stream, p, total_rows);
     case GRETA_FMT_Q8_0: return launch_quant<GRETA_FMT_Q8_0, EPI>(stream, p, total_rows);
+    case GRETA_FMT_F16: return launch_any<GRETA_FMT_F16, EPI, 2>(stream, p);
     default: break;
   }
   set_error("gemv: format %d is not supported by this operator", fmt);
@@ -909,6 +916,24 @@ int greta_cuda_gemv(greta_stream_t stream, int fmt, const void *x, int x_is_f16,
   }
 }
 
+int greta_cuda_rmsnorm_gemv(greta_stream_t stream, int fmt, const float *x, const float *gamma, float eps, const void *qs,
+                            const void *d, float *y, uint32_t N, uint32_t K) {
+  if (N == 0 || K == 0) return GRETA_OK;
+  GRETA_REQUIRE(K % 32 == 0, "rmsnorm_gemv: K=%u is not a multiple of 32", K);
+  GRETA_REQUIRE(x && y && gamma, "rmsnorm_gemv: null pointer");
+  if (int rc = check_plane("rmsnorm_gemv", qs, d, fmt)) return rc;
+  GemvParams p{};
+  p.x = x;
+  p.gamma = gamma;
+  p.eps = eps;
+  p.w[0] = {(const uint8_t *)qs, d};
+  p.K = K;
+  p.N = N;
+  p.M = 1;
+  p.y = y;
+  return dispatch_quant<EPI_PLAIN>((cudaStream_t)stream, fmt, p, N);
+}
+
 int greta_cuda_gemv_residual(greta_stream_t stream, int fmt, const float *x, const void *qs, const void *d,
                              const float *resid, float *y, uint32_t N, uint32_t K) {
   if (N == 0 || K == 0) return GRETA_OK;
@@ -935,7 +960,9 @@ int greta_cuda_fused_rmsnorm_qkv_rope_kv(greta_stream_t stream, int fmt, const f
   GRETA_REQUIRE(D % 32 == 0, "fused_qkv: D=%u is not a multiple of 32", D);
   GRETA_REQUIRE(Dh % 2 == 0, "fused_qkv: head_dim=%u is odd", Dh);
   GRETA_REQUIRE(H % Hkv == 0, "fused_qkv: num_heads=%u is not a multiple of num_heads_kv=%u", H, Hkv);
-  GRETA_REQUIRE(x && q_out && k_cache && v_cache && d_pos, "fused_qkv: null pointer");
+  GRETA_REQUIRE(x && q_out, "fused_qkv: null pointer");
+  GRETA_REQUIRE(d_pos ? (k_cache && v_cache) : (k_out && v_out),
+                "fused_qkv: with d_pos the caches are required, without it k_out and v_out");
   if (int rc = check_plane("fused_qkv(wq)", wq_qs, wq_d, fmt)) return rc;
   if (int rc = check_plane("fused_qkv(wk)", wk_qs, wk_d, fmt)) return rc;
   if (int rc = check_plane("fused_qkv(wv)", wv_qs, wv_d, fmt)) return rc;

@@ -1,0 +1,3 @@
+// Same include path as in the reference tree; the GretaCompute / GretaFused live in gcore/greta_b200.hpp.
+#pragma once
+#include "gcore/greta_b200.hpp"

@@ -130,6 +130,13 @@ GRETA_API int greta_cuda_gemv(greta_stream_t stream, int fmt, const void *x, int
                               const void *qs, const void *d, float *y, uint32_t M, uint32_t N,
                               uint32_t K);
 
+/* y[N] = dequant(W)[N x K] * rmsnorm(x, gamma, eps)   (M = 1): the final norm fused
+ * into the LM-head projection (launch_rmsnorm_naive + gemm, block_scheduler.cpp:4207,
+ * 4295-4304, on the last position only).  Formats: Q4_0, Q8_0, F16. */
+GRETA_API int greta_cuda_rmsnorm_gemv(greta_stream_t stream, int fmt, const float *x, const float *gamma,
+                                      float eps, const void *qs, const void *d, float *y, uint32_t N,
+                                      uint32_t K);
+
 /* y[N] = resid[N] + dequant(W)[N x K] * x[K]   (M = 1; y may alias resid).
  * O-projection / down-projection followed by the residual add
  * (block_scheduler.cpp:2769-2775 + launch_add :2896; :3003-3006 + :3032). */
@@ -141,6 +148,8 @@ GRETA_API int greta_cuda_gemv_residual(greta_stream_t stream, int fmt, const flo
  * rotate-half RoPE at position *d_pos on q and k; q -> q_out fp32 [H*Dh];
  * k, v -> fp16 caches [Hkv][max_seq][Dh] at row *d_pos.  gamma may be NULL (no
  * norm).  k_out / v_out (fp32 [Hkv*Dh], post-RoPE k) are optional copies.
+ * With d_pos == NULL no rotation is applied and nothing is cached: q, k, v go to
+ * q_out / k_out / v_out only (all three required then).  Formats: Q4_0, Q8_0, F16.
  * Replaces launch_rmsnorm_naive + 3 x GretaCompute::gemm + 2 x launch_rope +
  * launch_kv_update (block_scheduler.cpp:1814-1977) and is the Q4_0/Q8_0 form of
  * launch_fused_rmsnorm_qkv_gemv_f16 (fused_compute_kernels.hip:22-157) and
@@ -221,6 +230,9 @@ GRETA_API int greta_cuda_rmsnorm(greta_stream_t stream, const float *x, const fl
                                  uint32_t rows, uint32_t cols, float eps);
 /* launch_add (basic_kernels.hip:127-140). */
 GRETA_API int greta_cuda_add(greta_stream_t stream, const float *a, const float *b, float *c, size_t n);
+/* launch_silu, launch_mul (basic_kernels.hip:141-167), separately. */
+GRETA_API int greta_cuda_silu(greta_stream_t stream, const float *x, float *y, size_t n);
+GRETA_API int greta_cuda_mul(greta_stream_t stream, const float *a, const float *b, float *c, size_t n);
 /* launch_silu then launch_mul in one pass (basic_kernels.hip:141-167): y = silu(gate) * up. */
 GRETA_API int greta_cuda_silu_mul(greta_stream_t stream, const float *gate, const float *up, float *y,
                                   size_t n);
@@ -232,6 +244,23 @@ GRETA_API int greta_cuda_embedding(greta_stream_t stream, const int32_t *tokens,
 /* launch_argmax (basic_kernels.hip:330-373) without its per-call allocation and
  * synchronisation: writes the index of the first maximum to *d_out (device). */
 GRETA_API int greta_cuda_argmax(greta_stream_t stream, const float *logits, uint32_t n, int32_t *d_out);
+/* Arg-max that also closes a decode step on the device, so the next step can start
+ * without a host round trip (the reference returns to the host for every token,
+ * generator.cpp:1142-1156): *d_next = id; d_out_tokens[*d_count] = id when
+ * *d_count < out_capacity; ++*d_count; ++*d_pos. */
+GRETA_API int greta_cuda_argmax_advance(greta_stream_t stream, const float *logits, uint32_t n,
+                                        int32_t *d_next, uint32_t *d_pos, int32_t *d_out_tokens,
+                                        uint32_t *d_count, uint32_t out_capacity);
+
+/* ------------------------------------------------------------------ tensor-parallel exchange
+ * The reference is single-GPU (hipSetDevice(0), greta_runtime_hip.cpp:153); these are new.
+ * One process per GPU; NCCL over NVLink / NVSwitch.  unique_id128 is a 128-byte buffer made on
+ * rank 0 and handed to every rank by the launcher. */
+GRETA_API int greta_cuda_comm_unique_id(void *unique_id128);
+GRETA_API int greta_cuda_comm_init(void **comm, const void *unique_id128, int nranks, int rank);
+GRETA_API int greta_cuda_comm_destroy(void *comm);
+/* In-place sum over ranks of `count` floats, enqueued on `stream` (capturable into a graph). */
+GRETA_API int greta_cuda_comm_allreduce_f32(void *comm, float *buf, size_t count, greta_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,76 @@
+/*
+ * greta_host.h - C handles onto the C++ host layer (libgreta_host.so), for
+ * callers that are not C++: the Python tests and the benchmark drive the model
+ * through these.  Each function forwards to the gcore::inference class method
+ * named beside it (include/gcore/greta_b200.hpp), which mirrors the reference's
+ * BlockScheduler / Generator (src/inference/include/gcore/inference/
+ * block_scheduler.hpp:67-142, generator.hpp:55-90).  Return 0 on success,
+ * non-zero on failure with the text in greta_host_last_error().
+ */
+#ifndef GRETA_HOST_H
+#define GRETA_HOST_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#ifndef GRETA_API
+#define GRETA_API __attribute__((visibility("default")))
+#endif
+
+typedef void *greta_model_t;
+
+/* Same fields as gcore::inference::ModelConfig. weight_fmt / lm_head_fmt take GRETA_FMT_* values. */
+typedef struct greta_model_config {
+  uint32_t dim, num_heads, num_heads_kv, num_layers, vocab_size, hidden_dim, head_dim, max_seq_len;
+  float rope_base, rms_eps;
+  int weight_fmt, lm_head_fmt;
+  uint32_t tp_rank, tp_size;
+} greta_model_config;
+
+GRETA_API const char *greta_host_last_error(void);
+
+/* gcore::inference::synth: seeded, counter-based synthetic tensors (host memory). */
+GRETA_API int greta_host_synth_quant_blocks(uint64_t seed, uint64_t stream, int fmt, void *out, size_t first_block, size_t n_blocks);
+GRETA_API int greta_host_synth_normal_f16(uint64_t seed, uint64_t stream, float sigma, void *out_f16, size_t first, size_t n);
+GRETA_API int greta_host_synth_normal_f16_as_f32(uint64_t seed, uint64_t stream, float sigma, float *out, size_t first, size_t n);
+GRETA_API int greta_host_synth_normal_f32(uint64_t seed, uint64_t stream, float sigma, float *out, size_t first, size_t n);
+GRETA_API int greta_host_synth_tokens(uint64_t seed, uint64_t stream, uint32_t vocab, int32_t *out, size_t n);
+GRETA_API uint64_t greta_host_tensor_stream(uint32_t layer, int which);
+
+/* BlockScheduler::init + allocate_weights + allocate_activations(1, max_seq_len). */
+GRETA_API int greta_model_create(const greta_model_config *cfg, greta_model_t *out);
+GRETA_API int greta_model_destroy(greta_model_t m);
+GRETA_API int greta_model_load_synthetic(greta_model_t m, uint64_t seed);                 /* load_synthetic_weights */
+/* set_layer_tensor / set_global_tensor: `which` is a LayerTensor / GlobalTensor value; host points at the GLOBAL tensor. */
+GRETA_API int greta_model_set_layer_tensor(greta_model_t m, uint32_t layer, int which, const void *host, size_t bytes);
+GRETA_API int greta_model_set_global_tensor(greta_model_t m, int which, const void *host, size_t bytes);
+GRETA_API int greta_model_forward(greta_model_t m, const int32_t *tokens, uint32_t seq_start, uint32_t seq_len);  /* forward */
+GRETA_API int greta_model_get_logits(greta_model_t m, float *out, uint32_t n);           /* get_logits() -> host */
+GRETA_API int greta_model_get_hidden(greta_model_t m, float *out, uint32_t row, uint32_t n); /* get_hidden_state() row -> host */
+GRETA_API int greta_model_sample_greedy(greta_model_t m, int32_t *id);                   /* sample_greedy_gpu */
+/* Generator::generate_tokens (greedy). stats5 = {prompt tokens, generated tokens, total ms, time to first token ms, decode ms}. */
+GRETA_API int greta_model_generate(greta_model_t m, const int32_t *prompt, uint32_t n_prompt, uint32_t n_new, int32_t *out,
+                                   double *stats5);
+GRETA_API int greta_model_begin_decode(greta_model_t m, int32_t first_token, uint32_t pos); /* begin_decode */
+GRETA_API int greta_model_decode_step(greta_model_t m);                                   /* decode_step (asynchronous) */
+GRETA_API int greta_model_read_generated(greta_model_t m, int32_t *out, uint32_t n);      /* read_generated (synchronises) */
+/* `steps` decode_step() calls bracketed by events on the model's stream; *ms = device time. */
+GRETA_API int greta_model_decode_timed(greta_model_t m, uint32_t steps, float *ms);
+/* The reference's decode loop shape (src/inference/src/generator.cpp:1128-1156): every step uploads the
+ * previous token id from pinned host memory, runs forward for one position and reads the sampled id back
+ * to the host before the next step.  *ms = device time of the whole loop (events), copies included;
+ * out receives the `steps` ids.  Bytes per step: 4 up, 4 down. */
+GRETA_API int greta_model_decode_e2e(greta_model_t m, int32_t first_token, uint32_t pos, uint32_t steps, int32_t *out, float *ms);
+GRETA_API uint64_t greta_model_weight_bytes(greta_model_t m);
+GRETA_API void *greta_model_stream(greta_model_t m);
+/* Installs the tensor-parallel exchange: an NCCL communicator made with greta_cuda_comm_init. */
+GRETA_API int greta_model_set_comm(greta_model_t m, void *comm);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GRETA_HOST_H */
