@@ -14,6 +14,7 @@
 #include <math.h>
 
 #include <algorithm>
+#include <mutex>
 
 #include "greta_common.cuh"
 
@@ -287,6 +288,46 @@ int greta_cuda_attn_decode_f32cache(greta_stream_t stream, const float *q, const
                                     const uint32_t *d_pos, uint32_t seq_len, uint32_t H, uint32_t Hkv, uint32_t Dh,
                                     uint32_t max_seq, float scale, void *scratch, size_t scratch_bytes) {
   return attn_decode_impl<float>(stream, q, kc, vc, o, d_pos, seq_len, H, Hkv, Dh, max_seq, scale, scratch, scratch_bytes);
+}
+
+// ---- allocation-free variant --------------------------------------------------------------
+// Scratch for greta_cuda_attn_decode_static: lives in the module image, so every GPU that loads
+// this library carries it (about 1 MiB) until the process exits.  Sized for 64 query heads of
+// head_dim 128: the ticket words first, then the per-split partial results.
+constexpr uint32_t STATIC_MAX_HEADS = 64, STATIC_MAX_HEAD_DIM = 128;
+constexpr size_t STATIC_SCRATCH_BYTES = 256 + (size_t)STATIC_MAX_HEADS * MAX_SPLITS * (STATIC_MAX_HEAD_DIM + 2) * sizeof(float);
+static __device__ __align__(256) unsigned char g_static_attn_scratch[STATIC_SCRATCH_BYTES];
+
+// In host code the array's name is only a handle for the runtime, not an address a kernel can
+// use; the device address is looked up once per device, with that device current.
+static int static_scratch_address(void **out) {
+  static std::mutex mu;
+  static void *addr[64] = {};
+  int dev = 0;
+  GRETA_CUDA_TRY(cudaGetDevice(&dev));
+  GRETA_REQUIRE(dev >= 0 && dev < 64, "attn_decode_static: device index %d out of range", dev);
+  std::lock_guard<std::mutex> lk(mu);
+  if (!addr[dev]) {
+    void *p = nullptr;
+    GRETA_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_attn_scratch));
+    addr[dev] = p;
+  }
+  *out = addr[dev];
+  return GRETA_OK;
+}
+
+int greta_cuda_attn_decode_static(greta_stream_t stream, const float *q, const void *kc, const void *vc, float *o,
+                                  const uint32_t *d_pos, uint32_t seq_len, uint32_t H, uint32_t Hkv, uint32_t Dh,
+                                  uint32_t max_seq, float scale) {
+  GRETA_REQUIRE(H <= STATIC_MAX_HEADS && Dh <= STATIC_MAX_HEAD_DIM,
+                "attn_decode_static: %u heads of dim %u exceed the built-in scratch (at most %u heads of dim %u); "
+                "use greta_cuda_attn_decode with caller-provided scratch",
+                H, Dh, STATIC_MAX_HEADS, STATIC_MAX_HEAD_DIM);
+  void *scratch = nullptr;
+  if (int rc = static_scratch_address(&scratch)) return rc;
+  // The array keeps whatever the previous call left; the tickets must start at zero.
+  GRETA_CUDA_TRY(cudaMemsetAsync(scratch, 0, counters_bytes(H), (cudaStream_t)stream));
+  return attn_decode_impl<__half>(stream, q, kc, vc, o, d_pos, seq_len, H, Hkv, Dh, max_seq, scale, scratch, STATIC_SCRATCH_BYTES);
 }
 
 int greta_cuda_attn_prefill(greta_stream_t stream, const float *q, const void *kc, const void *vc, float *o, uint32_t S,

@@ -203,6 +203,23 @@ GRETA_API int greta_cuda_attn_decode_f32cache(greta_stream_t stream, const float
                                               uint32_t num_heads, uint32_t num_heads_kv,
                                               uint32_t head_dim, uint32_t max_seq_len, float scale,
                                               void *scratch, size_t scratch_bytes);
+/* Decode attention for callers that must not allocate and have no scratch to lend.  No counterpart in
+ * the reference: its launchers take no scratch argument because its attention kernel needs none, and
+ * the split-sequence kernel here does.  Such callers are, for example, a host application that gives
+ * this library raw pointers out of a memory pool it owns in full (a fixed budget, no cudaMalloc allowed
+ * after start-up), or code on a latency-critical serving path where cudaMalloc / cudaFree would
+ * synchronise the whole device.  Same arguments and results as greta_cuda_attn_decode (fp16 cache), minus
+ * the scratch: the partial results go to an array built into the library, about 1 MiB that every GPU
+ * loading the library holds until the process exits.  Limit: num_heads <= 64 and head_dim <= 128 (larger
+ * shapes are rejected with GRETA_ERR_INVALID_ARGS; use greta_cuda_attn_decode).  The call allocates
+ * nothing.  Its first call on a device looks up the array's device address; make that call outside any
+ * stream capture.  All calls share the one array and it keeps the last call's contents (the call clears
+ * the words that must start at zero), so two calls that may overlap on the GPU - different streams without
+ * an ordering between them - race; keep them on one stream or order them with events. */
+GRETA_API int greta_cuda_attn_decode_static(greta_stream_t stream, const float *q, const void *k_cache_f16,
+                                            const void *v_cache_f16, float *o, const uint32_t *d_pos,
+                                            uint32_t seq_len, uint32_t num_heads, uint32_t num_heads_kv,
+                                            uint32_t head_dim, uint32_t max_seq_len, float scale);
 /* Causal prefill attention: q [S][H][Dh] fp32 against rows [pos0, pos0+S) of the
  * fp16 cache (keys 0 .. pos0+s for query s), o [S][H][Dh] fp32.
  * Replaces launch_flash_attention_prefill (attention_kernels.hip:543-618). */
