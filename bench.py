@@ -281,7 +281,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
-    ap.add_argument("--prefill-chunk", type=int, default=32, help="tokens per prefill call (0 = the whole prompt at once)")
+    ap.add_argument("--prefill-chunk", type=int, default=0, help="tokens per prefill call (0 = the whole prompt at once)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     ranks = Ranks()
@@ -313,7 +313,7 @@ def main():
         model.set_comm(comm)
     model.load_synthetic(SEED)
     prompt = pkg.model.synth_tokens(SEED, args.prompt_len, cfg["vocab"])
-    chunk = args.prefill_chunk or args.prompt_len           # prefill (not timed); chunks <= 32 take the GEMV route
+    chunk = args.prefill_chunk or args.prompt_len           # prefill (not timed): one tensor-core pass by default
     for c0 in range(0, args.prompt_len, chunk):
         logits = model.forward(prompt[c0:c0 + chunk], c0)
     first = int(np.argmax(logits))

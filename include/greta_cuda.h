@@ -179,6 +179,10 @@ GRETA_API int greta_cuda_fused_ffn_front(greta_stream_t stream, int fmt, const f
  * workspace: device scratch of greta_cuda_gemm_workspace_bytes(M, K) bytes, used
  * for the fp16 copy of A when A is fp32 (may be NULL when a_is_f16). */
 GRETA_API size_t greta_cuda_gemm_workspace_bytes(uint32_t M, uint32_t K);
+/* Every wait inside the GEMM kernel is bounded; if one ever gives up the kernel drains, frees its tensor
+ * memory and records a non-zero code (100 * role + stage) that this call returns in *code (0 = none).
+ * Synchronises with the device. */
+GRETA_API int greta_cuda_gemm_status(int *code);
 GRETA_API int greta_cuda_gemm(greta_stream_t stream, int fmt, const void *A, int a_is_f16,
                               const void *qs, const void *d, void *C, int c_is_f16, uint32_t M,
                               uint32_t N, uint32_t K, void *workspace);

@@ -363,3 +363,51 @@ def test_embedding_and_argmax(g):
             logits[[n // 3, n // 3 + 57 if n // 3 + 57 < n else n - 1]] = 9.5     # an exact tie: first index wins
         g.check(g.cuda().greta_cuda_argmax(None, _dev(g, logits).ptr, n, res.ptr))
         assert int(res.download(np.int32)[0]) == O.argmax(logits)[0] == int(np.argmax(logits))
+
+
+# ----------------------------------------------------------------------------- prefill GEMM (tcgen05)
+def _gemm_status(g):
+    code = C.c_int(-1)
+    g.check(g.cuda().greta_cuda_gemm_status(C.byref(code)))
+    return code.value
+
+
+@pytest.mark.parametrize("name", ["q4_0", "q8_0"])
+@pytest.mark.parametrize("M,N,K,a_f16,c_f16", [(33, 128, 256, True, False), (128, 130, 512, False, False), (130, 200, 256, True, True),
+                                               (257, 1000, 1024, False, True), (512, 384, 4096, True, True)])
+def test_gemm_matches_oracle(g, name, M, N, K, a_f16, c_f16):
+    """C = half(A) half(dequant(W))^T: both operands rounded to fp16 as the reference's MFMA route does
+    (gemm_kernels.hip:845, 886-887), fp32 accumulation on the tensor cores, against the double-accumulating oracle."""
+    ofmt, gfmt = FMTS[name]
+    rng = np.random.default_rng(200 + M + N)
+    blk = make_blocks(rng, ofmt, N, K)
+    a = rng.normal(0, 1, (M, K)).astype(np.float32)
+    a_in = a.astype(np.float16).view(np.uint16) if a_f16 else a
+    w = g.Weight(blk, gfmt, N, K)
+    ws = _KEEP.append(g.DeviceBuffer(g.cuda().greta_cuda_gemm_workspace_bytes(M, K))) or _KEEP[-1]
+    c = g.DeviceBuffer(M * N * (2 if c_f16 else 4))
+    _KEEP.append(c)
+    c.fill(0xFF)
+    g.check(g.cuda().greta_cuda_gemm(None, gfmt, _dev(g, a_in).ptr, int(a_f16), w.qs.ptr, w.d.ptr, c.ptr, int(c_f16), M, N, K, ws.ptr))
+    g.check(g.cuda().greta_cuda_device_synchronize())
+    assert _gemm_status(g) == 0
+    if c_f16:
+        got = O.f16_bits_to_f32(c.download(np.uint16)).reshape(M, N)
+        want = O.f16_bits_to_f32(O.gemm(a_in, blk, ofmt, N, K, out_f16=True))
+        bar = 1.5e-3          # one fp16 ulp of the output
+    else:
+        got = c.download(np.float32).reshape(M, N)
+        want = O.gemm(a_in, blk, ofmt, N, K)
+        bar = 1e-4            # fp32 accumulation order on the tensor core
+    assert np.isfinite(got).all()
+    err = max_abs_rel(got, want)
+    assert err < TOL and err < bar, err
+
+
+def test_gemm_rejects_what_it_cannot_do(g):
+    lib = g.cuda()
+    buf = g.DeviceBuffer(1 << 16)
+    assert lib.greta_cuda_gemm(None, g.FMT_Q4_0, buf.ptr, 1, buf.ptr, buf.ptr, buf.ptr, 0, 64, 64, 96, None) == 4      # K % 256
+    assert lib.greta_cuda_gemm(None, g.FMT_F16, buf.ptr, 1, buf.ptr, buf.ptr, buf.ptr, 0, 64, 64, 256, None) == 4     # format
+    assert lib.greta_cuda_gemm(None, g.FMT_Q4_0, buf.ptr, 0, buf.ptr, buf.ptr, buf.ptr, 0, 64, 64, 256, None) == 4    # fp32 A without workspace
+    assert lib.greta_cuda_gemm(None, g.FMT_Q4_0, None, 1, None, None, None, 0, 0, 64, 256, None) == 0                  # empty

@@ -73,6 +73,26 @@ def test_generate_on_device_loop_matches_oracle(pkg):
     m2.close()
 
 
+def test_long_prompt_takes_the_tensor_core_route_and_matches_oracle(pkg):
+    """A prompt of more than 32 tokens runs the projections through the tcgen05 GEMM (operands rounded to
+    fp16, as the reference's M > 32 route does); logits and the following greedy ids equal the oracle's."""
+    cfg, seed = SMALL_MHA, 11
+    weights = pkg.model.synth_weights(cfg, seed)
+    prompt = pkg.model.synth_tokens(seed, 45, cfg["vocab"])
+    m = pkg.model.Model(cfg)
+    m.load_synthetic(seed)
+    ref = O.Model(cfg, weights)
+    lg = m.forward(prompt, 0)
+    lo, xo = ref.forward(prompt, 0)
+    assert max_abs_rel(m.hidden(len(prompt) - 1), xo) < 1e-4
+    assert max_abs_rel(lg, lo) < 1e-4
+    ids, _ = m.generate(prompt, 12)
+    want, gaps = ref.generate(prompt, 12)
+    assert min(gaps) > 1e-5
+    assert ids == want
+    m.close()
+
+
 def test_forward_rejects_bad_ranges(pkg):
     m = pkg.model.Model(SMALL)
     m.load_synthetic(1)
