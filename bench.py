@@ -273,6 +273,62 @@ def time_dominant_kernel(pkg, cfg, tp, reps=4):
     return us, alg_bytes
 
 
+# ----------------------------------------------------------------------------- small single-kernel cases (for ncu)
+def run_case(pkg, name):
+    """A few launches of one kernel on a small case whose data is larger than L2, for profiler captures
+    (`ncu -k regex:<kernel> ... python bench.py --case <name>`).  Prints nothing but 'ok'."""
+    import ctypes as C
+    g = pkg.ffi
+    g.require_device()
+    lib = g.cuda()
+    rng = np.random.default_rng(0)
+
+    def planes(N, K, copies):
+        nb = N * (K // 32)
+        qs = rng.integers(0, 256, nb * 16, dtype=np.uint8)
+        d = (np.abs(rng.normal(0, 0.02, nb)) / 8).astype(np.float16).view(np.uint16)
+        return [(g.DeviceBuffer.from_numpy(qs), g.DeviceBuffer.from_numpy(d)) for _ in range(copies)]
+
+    if name == "gemv_swiglu":        # 7B FFN front: 50.8 MB per launch, 6 distinct weight sets (305 MB > 126 MB L2)
+        D, F = 4096, 11008
+        w1, w3 = planes(F, D, 6), planes(F, D, 6)
+        x = g.DeviceBuffer.from_numpy(rng.normal(0, 1, D).astype(np.float32))
+        gam = g.DeviceBuffer.from_numpy(np.ones(D, np.float32))
+        y = g.DeviceBuffer(F * 4)
+        for i in range(12):
+            a, b = w1[i % 6], w3[i % 6]
+            g.check(lib.greta_cuda_fused_ffn_front(None, g.FMT_Q4_0, x.ptr, gam.ptr, 1e-5, a[0].ptr, a[1].ptr, b[0].ptr, b[1].ptr, y.ptr, D, F))
+    elif name == "gemv_plain":       # 11008 x 4096 Q4_0 GEMV, 12 distinct copies
+        N, K = 11008, 4096
+        w = planes(N, K, 12)
+        x = g.DeviceBuffer.from_numpy(rng.normal(0, 1, K).astype(np.float32))
+        y = g.DeviceBuffer(N * 4)
+        for i in range(12):
+            g.check(lib.greta_cuda_gemv(None, g.FMT_Q4_0, x.ptr, 0, w[i][0].ptr, w[i][1].ptr, y.ptr, 1, N, K))
+    elif name == "gemm_c2":          # BASELINE config 2: 512 x 4096 -> 11008, fp16 in / out
+        M, N, K = 512, 11008, 4096
+        w = planes(N, K, 6)
+        a = g.DeviceBuffer.from_numpy(rng.normal(0, 1, (M, K)).astype(np.float16).view(np.uint16))
+        c = g.DeviceBuffer(M * N * 2)
+        for i in range(6):
+            g.check(lib.greta_cuda_gemm(None, g.FMT_Q4_0, a.ptr, 1, w[i][0].ptr, w[i][1].ptr, c.ptr, 1, M, N, K, None))
+    elif name == "attn_decode":      # 32 heads x 128, 2049 keys, fp16 cache, 6 distinct caches (201 MB)
+        H, Dh, L, S = 32, 128, 2049, 2304
+        kv = rng.normal(0, 1, H * S * Dh).astype(np.float16).view(np.uint16)
+        caches = [(g.DeviceBuffer.from_numpy(kv), g.DeviceBuffer.from_numpy(kv)) for _ in range(6)]
+        q = g.DeviceBuffer.from_numpy(rng.normal(0, 1, H * Dh).astype(np.float32))
+        o = g.DeviceBuffer(H * Dh * 4)
+        nbytes = lib.greta_cuda_attn_decode_scratch_bytes(H, Dh)
+        scratch = g.DeviceBuffer(nbytes, zero=True)
+        for i in range(12):
+            k, v = caches[i % 6]
+            g.check(lib.greta_cuda_attn_decode(None, q.ptr, k.ptr, v.ptr, o.ptr, None, L, H, H, Dh, S, 0.0884, scratch.ptr, nbytes))
+    else:
+        raise SystemExit(f"unknown case {name}")
+    g.check(lib.greta_cuda_device_synchronize())
+    print("ok")
+
+
 # ----------------------------------------------------------------------------- main
 def main():
     ap = argparse.ArgumentParser()
@@ -283,12 +339,16 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
     ap.add_argument("--prefill-chunk", type=int, default=0, help="tokens per prefill call (0 = the whole prompt at once)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--case", default=None, help="run a small single-kernel case (gemv_swiglu, gemv_plain, gemm_c2, attn_decode) and exit")
     args = ap.parse_args()
     ranks = Ranks()
     if ranks.world != args.gpus and ranks.world > 1:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={ranks.world}")
 
     pkg = load_pkg()
+    if args.case:
+        run_case(pkg, args.case)
+        return
     from gretacore_v3_b200.model import LLAMA2_7B
     cfg = dict(LLAMA2_7B)
     if args.impl == "reference":
