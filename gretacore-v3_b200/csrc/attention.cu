@@ -78,6 +78,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnParams p) {
   __shared__ float sm_o[ATT_WARPS][Dh];
   __shared__ uint32_t sm_last;
 
+  pdl_launch_dependents();
+  pdl_wait();  // q, the position and the newest cache row come from the previous kernel
   const uint32_t split = blockIdx.x, head = blockIdx.y, qi = blockIdx.z;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane & 7, grp = lane >> 3;  // 8 lanes per key, 4 keys per warp step
@@ -234,9 +236,9 @@ template <typename KV>
 int launch_attn(cudaStream_t stream, AttnParams p, uint32_t nq, uint32_t Dh) {
   dim3 grid(p.splits, p.H, nq);
   if (Dh == 128)
-    attn_kernel<KV, 16><<<grid, ATT_THREADS, 0, stream>>>(p);
+    GRETA_CUDA_TRY(launch_pdl(attn_kernel<KV, 16>, grid, dim3(ATT_THREADS), 0, stream, p));
   else if (Dh == 64)
-    attn_kernel<KV, 8><<<grid, ATT_THREADS, 0, stream>>>(p);
+    GRETA_CUDA_TRY(launch_pdl(attn_kernel<KV, 8>, grid, dim3(ATT_THREADS), 0, stream, p));
   else {
     set_error("attention: head_dim=%u is not supported (64 or 128)", Dh);
     return GRETA_ERR_NOT_IMPLEMENTED;

@@ -10,13 +10,13 @@ namespace {
 // One thread per GGUF block: splits {fp16 d; payload} into the two planes.
 template <int FMT>
 __global__ void repack_kernel(const uint8_t *__restrict__ blocks, uint8_t *__restrict__ qs,
-                              uint16_t *__restrict__ d, size_t n_blocks) {
+                              uint16_t *__restrict__ d, size_t n_blocks, uint32_t nb_row) {
   constexpr int PB = payload_bytes(FMT), BB = PB + 2;
   size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= n_blocks) return;
   const uint8_t *src = blocks + b * BB;   // 2-byte aligned only (18 / 34 byte stride)
   const uint16_t *s16 = reinterpret_cast<const uint16_t *>(src);
-  d[b] = s16[0];
+  d[(b / nb_row) * d_row_stride(nb_row) + b % nb_row] = s16[0];
   uint16_t *dst = reinterpret_cast<uint16_t *>(qs + b * PB);
 #pragma unroll
   for (int i = 0; i < PB / 2; ++i) dst[i] = s16[1 + i];
@@ -25,19 +25,20 @@ __global__ void repack_kernel(const uint8_t *__restrict__ blocks, uint8_t *__res
 // One thread per block of 32 weights; bit-exact (float)q * fp32(d).
 template <int FMT>
 __global__ void dequant_kernel(const uint8_t *__restrict__ qs, const void *__restrict__ d,
-                               float *__restrict__ out, size_t n_blocks) {
+                               float *__restrict__ out, size_t n_blocks, uint32_t nb_row) {
   size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= n_blocks) return;
+  const size_t sb = (b / nb_row) * d_row_stride(nb_row) + b % nb_row;  // index in the padded fp16 d plane
   float *o = out + b * 32;
   if (FMT == GRETA_FMT_Q4_0) {
-    float s = __half2float(reinterpret_cast<const __half *>(d)[b]);
+    float s = __half2float(reinterpret_cast<const __half *>(d)[sb]);
     const uint8_t *p = qs + b * 16;
     for (int j = 0; j < 16; ++j) {
       o[j] = __fmul_rn((float)((int)(p[j] & 0xF) - 8), s);
       o[j + 16] = __fmul_rn((float)((int)(p[j] >> 4) - 8), s);
     }
   } else if (FMT == GRETA_FMT_Q8_0) {
-    float s = __half2float(reinterpret_cast<const __half *>(d)[b]);
+    float s = __half2float(reinterpret_cast<const __half *>(d)[sb]);
     const int8_t *p = reinterpret_cast<const int8_t *>(qs) + b * 32;
     for (int j = 0; j < 32; ++j) o[j] = __fmul_rn((float)p[j], s);
   } else if (FMT == GRETA_FMT_REF_INT4) {
@@ -128,6 +129,8 @@ __global__ void silu_mul_kernel(const float *g, const float *u, float *y, size_t
 template <bool F16>
 __global__ void embedding_kernel(const int32_t *__restrict__ tokens, const void *__restrict__ table,
                                  float *__restrict__ out, uint32_t S, uint32_t dim, uint32_t vocab) {
+  pdl_launch_dependents();
+  pdl_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (size_t)S * dim) return;
   uint32_t s = i / dim, dd = i % dim;
@@ -146,6 +149,8 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ 
                                                       uint32_t *d_count, uint32_t out_capacity) {
   __shared__ float sv[32];
   __shared__ uint32_t si[32];
+  pdl_launch_dependents();
+  pdl_wait();
   float best = -INFINITY;
   uint32_t bi = 0xffffffffu;
   for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
@@ -206,7 +211,8 @@ size_t greta_cuda_qs_bytes(int fmt, uint32_t N, uint32_t K) {
 }
 size_t greta_cuda_d_bytes(int fmt, uint32_t N, uint32_t K) {
   if (fmt == GRETA_FMT_F16) return 0;
-  return (size_t)N * (K / 32) * ((fmt == GRETA_FMT_REF_INT4 || fmt == GRETA_FMT_REF_INT8) ? 4 : 2);
+  if (fmt == GRETA_FMT_REF_INT4 || fmt == GRETA_FMT_REF_INT8) return (size_t)N * (K / 32) * 4;
+  return (size_t)N * d_row_stride(K / 32) * 2;
 }
 
 int greta_cuda_repack_gguf(greta_stream_t stream, int fmt, const void *blocks, void *qs, void *d, uint32_t N,
@@ -217,10 +223,11 @@ int greta_cuda_repack_gguf(greta_stream_t stream, int fmt, const void *blocks, v
   if (nb == 0) return GRETA_OK;
   GRETA_REQUIRE(blocks && qs && d, "repack_gguf: null pointer");
   GRETA_REQUIRE(((uintptr_t)blocks & 1) == 0 && aligned16(qs) && ((uintptr_t)d & 1) == 0, "repack_gguf: misaligned pointer");
+  if (d_row_stride(K / 32) != K / 32) GRETA_CUDA_TRY(cudaMemsetAsync(d, 0, greta_cuda_d_bytes(fmt, N, K), S(stream)));  // row padding
   if (fmt == GRETA_FMT_Q4_0)
-    repack_kernel<GRETA_FMT_Q4_0><<<blocks_for(nb, 256), 256, 0, S(stream)>>>((const uint8_t *)blocks, (uint8_t *)qs, (uint16_t *)d, nb);
+    repack_kernel<GRETA_FMT_Q4_0><<<blocks_for(nb, 256), 256, 0, S(stream)>>>((const uint8_t *)blocks, (uint8_t *)qs, (uint16_t *)d, nb, K / 32);
   else
-    repack_kernel<GRETA_FMT_Q8_0><<<blocks_for(nb, 256), 256, 0, S(stream)>>>((const uint8_t *)blocks, (uint8_t *)qs, (uint16_t *)d, nb);
+    repack_kernel<GRETA_FMT_Q8_0><<<blocks_for(nb, 256), 256, 0, S(stream)>>>((const uint8_t *)blocks, (uint8_t *)qs, (uint16_t *)d, nb, K / 32);
   return launched("repack_kernel");
 }
 
@@ -231,10 +238,10 @@ int greta_cuda_dequant(greta_stream_t stream, int fmt, const void *qs, const voi
   GRETA_REQUIRE(qs && d && out, "dequant: null pointer");
   unsigned g = blocks_for(nb, 128);
   switch (fmt) {
-    case GRETA_FMT_Q4_0: dequant_kernel<GRETA_FMT_Q4_0><<<g, 128, 0, S(stream)>>>((const uint8_t *)qs, d, out, nb); break;
-    case GRETA_FMT_Q8_0: dequant_kernel<GRETA_FMT_Q8_0><<<g, 128, 0, S(stream)>>>((const uint8_t *)qs, d, out, nb); break;
-    case GRETA_FMT_REF_INT4: dequant_kernel<GRETA_FMT_REF_INT4><<<g, 128, 0, S(stream)>>>((const uint8_t *)qs, d, out, nb); break;
-    case GRETA_FMT_REF_INT8: dequant_kernel<GRETA_FMT_REF_INT8><<<g, 128, 0, S(stream)>>>((const uint8_t *)qs, d, out, nb); break;
+    case GRETA_FMT_Q4_0: dequant_kernel<GRETA_FMT_Q4_0><<<g, 128, 0, S(stream)>>>((const uint8_t *)qs, d, out, nb, K / 32); break;
+    case GRETA_FMT_Q8_0: dequant_kernel<GRETA_FMT_Q8_0><<<g, 128, 0, S(stream)>>>((const uint8_t *)qs, d, out, nb, K / 32); break;
+    case GRETA_FMT_REF_INT4: dequant_kernel<GRETA_FMT_REF_INT4><<<g, 128, 0, S(stream)>>>((const uint8_t *)qs, d, out, nb, K / 32); break;
+    case GRETA_FMT_REF_INT8: dequant_kernel<GRETA_FMT_REF_INT8><<<g, 128, 0, S(stream)>>>((const uint8_t *)qs, d, out, nb, K / 32); break;
     default: GRETA_REQUIRE(false, "dequant: unsupported format %d", fmt);
   }
   return launched("dequant_kernel");
@@ -278,22 +285,23 @@ int greta_cuda_embedding(greta_stream_t stream, const int32_t *tokens, const voi
   if (n == 0) return GRETA_OK;
   GRETA_REQUIRE(tokens && table && out, "embedding: null pointer");
   if (table_is_f16)
-    embedding_kernel<true><<<blocks_for(n, 256), 256, 0, S(stream)>>>(tokens, table, out, Sq, dim, vocab);
+    GRETA_CUDA_TRY(launch_pdl(embedding_kernel<true>, dim3(blocks_for(n, 256)), dim3(256), 0, S(stream), tokens, table, out, Sq, dim, vocab));
   else
-    embedding_kernel<false><<<blocks_for(n, 256), 256, 0, S(stream)>>>(tokens, table, out, Sq, dim, vocab);
+    GRETA_CUDA_TRY(launch_pdl(embedding_kernel<false>, dim3(blocks_for(n, 256)), dim3(256), 0, S(stream), tokens, table, out, Sq, dim, vocab));
   return launched("embedding_kernel");
 }
 int greta_cuda_argmax(greta_stream_t stream, const float *logits, uint32_t n, int32_t *d_out) {
   GRETA_REQUIRE(n > 0, "argmax: empty input");
   GRETA_REQUIRE(logits && d_out, "argmax: null pointer");
-  argmax_kernel<<<1, 1024, 0, S(stream)>>>(logits, n, d_out, nullptr, nullptr, nullptr, 0);
+  GRETA_CUDA_TRY(launch_pdl(argmax_kernel, dim3(1), dim3(1024), 0, S(stream), logits, n, d_out, (uint32_t *)nullptr, (int32_t *)nullptr,
+                            (uint32_t *)nullptr, 0u));
   return launched("argmax_kernel");
 }
 int greta_cuda_argmax_advance(greta_stream_t stream, const float *logits, uint32_t n, int32_t *d_next, uint32_t *d_pos,
                               int32_t *d_out_tokens, uint32_t *d_count, uint32_t out_capacity) {
   GRETA_REQUIRE(n > 0, "argmax_advance: empty input");
   GRETA_REQUIRE(logits && d_next, "argmax_advance: null pointer");
-  argmax_kernel<<<1, 1024, 0, S(stream)>>>(logits, n, d_next, d_pos, d_out_tokens, d_count, out_capacity);
+  GRETA_CUDA_TRY(launch_pdl(argmax_kernel, dim3(1), dim3(1024), 0, S(stream), logits, n, d_next, d_pos, d_out_tokens, d_count, out_capacity));
   return launched("argmax_kernel");
 }
 int greta_cuda_silu(greta_stream_t stream, const float *x, float *y, size_t n) {

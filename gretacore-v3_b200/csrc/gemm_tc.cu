@@ -173,13 +173,18 @@ struct Raw {  // one thread's weights for one stage: 64 weights of its row
   uint32_t d;  // two fp16 scales
 };
 
+// Stage kt covers blocks 2kt and 2kt+1 of the row; when K is an odd number of blocks the last stage
+// has only the first one, and the missing half is made zero (the activations there are zero-filled
+// by TMA, but 0 * garbage must not produce a NaN).
 template <int FMT>
-__device__ __forceinline__ void load_raw(Raw<FMT> &r, const uint8_t *qs_row, const __half *d_row, uint32_t kt) {
+__device__ __forceinline__ void load_raw(Raw<FMT> &r, const uint8_t *qs_row, const __half *d_row, uint32_t kt, uint32_t nb) {
   constexpr int QV = Raw<FMT>::QV;
   const uint8_t *p = qs_row + (size_t)kt * QV * 16;
+  const bool second = 2 * kt + 1 < nb;
 #pragma unroll
-  for (int v = 0; v < QV; ++v) r.q[v] = ld_stream(p + v * 16);
-  r.d = __ldg(reinterpret_cast<const uint32_t *>(d_row + 2 * kt));
+  for (int v = 0; v < QV; ++v) r.q[v] = (v < QV / 2 || second) ? ld_stream(p + v * 16) : make_uint4(0, 0, 0, 0);
+  r.d = __ldg(reinterpret_cast<const uint32_t *>(d_row + 2 * kt));  // rows of the d plane are padded: always in bounds
+  if (!second) r.d &= 0xFFFFu;                                      // scale 0 for the absent block
 }
 
 // Dequantises the thread's 64 weights and writes its 128-byte row of the swizzled B tile.
@@ -231,7 +236,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t *__rest
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t n0 = blockIdx.x * TILE_N, m0 = blockIdx.y * TN;
-  const uint32_t KT = K / BK, nb = K / 32;
+  const uint32_t KT = (K + BK - 1) / BK, nb = K / 32;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -294,14 +299,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t *__rest
     const int t = threadIdx.x - 64;  // weight row inside the tile, 0..127
     const uint32_t n = min(n0 + (uint32_t)t, N - 1);
     const uint8_t *qs_row = qs + (size_t)n * nb * (FMT == GRETA_FMT_Q4_0 ? 16 : 32);
-    const __half *d_row = dsc + (size_t)n * nb;
+    const __half *d_row = dsc + (size_t)n * d_row_stride(nb);
     Raw<FMT> r0, r1, r2;
-    load_raw<FMT>(r0, qs_row, d_row, 0);
-    if (KT > 1) load_raw<FMT>(r1, qs_row, d_row, 1);
+    load_raw<FMT>(r0, qs_row, d_row, 0, nb);
+    if (KT > 1) load_raw<FMT>(r1, qs_row, d_row, 1, nb);
     bool ok = true;
     for (uint32_t kt = 0; kt < KT; ++kt) {
       const uint32_t s = kt % STAGES, ph = (kt / STAGES) & 1;
-      if (kt + 2 < KT) load_raw<FMT>(r2, qs_row, d_row, kt + 2);
+      if (kt + 2 < KT) load_raw<FMT>(r2, qs_row, d_row, kt + 2, nb);
       ok = mbar_wait(&empty[s], ph ^ 1, abort_flag, 400 + s);
       if (!ok) break;
       dequant_store<FMT>(r0, b_tiles + s * B_STAGE_BYTES + t * 128, t & 7);
@@ -399,7 +404,7 @@ int greta_cuda_gemm(greta_stream_t stream, int fmt, const void *A, int a_is_f16,
                     uint32_t M, uint32_t N, uint32_t K, void *workspace) {
   if (M == 0 || N == 0 || K == 0) return GRETA_OK;
   GRETA_REQUIRE(fmt == GRETA_FMT_Q4_0 || fmt == GRETA_FMT_Q8_0, "gemm: format %d is not supported (Q4_0 or Q8_0)", fmt);
-  GRETA_REQUIRE(K % 256 == 0, "gemm: K=%u is not a multiple of 256", K);
+  GRETA_REQUIRE(K % 32 == 0, "gemm: K=%u is not a multiple of the block size 32", K);
   GRETA_REQUIRE(A && qs && d && Cout, "gemm: null pointer");
   GRETA_REQUIRE(aligned16(A) && aligned16(qs) && ((uintptr_t)d & 3) == 0 && aligned16(Cout), "gemm: misaligned pointer");
   cudaStream_t s = (cudaStream_t)stream;

@@ -28,8 +28,8 @@
 //     that spans warps meet in shared memory in a fixed order (deterministic).
 //
 // fp16 weights (the LM head) use the same pipeline with fp32 activations and
-// packed fp32 FMAs.  Shapes whose K is not a multiple of 256 take a simpler
-// kernel (direct loads, float math).
+// packed fp32 FMAs.  A simpler kernel (direct loads, float math) remains for K so
+// large that the staged activations leave no room for the ring.
 #include <math.h>
 
 #include <algorithm>
@@ -352,7 +352,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_simple_kernel(const GemvParam
       }
       qrow[r] = p.w[mat].qs + (size_t)row * nb * PB;
       drow[r] = p.w[mat].d;
-      dbase[r] = (size_t)row * nb;
+      dbase[r] = (size_t)row * (Fmt<FMT>::SCALE_BYTES == 2 ? d_row_stride(nb) : nb);
     }
     b = kp * bps + lane;
     bend = min(nb, (kp + 1) * bps);
@@ -437,7 +437,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_simple_kernel(const GemvParam
   }
 }
 
-// ------------------------------------------------------------------ pipelined kernel (K % 256 == 0)
+// ------------------------------------------------------------------ pipelined kernel
 __device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc) {
   uint32_t s = (uint32_t)__cvta_generic_to_shared(smem_dst);
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gsrc) : "memory");
@@ -619,10 +619,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pipe_kernel(const GemvParams 
   const uint32_t T = (g1 - g0) * C;
   const uint32_t c0 = (uint32_t)((uint64_t)warp * T / WARPS), c1 = (uint32_t)((uint64_t)(warp + 1) * T / WARPS);
 
-  // ---- producer state: next cell to request ----
-  uint32_t pc = c0, pg = g0 + (c0 / C), pk = c0 % C;
-  const uint8_t *qrow[R];
-  const uint8_t *drow[R];
+  // ---- producer state: next cell to request.  Source pointers run along the rows (one add per cell). ----
+  uint32_t pc = c0, pg = g0 + (c0 / C), pk = c0 % C, pstage = 0;
+  const uint8_t *qsrc[R];       // this lane's payload of the next cell, per row
+  const uint8_t *dsrc4[R];      // fp32-scale formats: this lane's scale, per row
+  const uint8_t *dsrc = nullptr;  // fp16-scale formats: lanes < 4R copy 8 scales each: (row lane/4, segment lane%4)
+  const uint32_t dst_q = (uint32_t)lane * PB;
+  const uint32_t dst_d = R * 32 * PB + (F::SCALE_BYTES == 2 ? (uint32_t)(lane >> 2) * SCALE_ROW + (uint32_t)(lane & 3) * 16 : (uint32_t)lane * 4);
   auto producer_rows = [&]() {
 #pragma unroll
     for (int r = 0; r < R; ++r) {
@@ -632,47 +635,51 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pipe_kernel(const GemvParams 
         mat = 0;
         row = 0;
       }
-      qrow[r] = p.w[mat].qs + (size_t)row * nb * PB;
-      drow[r] = reinterpret_cast<const uint8_t *>(p.w[mat].d) + (size_t)row * nb * F::SCALE_BYTES;
+      qsrc[r] = p.w[mat].qs + ((size_t)row * nb + pk * 32 + lane) * PB;
+      const uint8_t *dbase = reinterpret_cast<const uint8_t *>(p.w[mat].d);
+      if (F::SCALE_BYTES == 2) {
+        if ((lane >> 2) == r) dsrc = dbase + ((size_t)row * d_row_stride(nb) + pk * 32 + (lane & 3) * 8) * 2;
+      } else if (F::SCALE_BYTES == 4) {
+        dsrc4[r] = dbase + ((size_t)row * nb + pk * 32 + lane) * 4;
+      }
     }
   };
   if (pc < c1) producer_rows();
-  auto request = [&](uint32_t stage) {  // requests cell pc into `stage`, advances the producer
+  auto request = [&]() {  // requests cell pc into stage pstage, advances the producer
     if (pc < c1) {
-      uint8_t *st = ring + (size_t)stage * STAGE_BYTES;
-      const uint32_t blk = pk * 32 + lane;
-      if (blk < nb) {
+      uint8_t *st = ring + pstage * STAGE_BYTES;
+      if (pk * 32 + lane < nb) {
 #pragma unroll
         for (int r = 0; r < R; ++r) {
 #pragma unroll
-          for (int v = 0; v < QV; ++v)
-            cp_async16(st + ((size_t)r * 32 + lane) * PB + v * 16, qrow[r] + (size_t)blk * PB + v * 16);
-          if (F::SCALE_BYTES == 4) cp_async4(st + R * 32 * PB + r * SCALE_ROW + lane * 4, drow[r] + (size_t)blk * 4);
+          for (int v = 0; v < QV; ++v) cp_async16(st + r * 32 * PB + dst_q + v * 16, qsrc[r] + v * 16);
+          if (F::SCALE_BYTES == 4) cp_async4(st + dst_d + r * SCALE_ROW, dsrc4[r]);
         }
       }
-      if (F::SCALE_BYTES == 2 && lane < 4 * R) {  // lane -> (row, segment of 8 scales)
-        const int r = lane >> 2, seg = lane & 3;
-        const uint32_t b8 = pk * 32 + seg * 8;
-        if (b8 < nb) {
-          const uint8_t *src = drow[0];
-#pragma unroll
-          for (int rr = 1; rr < R; ++rr) src = (r == rr) ? drow[rr] : src;
-          cp_async16(st + R * 32 * PB + r * SCALE_ROW + seg * 16, src + (size_t)b8 * 2);
-        }
-      }
+      if (F::SCALE_BYTES == 2 && lane < 4 * R && pk * 32 + (lane & 3) * 8 < nb) cp_async16(st + dst_d, dsrc);
       ++pc;
       if (++pk == C) {
         pk = 0;
         ++pg;
         if (pc < c1) producer_rows();
+      } else {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          qsrc[r] += 32 * PB;
+          if (F::SCALE_BYTES == 4) dsrc4[r] += 128;
+        }
+        if (F::SCALE_BYTES == 2) dsrc += 64;
       }
     }
     cp_async_commit();
+    pstage = (pstage + 1 == D) ? 0 : pstage + 1;
   };
 
   // Request the first cells before touching the activations: weights do not
   // depend on the previous kernel's output.
-  for (uint32_t s = 0; s + 1 < D; ++s) request(s);
+  for (uint32_t s = 0; s + 1 < D; ++s) request();
+  pdl_launch_dependents();  // the next kernel may begin its own weight prefetch as SMs free up
+  pdl_wait();               // everything below reads what the previous kernel wrote
 
   // ---- stage activations ----
   if (F::INTEGER) {
@@ -696,19 +703,21 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pipe_kernel(const GemvParams 
 #pragma unroll
   for (int r = 0; r < R; ++r) acc[r] = 0.f;
   const uint32_t first_grp = g0 + c0 / C;
-  uint32_t cg = first_grp, ck = c0 % C;
+  uint32_t cg = first_grp, ck = c0 % C, cstage = 0;
+  constexpr uint32_t X_BLOCK_BYTES = F::INTEGER ? XQ_WORDS * 4 : XPAD * 4;
+  const uint8_t *xrun = smem + (size_t)(ck * 32 + lane) * X_BLOCK_BYTES;  // this lane's activation block, runs along K
   for (uint32_t c = c0; c < c1; ++c) {
-    const uint32_t stage = (c - c0) % D;
     cp_async_wait((int)D - 2);
     __syncwarp();
-    const uint8_t *st = ring + (size_t)stage * STAGE_BYTES;
-    const uint32_t blk = ck * 32 + lane;
+    const uint8_t *st = ring + cstage * STAGE_BYTES;
+    cstage = (cstage + 1 == D) ? 0 : cstage + 1;
+    const bool live = ck * 32 + lane < nb;
     uint4 q[R][QV];
     float dsc[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
 #pragma unroll
-      for (int v = 0; v < QV; ++v) q[r][v] = *reinterpret_cast<const uint4 *>(st + ((size_t)r * 32 + lane) * PB + v * 16);
+      for (int v = 0; v < QV; ++v) q[r][v] = *reinterpret_cast<const uint4 *>(st + r * 32 * PB + dst_q + v * 16);
       if (F::SCALE_BYTES == 2)
         dsc[r] = __half2float(*reinterpret_cast<const __half *>(st + R * 32 * PB + r * SCALE_ROW + lane * 2));
       else if (F::SCALE_BYTES == 4)
@@ -716,12 +725,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pipe_kernel(const GemvParams 
       else
         dsc[r] = 1.0f;
     }
-    __syncwarp();                      // every lane has read its stage (scales are shared between lanes)
-    request((c - c0 + D - 1) % D);     // refill the stage consumed in the previous iteration
-    if (blk < nb) {
+    __syncwarp();  // every lane has read its stage (scales are shared between lanes)
+    request();     // refill the stage consumed in the previous iteration
+    if (live) {
       if (F::INTEGER) {
         uint4 xp[7];
-        const uint4 *xb = reinterpret_cast<const uint4 *>(smem) + (size_t)blk * 7;
+        const uint4 *xb = reinterpret_cast<const uint4 *>(xrun);
 #pragma unroll
         for (int i = 0; i < 7; ++i) xp[i] = xb[i];
         const float xsc = __uint_as_float(xp[6].w);
@@ -729,14 +738,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pipe_kernel(const GemvParams 
         for (int r = 0; r < R; ++r) acc[r] = fmaf(dsc[r] * xsc, block_dot_i<FMT>(q[r], xp), acc[r]);
       } else {
         float4 xv[8];
-        const float4 *xb = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(smem) + (size_t)blk * XPAD);
+        const float4 *xb = reinterpret_cast<const float4 *>(xrun);
 #pragma unroll
         for (int i = 0; i < 8; ++i) xv[i] = xb[i];
 #pragma unroll
         for (int r = 0; r < R; ++r) acc[r] += block_dot_f<FMT>(q[r], xv);
       }
     }
-    if (++ck == C || c + 1 == c1) {    // group finished for this warp: reduce and publish
+    xrun += 32 * X_BLOCK_BYTES;
+    if (++ck == C || c + 1 == c1) {  // group finished for this warp: reduce and publish
 #pragma unroll
       for (int r = 0; r < R; ++r) acc[r] = warp_sum(acc[r]);
       if (lane == 0) {
@@ -749,6 +759,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pipe_kernel(const GemvParams 
       if (ck == C) {
         ck = 0;
         ++cg;
+        xrun = smem + (size_t)lane * X_BLOCK_BYTES;
       }
     }
   }
@@ -832,7 +843,7 @@ int launch_pipe(cudaStream_t stream, GemvParams p) {
   static bool attr_set[64] = {};
   if (int rc = ensure_smem_attr(gemv_pipe_kernel<FMT, EPI, R>, attr_set)) return rc;
   dim3 grid(ctas, p.M ? p.M : 1);
-  gemv_pipe_kernel<FMT, EPI, R><<<grid, THREADS, smem, stream>>>(p);
+  GRETA_CUDA_TRY(launch_pdl(gemv_pipe_kernel<FMT, EPI, R>, grid, dim3(THREADS), smem, stream, p));
   return launched("gemv_pipe_kernel");
 }
 
@@ -847,9 +858,7 @@ uint32_t count_groups(const GemvParams &p) {
 template <int FMT, int EPI, int R>
 int launch_any(cudaStream_t stream, GemvParams p) {
   p.groups = count_groups<EPI, R>(p);
-  const bool pipe_ok = Fmt<FMT>::SCALE_BYTES == 2 ? (p.K % 256 == 0) : (p.K % 32 == 0);
-  if (pipe_ok) return launch_pipe<FMT, EPI, R>(stream, p);
-  return launch_simple<FMT, EPI, R>(stream, p);
+  return launch_pipe<FMT, EPI, R>(stream, p);  // falls back to the simple kernel when K does not fit in shared memory
 }
 
 // Few rows: groups of 2 give twice as many cells to balance over the warps.

@@ -39,6 +39,31 @@ inline int launched(const char *kernel, unsigned n = 1) {
   return GRETA_OK;
 }
 
+// Programmatic dependent launch: a kernel launched with the attribute may start while its predecessor
+// in the stream is still draining; it must execute pdl_wait() before it touches anything the
+// predecessor produces (and before it overwrites anything the predecessor reads).  Weight prefetch
+// sits in front of that wait.  pdl_enabled() is read once from GRETA_PDL (default on) and can be
+// switched with greta_cuda_set_pdl().
+bool pdl_enabled();
+void set_pdl(bool on);
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // Payload bytes per block of 32 weights in the qs plane; 0 for unknown formats.
@@ -46,6 +71,10 @@ __host__ __device__ constexpr int payload_bytes(int fmt) {
   return fmt == GRETA_FMT_Q4_0 ? 16 : fmt == GRETA_FMT_Q8_0 ? 32 : fmt == GRETA_FMT_F16 ? 64
        : fmt == GRETA_FMT_REF_INT4 ? 16 : fmt == GRETA_FMT_REF_INT8 ? 32 : 0;
 }
+
+// Scales per row in the fp16 d plane of a GGUF format: the K/32 block scales padded to a multiple
+// of 8, so every row of the plane starts on a 16-byte boundary whatever K is.
+__host__ __device__ constexpr uint32_t d_row_stride(uint32_t blocks_per_row) { return (blocks_per_row + 7u) & ~7u; }
 
 // 128-bit streaming load of weights that are read once: bypass L1 allocation.
 __device__ __forceinline__ uint4 ld_stream(const void *p) {

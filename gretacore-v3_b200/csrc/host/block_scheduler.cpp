@@ -32,15 +32,14 @@ namespace {
 inline size_t block_bytes(GretaDataType t) { return t == GretaDataType::Q4_0 ? 18 : 34; }
 inline int fmt_of(GretaDataType t) { return t == GretaDataType::Q4_0 ? GRETA_FMT_Q4_0 : t == GretaDataType::Q8_0 ? GRETA_FMT_Q8_0 : GRETA_FMT_F16; }
 
-struct Shape {
-  uint32_t rows, cols;          // local shard [rows x cols]
-  uint32_t grows, gcols;        // global shape
-  uint32_t row0, col0;          // offset of the shard in the global matrix
-};
+using Shape = TensorShard;
 
 // Local shard of a projection under Megatron-style tensor parallelism: Q/K/V/gate/up are split by
 // rows (output features), O and down by columns (input features, whole quant blocks).
-Shape shard_of(const ModelConfig &c, LayerTensor t) {
+Shape shard_of(const ModelConfig &c, LayerTensor t) { return tensor_shard(c, t); }
+}  // namespace
+
+TensorShard tensor_shard(const ModelConfig &c, LayerTensor t) {
   const uint32_t tp = c.tp_size, r = c.tp_rank;
   const uint32_t q = c.num_heads * c.head_dim, kv = c.num_heads_kv * c.head_dim;
   switch (t) {
@@ -55,6 +54,7 @@ Shape shard_of(const ModelConfig &c, LayerTensor t) {
   }
 }
 
+namespace {
 struct PlanePair {
   Buffer *qs, *d;
 };

@@ -53,6 +53,17 @@ int greta_host_synth_tokens(uint64_t seed, uint64_t stream, uint32_t vocab, int3
 }
 uint64_t greta_host_tensor_stream(uint32_t layer, int which) { return synth::tensor_stream(layer, which); }
 
+int greta_host_tensor_shard(const greta_model_config *c, int which, uint32_t *out6) {
+  if (!c || !out6 || which < 0 || which > (int)LayerTensor::W3_UP || c->tp_size == 0 || c->tp_rank >= c->tp_size)
+    return done(false, "tensor_shard: bad argument");
+  ModelConfig k;
+  k.dim = c->dim; k.num_heads = c->num_heads; k.num_heads_kv = c->num_heads_kv; k.hidden_dim = c->hidden_dim; k.head_dim = c->head_dim;
+  k.tp_rank = c->tp_rank; k.tp_size = c->tp_size;
+  TensorShard s = tensor_shard(k, (LayerTensor)which);
+  out6[0] = s.rows; out6[1] = s.cols; out6[2] = s.grows; out6[3] = s.gcols; out6[4] = s.row0; out6[5] = s.col0;
+  return 0;
+}
+
 int greta_model_create(const greta_model_config *c, greta_model_t *out) {
   if (!c || !out) return done(false, "model_create: null argument");
   auto m = std::make_unique<Model>();

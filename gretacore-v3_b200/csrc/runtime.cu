@@ -5,6 +5,7 @@
 #include <unordered_map>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "greta_common.cuh"
@@ -39,6 +40,16 @@ static std::mutex g_graph_mu;
 static std::unordered_map<void *, uint64_t> g_graph_nodes;
 static thread_local uint64_t g_capture_mark = 0;
 
+static int g_pdl = -1;
+bool pdl_enabled() {
+  if (g_pdl < 0) {
+    const char *e = getenv("GRETA_PDL");
+    g_pdl = (e && e[0] == '0') ? 0 : 1;
+  }
+  return g_pdl != 0;
+}
+void set_pdl(bool on) { g_pdl = on ? 1 : 0; }
+
 int sm_count() {
   static int cached[64];
   int dev = 0;
@@ -60,6 +71,10 @@ extern "C" {
 
 const char *greta_cuda_last_error(void) { return g_err; }
 uint64_t greta_cuda_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+int greta_cuda_set_pdl(int on) {
+  set_pdl(on != 0);
+  return GRETA_OK;
+}
 
 int greta_cuda_device_count(int *count) {
   GRETA_REQUIRE(count, "device_count: null out pointer");

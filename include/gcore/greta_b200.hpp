@@ -355,6 +355,15 @@ struct ModelConfig {
 enum class LayerTensor : int { WQ = 0, WK, WV, WO, W1_GATE, W2_DOWN, W3_UP, ATTN_NORM, FFN_NORM };
 enum class GlobalTensor : int { TOK_EMBD = 0, OUT_NORM, OUT_WEIGHT };
 
+// Shard of a projection held by rank tp_rank of tp_size (Megatron style): Q/K/V/gate/up are split by
+// rows (output features), O and down by columns (input features, whole quant blocks).
+struct TensorShard {
+  uint32_t rows, cols;    // local shard [rows x cols]
+  uint32_t grows, gcols;  // global shape
+  uint32_t row0, col0;    // offset of the shard in the global matrix
+};
+TensorShard tensor_shard(const ModelConfig &config, LayerTensor which);
+
 struct BlockBuffers {
   gcore::rt::cuda::Buffer wq, wk, wv, wo, w1, w2, w3;            // qs planes (w1 gate, w2 down, w3 up)
   gcore::rt::cuda::Buffer s_wq, s_wk, s_wv, s_wo, s_w1, s_w2, s_w3;  // d planes

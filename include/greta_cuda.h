@@ -18,12 +18,14 @@
  *             of a payload = element j in the low nibble, element j+16 in the
  *             high nibble, q in 0..15, value (q-8)*d) and 32 bytes for Q8_0
  *             (int8 q, value q*d) - i.e. the GGUF block with its scale removed;
- *   d  plane: N * (K/32) fp16 scales, row-major.
- * Bytes per weight are those of GGUF (18/32 and 34/32); the split makes every
- * payload 16-byte aligned for 128-bit loads and TMA.  The pair (qs, d) plays
+ *   d  plane: N rows of fp16 scales, K/32 per row, each row padded to a multiple of 8
+ *             scales (16 bytes) - no padding when K is a multiple of 256.
+ * Bytes per weight are those of GGUF (18/32 and 34/32; the row padding adds at most
+ * 14 bytes per row); the split makes every payload and every scale row 16-byte
+ * aligned for 128-bit loads and TMA.  The pair (qs, d) plays
  * the role of the reference's (weights, GretaQuantInfo::scales) pair with
  * group_size 32 (greta_runtime.hpp:35-41).  K must be a multiple of 32 and both
- * planes 16-byte aligned.
+ * planes 16-byte aligned.  greta_cuda_qs_bytes / greta_cuda_d_bytes give the sizes.
  */
 #ifndef GRETA_CUDA_H
 #define GRETA_CUDA_H
@@ -98,6 +100,10 @@ GRETA_API int greta_cuda_graph_instantiate(void *graph, void **exec);
 GRETA_API int greta_cuda_graph_launch(void *exec, greta_stream_t stream);
 GRETA_API int greta_cuda_graph_destroy(void *graph);
 GRETA_API int greta_cuda_graph_exec_destroy(void *exec);
+/* Programmatic dependent launch between consecutive kernels of this library on one stream (the next
+ * kernel's weight prefetch overlaps the previous kernel's tail).  On by default; GRETA_PDL=0 in the
+ * environment or greta_cuda_set_pdl(0) turns it off.  Results do not depend on it. */
+GRETA_API int greta_cuda_set_pdl(int on);
 /* Number of kernel launches this library has issued on the calling process (all threads). */
 GRETA_API uint64_t greta_cuda_launch_count(void);
 

@@ -41,6 +41,10 @@ GRETA_API int greta_host_synth_normal_f32(uint64_t seed, uint64_t stream, float 
 GRETA_API int greta_host_synth_tokens(uint64_t seed, uint64_t stream, uint32_t vocab, int32_t *out, size_t n);
 GRETA_API uint64_t greta_host_tensor_stream(uint32_t layer, int which);
 
+/* gcore::inference::tensor_shard: out6 = {rows, cols, global rows, global cols, row0, col0} of the shard of
+ * projection `which` (LayerTensor 0..6) that rank cfg->tp_rank holds.  Needs no device. */
+GRETA_API int greta_host_tensor_shard(const greta_model_config *cfg, int which, uint32_t *out6);
+
 /* BlockScheduler::init + allocate_weights + allocate_activations(1, max_seq_len). */
 GRETA_API int greta_model_create(const greta_model_config *cfg, greta_model_t *out);
 GRETA_API int greta_model_destroy(greta_model_t m);

@@ -35,6 +35,8 @@ def test_size_helpers_need_no_device(pkg):
     # bytes per weight equal GGUF's: 18/32 and 34/32
     assert lib.greta_cuda_qs_bytes(f.FMT_Q4_0, 11008, 4096) + lib.greta_cuda_d_bytes(f.FMT_Q4_0, 11008, 4096) == 25362432
     assert lib.greta_cuda_qs_bytes(f.FMT_Q8_0, 4096, 4096) + lib.greta_cuda_d_bytes(f.FMT_Q8_0, 4096, 4096) == 17825792
+    # scale rows are padded to 16 bytes when K/32 is not a multiple of 8 (tensor-parallel shards of 11008)
+    assert lib.greta_cuda_d_bytes(f.FMT_Q4_0, 4096, 1376) == 4096 * 48 * 2
     assert lib.greta_cuda_attn_decode_scratch_bytes(32, 128) > 32 * 4
 
 

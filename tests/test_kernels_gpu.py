@@ -68,7 +68,12 @@ def test_repack_and_dequant_bit_exact(g, name):
     # the planes hold exactly GGUF's bytes: scales first two bytes of each block, payload the rest
     bb = g.GGUF_BLOCK_BYTES[gfmt]
     b2 = blk.reshape(-1, bb)
-    assert np.array_equal(w.d.download(np.uint8, N * (K // 32) * 2), b2[:, :2].reshape(-1))
+    nb = K // 32
+    nbp = (nb + 7) // 8 * 8                      # scale rows are padded to 8 entries (16 bytes), padding is zero
+    assert g.cuda().greta_cuda_d_bytes(gfmt, N, K) == N * nbp * 2
+    dplane = w.d.download(np.uint16, N * nbp).reshape(N, nbp)
+    assert np.array_equal(dplane[:, :nb].reshape(-1), b2[:, :2].copy().view(np.uint16).reshape(-1))
+    assert not dplane[:, nb:].any()
     assert np.array_equal(w.qs.download(np.uint8, b2[:, 2:].size), b2[:, 2:].reshape(-1))
 
 
@@ -374,6 +379,7 @@ def _gemm_status(g):
 
 @pytest.mark.parametrize("name", ["q4_0", "q8_0"])
 @pytest.mark.parametrize("M,N,K,a_f16,c_f16", [(33, 128, 256, True, False), (128, 130, 512, False, False), (130, 200, 256, True, True),
+                                               (40, 96, 352, True, False), (200, 4096, 1376, False, False),
                                                (257, 1000, 1024, False, True), (512, 384, 4096, True, True)])
 def test_gemm_matches_oracle(g, name, M, N, K, a_f16, c_f16):
     """C = half(A) half(dequant(W))^T: both operands rounded to fp16 as the reference's MFMA route does
@@ -407,7 +413,7 @@ def test_gemm_matches_oracle(g, name, M, N, K, a_f16, c_f16):
 def test_gemm_rejects_what_it_cannot_do(g):
     lib = g.cuda()
     buf = g.DeviceBuffer(1 << 16)
-    assert lib.greta_cuda_gemm(None, g.FMT_Q4_0, buf.ptr, 1, buf.ptr, buf.ptr, buf.ptr, 0, 64, 64, 96, None) == 4      # K % 256
+    assert lib.greta_cuda_gemm(None, g.FMT_Q4_0, buf.ptr, 1, buf.ptr, buf.ptr, buf.ptr, 0, 64, 64, 48, None) == 4      # K % 32
     assert lib.greta_cuda_gemm(None, g.FMT_F16, buf.ptr, 1, buf.ptr, buf.ptr, buf.ptr, 0, 64, 64, 256, None) == 4     # format
     assert lib.greta_cuda_gemm(None, g.FMT_Q4_0, buf.ptr, 0, buf.ptr, buf.ptr, buf.ptr, 0, 64, 64, 256, None) == 4    # fp32 A without workspace
     assert lib.greta_cuda_gemm(None, g.FMT_Q4_0, None, 1, None, None, None, 0, 0, 64, 256, None) == 0                  # empty

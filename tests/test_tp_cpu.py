@@ -1,0 +1,99 @@
+"""Host-side logic of the multi-GPU path, on CPU with two processes: the rendezvous star that
+bench.py uses to hand out the NCCL id and gather timings, and the tensor-parallel algebra (row-split
+and column-split shards from the host layer's tensor_shard, partial products summed across ranks)
+checked with the CPU oracle standing in for the kernels."""
+import ctypes as C
+import multiprocessing as mp
+import os
+import struct
+
+import numpy as np
+
+from _support import ROOT, load_package, q4_0_blocks
+
+CFG = dict(dim=256, num_heads=4, num_heads_kv=2, hidden_dim=768, head_dim=64)
+
+
+def _shard(pkg, which, rank, world):
+    from gretacore_v3_b200.model import _Config
+    c = _Config(CFG["dim"], CFG["num_heads"], CFG["num_heads_kv"], 1, 1000, CFG["hidden_dim"], CFG["head_dim"], 64, 1e4, 1e-5,
+                pkg.ffi.FMT_Q4_0, pkg.ffi.FMT_F16, rank, world)
+    out = (C.c_uint32 * 6)()
+    assert pkg.ffi.host().greta_host_tensor_shard(C.byref(c), which, out) == 0
+    return list(out)
+
+
+def _rank_main(rank, world, port, q):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    import sys
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import bench
+    from oracle import oracle as O
+    pkg = load_package()
+    ranks = bench.Ranks()
+    # 1. id hand-out: every rank ends up with rank 0's 128 bytes
+    uid = bytes(range(128)) if rank == 0 else b"\0" * 128
+    got = ranks.bcast(uid, 128)
+    ranks.barrier()
+    # 2. max over ranks lands on rank 0
+    mx = ranks.gather_max(10.0 + rank)
+    # 3. column-parallel gate (rows split) then row-parallel down (K split), partial sums exchanged through rank 0
+    rng = np.random.default_rng(5)
+    D, F = CFG["dim"], CFG["hidden_dim"]
+    w1, w2 = q4_0_blocks(rng, F, D), q4_0_blocks(rng, D, F)
+    x = rng.normal(0, 1, D).astype(np.float32)
+    r1 = _shard(pkg, 4, rank, world)      # W1 gate: rows split
+    r2 = _shard(pkg, 5, rank, world)      # W2 down: columns split
+    w1s = w1.reshape(F, D // 32, 18)[r1[4]:r1[4] + r1[0]].reshape(-1)
+    h_local = O.gemv(x, w1s, O.FMT_Q4_0, r1[0], D)[0]
+    w2s = w2.reshape(D, F // 32, 18)[:, r2[5] // 32:(r2[5] + r2[1]) // 32].reshape(-1)
+    part = O.gemv(h_local, np.ascontiguousarray(w2s), O.FMT_Q4_0, D, r2[1])[0].astype(np.float64)
+    if rank == 0:
+        total = part.copy()
+        for c in ranks.peers:
+            total += np.frombuffer(ranks._recv(c, D * 8), np.float64)
+        full = O.gemv(O.gemv(x, w1, O.FMT_Q4_0, F, D)[0], w2, O.FMT_Q4_0, D, F)[0]
+        err = float(np.abs(total - full).max() / np.abs(full).max())
+        q.put((rank, got == bytes(range(128)), mx, err, r1, r2))
+    else:
+        ranks.sock.sendall(part.tobytes())
+        q.put((rank, got == bytes(range(128)), mx, None, r1, r2))
+
+
+def test_two_rank_rendezvous_and_tensor_parallel_algebra():
+    pkg = load_package()
+    pkg.build()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 24000 + os.getpid() % 5000
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(30)
+        assert p.exitcode == 0
+    (_, ok0, mx0, err, a1, a2), (_, ok1, _, _, b1, b2) = res
+    assert ok0 and ok1                     # both ranks hold the id made on rank 0
+    assert mx0 == 11.0                     # rank 0 sees the maximum of the per-rank timings
+    assert err < 1e-6                      # sharded product + sum over ranks == unsharded product
+    F, D = CFG["hidden_dim"], CFG["dim"]
+    assert a1[:4] == [F // 2, D, F, D] and b1[4] == F // 2 and a1[4] == 0            # gate: rows split
+    assert a2[:4] == [D, F // 2, D, F] and b2[5] == F // 2 and a2[5] == 0            # down: whole blocks of K split
+
+
+def test_shards_tile_every_projection():
+    pkg = load_package()
+    pkg.build()
+    for world in (1, 2, 4):
+        if CFG["num_heads_kv"] % world:
+            continue
+        for which in range(7):
+            cover = None
+            for r in range(world):
+                rows, cols, grows, gcols, r0, c0 = _shard(pkg, which, r, world)
+                cover = np.zeros((grows, gcols // 32), np.int32) if cover is None else cover
+                assert cols % 32 == 0 and c0 % 32 == 0
+                cover[r0:r0 + rows, c0 // 32:(c0 + cols) // 32] += 1
+            assert (cover == 1).all()
