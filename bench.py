@@ -323,6 +323,17 @@ def run_case(pkg, name):
         for i in range(12):
             k, v = caches[i % 6]
             g.check(lib.greta_cuda_attn_decode(None, q.ptr, k.ptr, v.ptr, o.ptr, None, L, H, H, Dh, S, 0.0884, scratch.ptr, nbytes))
+    elif name == "decode_step":      # persistent decode-step kernel on a 4-layer model of the 7B shape (0.46 GB of weights)
+        from gretacore_v3_b200.model import LLAMA2_7B
+        cfg = dict(LLAMA2_7B)
+        cfg["num_layers"] = 4
+        m = pkg.model.Model(cfg)
+        m.load_synthetic(SEED)
+        logits = m.forward(pkg.model.synth_tokens(SEED, 512, cfg["vocab"]), 0)
+        m.begin_decode(int(np.argmax(logits)), 512)
+        m.decode_timed(6)
+        m.read_generated(6)
+        m.close()
     else:
         raise SystemExit(f"unknown case {name}")
     g.check(lib.greta_cuda_device_synchronize())
@@ -339,7 +350,7 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
     ap.add_argument("--prefill-chunk", type=int, default=0, help="tokens per prefill call (0 = the whole prompt at once)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--case", default=None, help="run a small single-kernel case (gemv_swiglu, gemv_plain, gemm_c2, attn_decode) and exit")
+    ap.add_argument("--case", default=None, help="run a small single-kernel case (gemv_swiglu, gemv_plain, gemm_c2, attn_decode, decode_step) and exit")
     args = ap.parse_args()
     ranks = Ranks()
     if ranks.world != args.gpus and ranks.world > 1:

@@ -16,190 +16,18 @@
 #include <algorithm>
 #include <mutex>
 
-#include "greta_common.cuh"
-
-using namespace greta;
+#include "attention_device.cuh"
 
 namespace {
 
 constexpr int ATT_WARPS = 4;
 constexpr int ATT_THREADS = ATT_WARPS * 32;
-constexpr int MAX_SPLITS = 32;
-
-template <typename KV, int DPL>
-__device__ __forceinline__ void load_row(const KV *p, float (&f)[DPL]) {
-  if (sizeof(KV) == 2) {
-#pragma unroll
-    for (int v = 0; v < DPL / 8; ++v) {
-      uint4 u = ld_stream(reinterpret_cast<const uint8_t *>(p) + v * 16);
-      float2 a = h2_to_f2(u.x), b = h2_to_f2(u.y), c = h2_to_f2(u.z), d = h2_to_f2(u.w);
-      f[8 * v + 0] = a.x; f[8 * v + 1] = a.y; f[8 * v + 2] = b.x; f[8 * v + 3] = b.y;
-      f[8 * v + 4] = c.x; f[8 * v + 5] = c.y; f[8 * v + 6] = d.x; f[8 * v + 7] = d.y;
-    }
-  } else {
-#pragma unroll
-    for (int v = 0; v < DPL / 4; ++v) {
-      uint4 u = ld_stream(reinterpret_cast<const uint8_t *>(p) + v * 16);
-      f[4 * v + 0] = __uint_as_float(u.x); f[4 * v + 1] = __uint_as_float(u.y);
-      f[4 * v + 2] = __uint_as_float(u.z); f[4 * v + 3] = __uint_as_float(u.w);
-    }
-  }
-}
-
-struct AttnParams {
-  const float *q;        // [nq][H][Dh]
-  const void *kc, *vc;   // [Hkv][max_seq][Dh]
-  float *o;              // [nq][H][Dh]
-  const uint32_t *d_pos; // optional device position
-  uint32_t len0;         // keys visible to query 0 when d_pos == NULL (query z sees len0 + z)
-  uint32_t H, Hkv, max_seq;
-  float scale;
-  uint32_t splits;
-  uint32_t *counters;    // [H] zero on entry, left zero
-  float *partial;        // [H][splits][Dh + 2]
-};
-
-// Merge (m2, l2, o2) into (m, l, o).
-template <int DPL>
-__device__ __forceinline__ void merge(float &m, float &l, float (&o)[DPL], float m2, float l2, const float (&o2)[DPL]) {
-  float mn = fmaxf(m, m2);
-  float c1 = (m == -INFINITY) ? 0.f : expf(m - mn);
-  float c2 = (m2 == -INFINITY) ? 0.f : expf(m2 - mn);
-  l = l * c1 + l2 * c2;
-#pragma unroll
-  for (int i = 0; i < DPL; ++i) o[i] = o[i] * c1 + o2[i] * c2;
-  m = mn;
-}
 
 template <typename KV, int DPL>
 __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnParams p) {
-  constexpr int Dh = DPL * 8;
-  __shared__ float sm_m[ATT_WARPS], sm_l[ATT_WARPS];
-  __shared__ float sm_o[ATT_WARPS][Dh];
-  __shared__ uint32_t sm_last;
-
   pdl_launch_dependents();
   pdl_wait();  // q, the position and the newest cache row come from the previous kernel
-  const uint32_t split = blockIdx.x, head = blockIdx.y, qi = blockIdx.z;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int sub = lane & 7, grp = lane >> 3;  // 8 lanes per key, 4 keys per warp step
-  const uint32_t L = (p.d_pos ? *p.d_pos + 1 : p.len0) + qi;
-  const uint32_t kvh = head / (p.H / p.Hkv);
-  const uint32_t chunk = (L + p.splits - 1) / p.splits;
-  const uint32_t k0 = split * chunk, k1 = min(L, k0 + chunk);
-
-  const KV *kbase = reinterpret_cast<const KV *>(p.kc) + (size_t)kvh * p.max_seq * Dh + sub * DPL;
-  const KV *vbase = reinterpret_cast<const KV *>(p.vc) + (size_t)kvh * p.max_seq * Dh + sub * DPL;
-
-  float qv[DPL];
-  {
-    const float *qp = p.q + ((size_t)qi * p.H + head) * Dh + sub * DPL;
-#pragma unroll
-    for (int i = 0; i < DPL; i += 4) {
-      float4 t = *reinterpret_cast<const float4 *>(qp + i);
-      qv[i] = t.x * p.scale; qv[i + 1] = t.y * p.scale; qv[i + 2] = t.z * p.scale; qv[i + 3] = t.w * p.scale;
-    }
-  }
-
-  float m = -INFINITY, l = 0.f, o[DPL];
-#pragma unroll
-  for (int i = 0; i < DPL; ++i) o[i] = 0.f;
-
-  // warp step j covers keys tw .. tw+3 and tw+16 .. tw+19 (two steps in flight), one key per lane group
-  for (uint32_t tw = k0 + 4 * warp; tw < k1; tw += 4 * ATT_WARPS * 2) {
-    const uint32_t ta = tw + grp, tb = tw + 4 * ATT_WARPS + grp;
-    const bool va = ta < k1, vb = tb < k1;
-    float ka[DPL], kb[DPL], xa[DPL], xb[DPL];
-    if (va) { load_row<KV, DPL>(kbase + (size_t)ta * Dh, ka); load_row<KV, DPL>(vbase + (size_t)ta * Dh, xa); }
-    if (vb) { load_row<KV, DPL>(kbase + (size_t)tb * Dh, kb); load_row<KV, DPL>(vbase + (size_t)tb * Dh, xb); }
-    float sa = 0.f, sb = 0.f;
-    if (va) {
-#pragma unroll
-      for (int i = 0; i < DPL; ++i) sa = fmaf(qv[i], ka[i], sa);
-    }
-    if (vb) {
-#pragma unroll
-      for (int i = 0; i < DPL; ++i) sb = fmaf(qv[i], kb[i], sb);
-    }
-    // reduce across the 8 lanes that share a key (all lanes take part in the shuffles)
-#pragma unroll
-    for (int off = 4; off > 0; off >>= 1) {
-      sa += __shfl_xor_sync(0xffffffffu, sa, off);
-      sb += __shfl_xor_sync(0xffffffffu, sb, off);
-    }
-    if (va) {
-      float mn = fmaxf(m, sa), c = expf(m - mn), pe = expf(sa - mn);
-      l = l * c + pe;
-#pragma unroll
-      for (int i = 0; i < DPL; ++i) o[i] = fmaf(pe, xa[i], o[i] * c);
-      m = mn;
-    }
-    if (vb) {
-      float mn = fmaxf(m, sb), c = expf(m - mn), pe = expf(sb - mn);
-      l = l * c + pe;
-#pragma unroll
-      for (int i = 0; i < DPL; ++i) o[i] = fmaf(pe, xb[i], o[i] * c);
-      m = mn;
-    }
-  }
-
-  // merge the four lane groups of the warp (same dims, different keys)
-#pragma unroll
-  for (int off = 8; off <= 16; off <<= 1) {
-    float m2 = __shfl_xor_sync(0xffffffffu, m, off), l2 = __shfl_xor_sync(0xffffffffu, l, off), o2[DPL];
-#pragma unroll
-    for (int i = 0; i < DPL; ++i) o2[i] = __shfl_xor_sync(0xffffffffu, o[i], off);
-    merge<DPL>(m, l, o, m2, l2, o2);
-  }
-  // merge warps through shared memory
-  if (grp == 0) {
-    if (sub == 0) { sm_m[warp] = m; sm_l[warp] = l; }
-#pragma unroll
-    for (int i = 0; i < DPL; ++i) sm_o[warp][sub * DPL + i] = o[i];
-  }
-  __syncthreads();
-  const int tid = threadIdx.x;
-  float fm = -INFINITY, fl = 0.f, fo = 0.f;  // thread tid < Dh owns output dim tid
-  if (tid < Dh) {
-#pragma unroll
-    for (int w = 0; w < ATT_WARPS; ++w) fm = fmaxf(fm, sm_m[w]);
-#pragma unroll
-    for (int w = 0; w < ATT_WARPS; ++w) {
-      float c = (sm_m[w] == -INFINITY) ? 0.f : expf(sm_m[w] - fm);
-      fl += sm_l[w] * c;
-      fo += sm_o[w][tid] * c;
-    }
-  }
-  float *out = p.o + ((size_t)qi * p.H + head) * Dh;
-  if (p.splits == 1) {
-    if (tid < Dh) out[tid] = fo / fl;
-    return;
-  }
-  // publish the partial result, take a ticket; the last CTA of this head merges all splits
-  float *mine = p.partial + ((size_t)head * p.splits + split) * (Dh + 2);
-  if (tid < Dh) mine[2 + tid] = fo;
-  if (tid == 0) { mine[0] = fm; mine[1] = fl; }
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) sm_last = (atomicAdd(&p.counters[head], 1u) == p.splits - 1) ? 1u : 0u;
-  __syncthreads();
-  if (!sm_last) return;
-  __threadfence();
-  if (tid < Dh) {
-    const float *ph = p.partial + (size_t)head * p.splits * (Dh + 2);
-    float gm = -INFINITY;
-    for (uint32_t s = 0; s < p.splits; ++s) gm = fmaxf(gm, __ldcg(ph + (size_t)s * (Dh + 2)));
-    float gl = 0.f, go = 0.f;
-    for (uint32_t s = 0; s < p.splits; ++s) {
-      const float *ps = ph + (size_t)s * (Dh + 2);
-      float ms = __ldcg(ps);
-      float c = (ms == -INFINITY) ? 0.f : expf(ms - gm);
-      gl += __ldcg(ps + 1) * c;
-      go += __ldcg(ps + 2 + tid) * c;
-    }
-    out[tid] = go / gl;
-  }
-  if (tid == 0) p.counters[head] = 0;  // ready for the next call on this stream
+  attn_body<KV, DPL, ATT_WARPS, false>(p, blockIdx.x, blockIdx.y, blockIdx.z);
 }
 
 __global__ void rope_kernel(float *x, uint32_t S, uint32_t H, uint32_t Dh, float base, uint32_t pos_offset,

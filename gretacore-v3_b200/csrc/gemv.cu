@@ -31,284 +31,11 @@
 // packed fp32 FMAs.  A simpler kernel (direct loads, float math) remains for K so
 // large that the staged activations leave no room for the ring.
 #include <math.h>
-
 #include <algorithm>
 
-#include "greta_common.cuh"
-
-using namespace greta;
+#include "gemv_device.cuh"
 
 namespace {
-
-constexpr int WARPS = 16;
-constexpr int THREADS = WARPS * 32;
-constexpr int XPAD = 36;       // floats per staged block of 32 fp32 activations (4 pad -> conflict-free LDS.128)
-constexpr int XQ_WORDS = 28;   // 32-bit words per staged fixed-point block: 3 planes x 8 words + 4 words of meta
-constexpr int MAX_STAGES = 8;
-constexpr size_t SMEM_LIMIT = 220 * 1024;
-
-enum { EPI_PLAIN = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_QKV = 3 };
-
-struct WPlane {
-  const uint8_t *qs;
-  const void *d;
-};
-
-struct GemvParams {
-  const void *x;
-  int x_is_f16;
-  const float *gamma;
-  float eps;
-  WPlane w[3];
-  uint32_t K, N, M;
-  float *y;
-  const float *resid;
-  float *q_out, *k_out, *v_out;
-  __half *k_cache, *v_cache;
-  const uint32_t *d_pos;
-  uint32_t H, Hkv, Dh, max_seq;
-  float rope_base;
-  uint32_t groups;  // row groups
-  // simple kernel
-  uint32_t kw, iters;
-  // pipelined kernel
-  uint32_t stages, slots;
-};
-
-template <int FMT>
-struct Fmt;
-template <>
-struct Fmt<GRETA_FMT_Q4_0> {
-  static constexpr int QV = 1, SCALE_BYTES = 2;
-  static constexpr bool INTEGER = true, NIBBLES = true;
-};
-template <>
-struct Fmt<GRETA_FMT_Q8_0> {
-  static constexpr int QV = 2, SCALE_BYTES = 2;
-  static constexpr bool INTEGER = true, NIBBLES = false;
-};
-template <>
-struct Fmt<GRETA_FMT_REF_INT4> {
-  static constexpr int QV = 1, SCALE_BYTES = 4;
-  static constexpr bool INTEGER = true, NIBBLES = true;
-};
-template <>
-struct Fmt<GRETA_FMT_REF_INT8> {
-  static constexpr int QV = 2, SCALE_BYTES = 4;
-  static constexpr bool INTEGER = true, NIBBLES = false;
-};
-template <>
-struct Fmt<GRETA_FMT_F16> {
-  static constexpr int QV = 4, SCALE_BYTES = 0;
-  static constexpr bool INTEGER = false, NIBBLES = false;
-};
-
-// ------------------------------------------------------------------ shared pieces
-// Maps (row group, slot) to a weight plane and a row; false for a slot without a
-// row (ragged tail).  A group holds R/2 "pairs": slot j and slot j + R/2 are the
-// two rows an epilogue combines (gate/up of one output, the two halves of one
-// rotation pair).
-template <int EPI, int R>
-__device__ __forceinline__ bool resolve(const GemvParams &p, uint32_t grp, int slot, int *mat, uint32_t *row) {
-  constexpr int PAIRS = R / 2;
-  if (EPI == EPI_PLAIN || EPI == EPI_RESIDUAL) {
-    *mat = 0;
-    *row = grp * R + slot;
-    return *row < p.N;
-  }
-  if (EPI == EPI_SWIGLU) {
-    *mat = slot / PAIRS;
-    *row = grp * PAIRS + slot % PAIRS;
-    return *row < p.N;
-  }
-  const uint32_t gph = (p.Dh / 2) / PAIRS, nq = p.H * gph, nk = p.Hkv * gph;
-  if (grp < nq + nk) {
-    uint32_t g = grp < nq ? grp : grp - nq;
-    *mat = grp < nq ? 0 : 1;
-    uint32_t head = g / gph, i = (g % gph) * PAIRS + slot % PAIRS;
-    *row = head * p.Dh + i + (slot / PAIRS) * (p.Dh / 2);
-    return true;
-  }
-  *mat = 2;
-  *row = (grp - nq - nk) * R + slot;
-  return *row < p.Hkv * p.Dh;
-}
-
-// Applies the epilogue of one row group; v[r] are the finished dot products.
-template <int EPI, int R>
-__device__ __forceinline__ void epilogue(const GemvParams &p, uint32_t grp, uint32_t m, uint32_t pos, const float (&v)[R]) {
-  constexpr int PAIRS = R / 2;
-  if (EPI == EPI_PLAIN) {
-#pragma unroll
-    for (int r = 0; r < R; ++r)
-      if (grp * R + r < p.N) p.y[(size_t)m * p.N + grp * R + r] = v[r];
-  } else if (EPI == EPI_RESIDUAL) {
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      uint32_t row = grp * R + r;
-      if (row < p.N) p.y[row] = p.resid[row] + v[r];
-    }
-  } else if (EPI == EPI_SWIGLU) {
-#pragma unroll
-    for (int j = 0; j < PAIRS; ++j) {
-      uint32_t o = grp * PAIRS + j;
-      if (o < p.N) {
-        float g = v[j], u = v[j + PAIRS];
-        p.y[o] = (g / (1.0f + expf(-g))) * u;
-      }
-    }
-  } else {
-    const uint32_t gph = (p.Dh / 2) / PAIRS, nq = p.H * gph, nk = p.Hkv * gph;
-    if (grp < nq + nk) {
-      const bool is_q = grp < nq;
-      uint32_t g = is_q ? grp : grp - nq;
-      uint32_t head = g / gph;
-#pragma unroll
-      for (int j = 0; j < PAIRS; ++j) {
-        uint32_t i = (g % gph) * PAIRS + j;
-        float o0 = v[j], o1 = v[j + PAIRS];
-        if (p.d_pos) {
-          float theta = (float)pos * powf(p.rope_base, -2.0f * (float)i / (float)p.Dh);
-          float c = cosf(theta), s = sinf(theta);
-          o0 = v[j] * c - v[j + PAIRS] * s;
-          o1 = v[j] * s + v[j + PAIRS] * c;
-        }
-        if (is_q) {
-          p.q_out[head * p.Dh + i] = o0;
-          p.q_out[head * p.Dh + i + p.Dh / 2] = o1;
-        } else {
-          if (p.k_out) {
-            p.k_out[head * p.Dh + i] = o0;
-            p.k_out[head * p.Dh + i + p.Dh / 2] = o1;
-          }
-          if (p.k_cache) {
-            size_t dst = ((size_t)head * p.max_seq + pos) * p.Dh + i;
-            p.k_cache[dst] = __float2half_rn(o0);
-            p.k_cache[dst + p.Dh / 2] = __float2half_rn(o1);
-          }
-        }
-      }
-    } else {
-#pragma unroll
-      for (int r = 0; r < R; ++r) {
-        uint32_t row = (grp - nq - nk) * R + r;
-        if (row < p.Hkv * p.Dh) {
-          if (p.v_out) p.v_out[row] = v[r];
-          uint32_t head = row / p.Dh, dd = row % p.Dh;
-          if (p.v_cache) p.v_cache[((size_t)head * p.max_seq + pos) * p.Dh + dd] = __float2half_rn(v[r]);
-        }
-      }
-    }
-  }
-}
-
-// Sum of squares of the activation row over the CTA -> 1/rms.
-__device__ __forceinline__ float cta_inv_rms(const float *xf, const __half *xh, uint32_t K, float eps, float *red) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  float ss = 0.f;
-  for (uint32_t k = threadIdx.x; k < K; k += THREADS) {
-    float v = xf ? xf[k] : __half2float(xh[k]);
-    ss = fmaf(v, v, ss);
-  }
-  ss = warp_sum(ss);
-  if (lane == 0) red[warp] = ss;
-  __syncthreads();
-  float t = (lane < WARPS) ? red[lane] : 0.f;
-  t = warp_sum(t);
-  return rsqrtf(t / (float)K + eps);
-}
-
-__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
-
-// ------------------------------------------------------------------ float math (fp16 weights, simple kernel)
-__device__ __forceinline__ uint32_t lop_and_or(uint32_t a, uint32_t m, uint32_t o) {
-  uint32_t r;
-  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(m), "r"(o));  // (a & m) | o
-  return r;
-}
-__device__ __forceinline__ uint32_t hsub2_u(uint32_t a, uint32_t b) {
-  __half2 r = __hsub2(*reinterpret_cast<__half2 *>(&a), *reinterpret_cast<__half2 *>(&b));
-  return *reinterpret_cast<uint32_t *>(&r);
-}
-__device__ __forceinline__ uint32_t hfma2_u(uint32_t a, uint32_t b, uint32_t c) {
-  __half2 r = __hfma2(*reinterpret_cast<__half2 *>(&a), *reinterpret_cast<__half2 *>(&b),
-                      *reinterpret_cast<__half2 *>(&c));
-  return *reinterpret_cast<uint32_t *>(&r);
-}
-
-// Position of element j (0..31) of a block inside its staged 32-float slot (float path).
-template <int FMT>
-__device__ __forceinline__ int xs_slot(int j) {
-  if (FMT == GRETA_FMT_Q4_0) {
-    int hi = j >> 4, jj = j & 15, wi = jj >> 2, r = jj & 3;
-    int pr = (r == 1) ? 2 : (r == 2) ? 1 : r;  // order e0,e2,e1,e3
-    return 8 * wi + 4 * hi + pr;
-  }
-  if (FMT == GRETA_FMT_REF_INT4) {
-    int wi = j >> 3, e = j & 7;  // staged order e0,e4,e2,e6,e1,e5,e3,e7: the 3-bit reversal of e
-    return 8 * wi + ((e & 1) << 2 | (e & 2) | (e >> 2));
-  }
-  return j;
-}
-
-// x * (q - 8) over the 8 nibbles of one payload word (exact fp16 integers via the 0x6400 exponent trick).
-__device__ __forceinline__ float2 dot_nib8(uint32_t w, float4 xa, float4 xb, float2 s) {
-  const uint32_t MAGIC = 0x64006400u, C1032 = 0x64086408u, SIXTEENTH = 0x2C002C00u, CM72 = 0xD480D480u;
-  uint32_t w8 = w >> 8;
-  uint32_t lo = lop_and_or(w, 0x000F000Fu, MAGIC), hi = lop_and_or(w, 0x00F000F0u, MAGIC);
-  uint32_t lo2 = lop_and_or(w8, 0x000F000Fu, MAGIC), hi2 = lop_and_or(w8, 0x00F000F0u, MAGIC);
-  float2 a = h2_to_f2(hsub2_u(lo, C1032)), a2 = h2_to_f2(hsub2_u(lo2, C1032));
-  float2 b = h2_to_f2(hfma2_u(hi, SIXTEENTH, CM72)), b2 = h2_to_f2(hfma2_u(hi2, SIXTEENTH, CM72));
-  s = ffma2(make_float2(xa.x, xa.y), a, s);
-  s = ffma2(make_float2(xa.z, xa.w), a2, s);
-  s = ffma2(make_float2(xb.x, xb.y), b, s);
-  s = ffma2(make_float2(xb.z, xb.w), b2, s);
-  return s;
-}
-__device__ __forceinline__ float2 dot_i8x4(uint32_t w, float4 xv, float2 s) {
-  const uint32_t C1152 = 0x64806480u;  // 1024 + 128
-  uint32_t t = w ^ 0x80808080u;
-  uint32_t h01 = __byte_perm(t, 0x64646464u, 0x5140), h23 = __byte_perm(t, 0x64646464u, 0x7362);
-  s = ffma2(make_float2(xv.x, xv.y), h2_to_f2(hsub2_u(h01, C1152)), s);
-  s = ffma2(make_float2(xv.z, xv.w), h2_to_f2(hsub2_u(h23, C1152)), s);
-  return s;
-}
-template <int FMT>
-__device__ __forceinline__ float block_dot_f(const uint4 *q, const float4 *xv) {
-  float2 s = make_float2(0.f, 0.f);
-  if (FMT == GRETA_FMT_Q4_0 || FMT == GRETA_FMT_REF_INT4) {
-    const uint32_t flip = (FMT == GRETA_FMT_REF_INT4) ? 0x88888888u : 0u;  // two's complement -> offset 8
-    s = dot_nib8(q[0].x ^ flip, xv[0], xv[1], s);
-    s = dot_nib8(q[0].y ^ flip, xv[2], xv[3], s);
-    s = dot_nib8(q[0].z ^ flip, xv[4], xv[5], s);
-    s = dot_nib8(q[0].w ^ flip, xv[6], xv[7], s);
-  } else if (FMT == GRETA_FMT_Q8_0 || FMT == GRETA_FMT_REF_INT8) {
-    s = dot_i8x4(q[0].x, xv[0], s);
-    s = dot_i8x4(q[0].y, xv[1], s);
-    s = dot_i8x4(q[0].z, xv[2], s);
-    s = dot_i8x4(q[0].w, xv[3], s);
-    s = dot_i8x4(q[1].x, xv[4], s);
-    s = dot_i8x4(q[1].y, xv[5], s);
-    s = dot_i8x4(q[1].z, xv[6], s);
-    s = dot_i8x4(q[1].w, xv[7], s);
-  } else {
-#pragma unroll
-    for (int v = 0; v < 4; ++v) {
-      s = ffma2(make_float2(xv[2 * v].x, xv[2 * v].y), h2_to_f2(q[v].x), s);
-      s = ffma2(make_float2(xv[2 * v].z, xv[2 * v].w), h2_to_f2(q[v].y), s);
-      s = ffma2(make_float2(xv[2 * v + 1].x, xv[2 * v + 1].y), h2_to_f2(q[v].z), s);
-      s = ffma2(make_float2(xv[2 * v + 1].z, xv[2 * v + 1].w), h2_to_f2(q[v].w), s);
-    }
-  }
-  return s.x + s.y;
-}
-
-template <int FMT>
-__device__ __forceinline__ float load_scale(const void *d, size_t idx) {
-  if (Fmt<FMT>::SCALE_BYTES == 0) return 1.0f;
-  if (Fmt<FMT>::SCALE_BYTES == 2) return __half2float(__ldg(reinterpret_cast<const __half *>(d) + idx));
-  return __ldg(reinterpret_cast<const float *>(d) + idx);
-}
 
 // ------------------------------------------------------------------ simple kernel (any K % 32 == 0)
 // Direct register loads, two stages, float math; a warp owns one row group over
@@ -375,7 +102,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_simple_kernel(const GemvParam
     const __half *xh = p.x_is_f16 ? reinterpret_cast<const __half *>(p.x) + (size_t)m * K : nullptr;
     float inv = p.gamma ? cta_inv_rms(xf, xh, K, p.eps, red) : 1.0f;
     for (uint32_t k = threadIdx.x; k < K; k += THREADS) {
-      float v = xf ? xf[k] : __half2float(xh[k]);
+      float v = xf ? __ldcg(xf + k) : __half2float(__ldcg(xh + k));
       if (p.gamma) v = (v * inv) * p.gamma[k];
       xs[(k >> 5) * XPAD + xs_slot<FMT>(k & 31)] = v;
     }
@@ -437,164 +164,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_simple_kernel(const GemvParam
   }
 }
 
-// ------------------------------------------------------------------ pipelined kernel
-__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc) {
-  uint32_t s = (uint32_t)__cvta_generic_to_shared(smem_dst);
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gsrc) : "memory");
-}
-__device__ __forceinline__ void cp_async4(void *smem_dst, const void *gsrc) {
-  uint32_t s = (uint32_t)__cvta_generic_to_shared(smem_dst);
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(s), "l"(gsrc) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait(int pending) {  // at most `pending` groups still in flight
-  switch (pending) {
-    case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
-    case 1: asm volatile("cp.async.wait_group 1;" ::: "memory"); break;
-    case 2: asm volatile("cp.async.wait_group 2;" ::: "memory"); break;
-    case 3: asm volatile("cp.async.wait_group 3;" ::: "memory"); break;
-    case 4: asm volatile("cp.async.wait_group 4;" ::: "memory"); break;
-    case 5: asm volatile("cp.async.wait_group 5;" ::: "memory"); break;
-    default: asm volatile("cp.async.wait_group 6;" ::: "memory"); break;
-  }
-}
-
-__device__ __forceinline__ int dp4a_su(uint32_t x_s8x4, uint32_t w_u8x4, int c) {
-  int r;
-  asm("dp4a.s32.u32 %0, %1, %2, %3;" : "=r"(r) : "r"(x_s8x4), "r"(w_u8x4), "r"(c));
-  return r;
-}
-__device__ __forceinline__ int dp4a_ss(uint32_t x_s8x4, uint32_t w_s8x4, int c) {
-  int r;
-  asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(r) : "r"(x_s8x4), "r"(w_s8x4), "r"(c));
-  return r;
-}
-
-// Element of the block that sits in byte slot s (0..31) of the unpacked weight
-// bytes: slots 8w..8w+3 are the masked low nibbles of payload word w, 8w+4..8w+7
-// its high nibbles; int8 payloads are in natural order.
-template <int FMT>
-__device__ __forceinline__ int slot_element(int s) {
-  if (FMT == GRETA_FMT_Q4_0) return ((s >> 2) & 1) * 16 + (s >> 3) * 4 + (s & 3);
-  if (FMT == GRETA_FMT_REF_INT4) return (s >> 3) * 8 + (s & 3) * 2 + ((s >> 2) & 1);
-  return s;
-}
-
-// Stages the (normalised) activations as block fixed point.  Thread t of each
-// group of 8 owns byte slots 4j..4j+3 (j = t & 7) of block t >> 3.
-// Layout per block, 28 words: plane p word j at [8p + j]; meta at [24..27] =
-// {c0, c1, c2, scale bits}, c_p = -8 * sum of plane p's digits for the offset-8
-// nibble formats (0 for int8), folded into the dp4a accumulators.
-template <int FMT>
-__device__ void stage_fixed_point(const GemvParams &p, uint32_t m, uint32_t *xq, float *red) {
-  const uint32_t K = p.K, nb = K / 32;
-  const float *xf = p.x_is_f16 ? nullptr : reinterpret_cast<const float *>(p.x) + (size_t)m * K;
-  const __half *xh = p.x_is_f16 ? reinterpret_cast<const __half *>(p.x) + (size_t)m * K : nullptr;
-  const float inv = p.gamma ? cta_inv_rms(xf, xh, K, p.eps, red) : 1.0f;
-  const int j = threadIdx.x & 7;
-  for (uint32_t b = threadIdx.x >> 3; b < ((nb + 63) & ~63u); b += THREADS / 8) {  // uniform trip count for the shuffles
-    const bool live = b < nb;
-    float v[4];
-    float amax = 0.f;
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      uint32_t idx = b * 32 + slot_element<FMT>(4 * j + k);
-      float t = 0.f;
-      if (live) {
-        t = xf ? xf[idx] : __half2float(xh[idx]);
-        if (p.gamma) t = (t * inv) * p.gamma[idx];
-      }
-      v[k] = t;
-      amax = fmaxf(amax, fabsf(t));
-      if (t != t) amax = INFINITY;  // NaN in -> NaN out
-    }
-#pragma unroll
-    for (int o = 1; o <= 4; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    // amax in [2^E, 2^(E+1)): X = rint(x * 2^(21-E)) has |X| <= 2^22, so the signed byte digits
-    // d0, d1 in [-128, 127] leave d2 in [-64, 64] even after their carries.
-    const uint32_t ab = __float_as_uint(amax);
-    const int E = (int)(ab >> 23) - 127;
-    float sc, isc;
-    if (amax == INFINITY) {
-      sc = __uint_as_float(0x7FC00000u);  // poison the block
-      isc = 0.f;
-    } else if (E < -100) {
-      sc = 0.f;  // all (near) zero
-      isc = 0.f;
-    } else {
-      sc = __uint_as_float((uint32_t)(127 + E - 21) << 23);
-      isc = __uint_as_float((uint32_t)(127 + 21 - E) << 23);
-    }
-    uint32_t w0 = 0, w1 = 0, w2 = 0;
-    int s0 = 0, s1 = 0, s2 = 0;
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      int X = __float2int_rn(v[k] * isc);
-      int d0 = (int)(int8_t)(X & 0xFF);   // X = d0 + 256 d1 + 65536 d2, signed byte digits
-      int X1 = (X - d0) >> 8;
-      int d1 = (int)(int8_t)(X1 & 0xFF);
-      int d2 = (X1 - d1) >> 8;
-      w0 |= (uint32_t)(d0 & 0xFF) << (8 * k);
-      w1 |= (uint32_t)(d1 & 0xFF) << (8 * k);
-      w2 |= (uint32_t)(d2 & 0xFF) << (8 * k);
-      s0 += d0;
-      s1 += d1;
-      s2 += d2;
-    }
-#pragma unroll
-    for (int o = 1; o <= 4; o <<= 1) {
-      s0 += __shfl_xor_sync(0xffffffffu, s0, o);
-      s1 += __shfl_xor_sync(0xffffffffu, s1, o);
-      s2 += __shfl_xor_sync(0xffffffffu, s2, o);
-    }
-    if (live) {
-      uint32_t *blk = xq + (size_t)b * XQ_WORDS;
-      blk[j] = w0;
-      blk[8 + j] = w1;
-      blk[16 + j] = w2;
-      if (j == 0) {
-        const int off = Fmt<FMT>::NIBBLES ? -8 : 0;
-        blk[24] = (uint32_t)(off * s0);
-        blk[25] = (uint32_t)(off * s1);
-        blk[26] = (uint32_t)(off * s2);
-        blk[27] = __float_as_uint(sc);
-      }
-    }
-  }
-}
-
-// One block of 32 weights of one row against the fixed-point activations.
-// Returns sum_i X_i * q_i (offset already applied) as fp32.
-template <int FMT>
-__device__ __forceinline__ float block_dot_i(const uint4 *q, const uint4 (&xp)[7]) {
-  int s0 = (int)xp[6].x, s1 = (int)xp[6].y, s2 = (int)xp[6].z;
-  const uint32_t *p0 = reinterpret_cast<const uint32_t *>(&xp[0]);  // plane p word j at p0[8p + j]
-  if (Fmt<FMT>::NIBBLES) {
-    const uint32_t flip = (FMT == GRETA_FMT_REF_INT4) ? 0x88888888u : 0u;
-    const uint32_t w[4] = {q[0].x ^ flip, q[0].y ^ flip, q[0].z ^ flip, q[0].w ^ flip};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      uint32_t lo = w[i] & 0x0F0F0F0Fu, hi = (w[i] >> 4) & 0x0F0F0F0Fu;
-      s0 = dp4a_su(p0[2 * i], lo, s0);
-      s1 = dp4a_su(p0[8 + 2 * i], lo, s1);
-      s2 = dp4a_su(p0[16 + 2 * i], lo, s2);
-      s0 = dp4a_su(p0[2 * i + 1], hi, s0);
-      s1 = dp4a_su(p0[8 + 2 * i + 1], hi, s1);
-      s2 = dp4a_su(p0[16 + 2 * i + 1], hi, s2);
-    }
-  } else {
-    const uint32_t w[8] = {q[0].x, q[0].y, q[0].z, q[0].w, q[1].x, q[1].y, q[1].z, q[1].w};
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      s0 = dp4a_ss(p0[i], w[i], s0);
-      s1 = dp4a_ss(p0[8 + i], w[i], s1);
-      s2 = dp4a_ss(p0[16 + i], w[i], s2);
-    }
-  }
-  // X = d0 + 256 d1 + 65536 d2; |s0 + 256 s1| < 2^31, each term exact in fp32
-  return fmaf(65536.f, (float)s2, (float)(s0 + (s1 << 8)));
-}
-
 template <int FMT, int EPI, int R>
 __global__ void __launch_bounds__(THREADS, 1) gemv_pipe_kernel(const GemvParams p) {
   using F = Fmt<FMT>;
@@ -603,6 +172,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pipe_kernel(const GemvParams 
   constexpr int STAGE_BYTES = R * (32 * PB + SCALE_ROW);
   extern __shared__ __align__(16) uint8_t smem[];
   __shared__ float red[32];
+  __shared__ float2 rope_cs[64];                                  // head_dim <= 128
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const uint32_t nb = p.K / 32, C = (nb + 31) / 32;               // chunks (cells) per row group
@@ -691,11 +261,12 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pipe_kernel(const GemvParams 
     const __half *xh = p.x_is_f16 ? reinterpret_cast<const __half *>(p.x) + (size_t)m * K : nullptr;
     float inv = p.gamma ? cta_inv_rms(xf, xh, K, p.eps, red) : 1.0f;
     for (uint32_t k = threadIdx.x; k < K; k += THREADS) {
-      float v = xf ? xf[k] : __half2float(xh[k]);
+      float v = xf ? __ldcg(xf + k) : __half2float(__ldcg(xh + k));
       if (p.gamma) v = (v * inv) * p.gamma[k];
       xs[(k >> 5) * XPAD + (k & 31)] = v;
     }
   }
+  if (EPI == EPI_QKV && p.d_pos) fill_rope_table(p, __ldcg(p.d_pos), rope_cs);
   __syncthreads();
 
   // ---- consume ----
@@ -766,24 +337,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pipe_kernel(const GemvParams 
   cp_async_wait(0);
   __syncthreads();
 
-  // ---- epilogue: one thread per row group, contributions summed in warp order ----
-  const uint32_t pos = (EPI == EPI_QKV && p.d_pos) ? *p.d_pos : 0u;
-  for (uint32_t g = g0 + threadIdx.x; g < g1; g += THREADS) {
-    const uint32_t lo = (g - g0) * C, hi = lo + C;  // this group's cells
-    float v[R];
-#pragma unroll
-    for (int r = 0; r < R; ++r) v[r] = 0.f;
-    for (uint32_t w = 0; w < (uint32_t)WARPS; ++w) {
-      const uint32_t wc0 = (uint32_t)((uint64_t)w * T / WARPS), wc1 = (uint32_t)((uint64_t)(w + 1) * T / WARPS);
-      if (wc0 < hi && wc1 > lo && wc1 > wc0) {
-        const uint32_t wfirst = g0 + wc0 / C;
-        const float *src = part + ((size_t)w * p.slots + (g - wfirst)) * R;
-#pragma unroll
-        for (int r = 0; r < R; ++r) v[r] += src[r];
-      }
-    }
-    epilogue<EPI, R>(p, g, m, pos, v);
-  }
+  // ---- epilogue: one warp per row group ----
+  const uint32_t pos = (EPI == EPI_QKV && p.d_pos) ? __ldcg(p.d_pos) : 0u;
+  cta_epilogue<EPI, R>(p, part, p.slots, g0, g1, C, T, m, pos, (EPI == EPI_QKV && p.d_pos) ? rope_cs : nullptr);
 }
 
 // ------------------------------------------------------------------ host side

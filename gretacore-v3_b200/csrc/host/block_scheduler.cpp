@@ -13,6 +13,7 @@
 // single graph launch with no host round trip.
 #include <chrono>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 
 #include "gcore/greta_b200.hpp"
@@ -425,6 +426,49 @@ int32_t BlockScheduler::sample_greedy_gpu(size_t logits_offset_bytes, std::strin
   return id;
 }
 
+// Describes the model to the persistent decode-step kernel (single GPU only).
+static void fill_decode_desc(greta_decode_desc &d, const ModelConfig &c, ActivationBuffers &a, Buffer &embd, size_t max_seq) {
+  d = greta_decode_desc{};
+  d.weight_fmt = fmt_of(c.weight_type);
+  d.dim = c.dim; d.num_heads = c.num_heads; d.num_heads_kv = c.num_heads_kv; d.head_dim = c.head_dim; d.hidden_dim = c.hidden_dim;
+  d.max_seq_len = (uint32_t)max_seq; d.num_layers = c.num_layers; d.vocab_size = c.vocab_size;
+  d.rope_base = c.rope_base; d.rms_eps = c.rms_eps; d.attn_scale = 1.0f / std::sqrt((float)c.head_dim);
+  d.x = static_cast<float *>(a.x.data()); d.q = static_cast<float *>(a.q.data());
+  d.attn_out = static_cast<float *>(a.attn_out.data()); d.mlp_gate = static_cast<float *>(a.mlp_gate.data());
+  d.d_pos = static_cast<const uint32_t *>(a.d_pos.data()); d.d_token = static_cast<const int32_t *>(a.d_next.data());
+  d.tok_embd_f16 = embd.data(); d.attn_scratch = a.attn_scratch.data(); d.attn_scratch_bytes = a.attn_scratch.size();
+}
+
+bool BlockScheduler::build_decode_plan(std::string *err) {
+  const ModelConfig &c = config_;
+  greta_decode_desc d;
+  fill_decode_desc(d, c, activations_, token_embd_, max_seq_);
+  std::vector<greta_decode_layer> layers(c.num_layers);
+  const size_t cache_l = (size_t)kv_heads_l_ * max_seq_ * c.head_dim;
+  for (uint32_t l = 0; l < c.num_layers; ++l) {
+    BlockBuffers &b = blocks_[l];
+    greta_decode_layer &w = layers[l];
+    w.wq_qs = b.wq.data(); w.wq_d = b.s_wq.data(); w.wk_qs = b.wk.data(); w.wk_d = b.s_wk.data(); w.wv_qs = b.wv.data(); w.wv_d = b.s_wv.data();
+    w.wo_qs = b.wo.data(); w.wo_d = b.s_wo.data(); w.w1_qs = b.w1.data(); w.w1_d = b.s_w1.data(); w.w2_qs = b.w2.data(); w.w2_d = b.s_w2.data();
+    w.w3_qs = b.w3.data(); w.w3_d = b.s_w3.data();
+    w.attn_norm = static_cast<const float *>(b.attn_norm.data()); w.ffn_norm = static_cast<const float *>(b.ffn_norm.data());
+    w.k_cache = static_cast<uint16_t *>(activations_.kv_cache_k.data()) + l * cache_l;
+    w.v_cache = static_cast<uint16_t *>(activations_.kv_cache_v.data()) + l * cache_l;
+  }
+  const size_t bytes = greta_cuda_decode_plan_bytes(c.num_layers);
+  if (!decode_plan_.allocate(bytes, BufferUsage::DeviceOnly, GretaDataType::INT8, err)) return false;
+  GRETA_TRY(greta_cuda_memset(decode_plan_.data(), 0, bytes, nullptr), "decode plan");
+  GRETA_TRY(greta_cuda_device_synchronize(), "decode plan");
+  GRETA_TRY(greta_cuda_decode_plan_build(H(stream_), &d, layers.data(), decode_plan_.data(), bytes), "decode plan");
+  return true;
+}
+
+bool BlockScheduler::decode_trace(long long *out25) {
+  for (int i = 0; i < 25; ++i) out25[i] = 0;
+  if (!persistent_step_ || !decode_plan_.data()) return true;
+  return greta_cuda_decode_trace(decode_plan_.data(), out25) == GRETA_OK;
+}
+
 // ------------------------------------------------------------------ device-side decode loop
 bool BlockScheduler::begin_decode(int32_t first_token, size_t pos, std::string *err) {
   if (pos >= max_seq_) return fail(err, "begin_decode: position exceeds max_seq_len");
@@ -437,12 +481,28 @@ bool BlockScheduler::begin_decode(int32_t first_token, size_t pos, std::string *
   decode_steps_ = 0;
   if (!graph_captured_) {
     const ModelConfig &c = config_;
+    // The step is a graph of the per-layer operators chained by programmatic dependent launch.
+    // GRETA_PERSISTENT_STEP=1 (one GPU only) runs all layers as one persistent kernel instead; it
+    // gives identical results and is kept as an option: measured slower so far (the per-phase
+    // activation staging and grid barriers cost more than the launches they replace).
+    const char *env = std::getenv("GRETA_PERSISTENT_STEP");
+    persistent_step_ = c.tp_size == 1 && env && env[0] == '1';
+    if (persistent_step_ && !build_decode_plan(err)) return false;
+    greta_decode_desc desc;
+    fill_decode_desc(desc, c, a, token_embd_, max_seq_);
     graph_ = gcore::rt::GretaContext::instance().create_graph();
     graph_->capture_start(stream_);
-    bool ok = greta_cuda_embedding(s, static_cast<const int32_t *>(a.d_next.data()), token_embd_.data(), 1, static_cast<float *>(a.x.data()), 1,
-                                   c.dim, c.vocab_size) == GRETA_OK;
-    if (ok && c.tp_size > 1) ok = greta_cuda_memset(logits_.data(), 0, logits_.size(), s) == GRETA_OK;
-    ok = ok && decode_layers(err) && lm_head(static_cast<const float *>(a.x.data()), err);
+    bool ok;
+    if (persistent_step_) {
+      ok = greta_cuda_decode_layers(s, &desc, decode_plan_.data()) == GRETA_OK;
+      if (!ok && err) *err = gcore::host::cuda_error("decode_layers");
+    } else {
+      ok = greta_cuda_embedding(s, static_cast<const int32_t *>(a.d_next.data()), token_embd_.data(), 1, static_cast<float *>(a.x.data()), 1,
+                                c.dim, c.vocab_size) == GRETA_OK;
+      if (ok && c.tp_size > 1) ok = greta_cuda_memset(logits_.data(), 0, logits_.size(), s) == GRETA_OK;
+      ok = ok && decode_layers(err);
+    }
+    ok = ok && lm_head(static_cast<const float *>(a.x.data()), err);
     uint32_t *dp = static_cast<uint32_t *>(a.d_pos.data());
     ok = ok && greta_cuda_argmax_advance(s, static_cast<const float *>(logits_.data()), c.vocab_size, static_cast<int32_t *>(a.d_next.data()), dp,
                                          static_cast<int32_t *>(a.out_tokens.data()), dp + 1, (uint32_t)max_seq_) == GRETA_OK;

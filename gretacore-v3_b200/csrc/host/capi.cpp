@@ -171,6 +171,7 @@ int greta_model_decode_e2e(greta_model_t m, int32_t first_token, uint32_t pos, u
   *ms = e1->elapsed_time_since(e0.get());
   return 0;
 }
+int greta_model_decode_trace(greta_model_t m, long long *out25) { return done(M(m)->sched.decode_trace(out25), "decode_trace failed"); }
 uint64_t greta_model_weight_bytes(greta_model_t m) { return M(m)->sched.weight_bytes(); }
 void *greta_model_stream(greta_model_t m) { return static_cast<gcore::rt::cuda::GretaStreamCuda *>(M(m)->sched.stream())->handle(); }
 int greta_model_set_comm(greta_model_t m, void *comm) {

@@ -417,14 +417,18 @@ public:
   gcore::rt::GretaStream *stream() { return stream_; }
   void set_all_reduce(AllReduceFn fn) { all_reduce_ = std::move(fn); }
   uint64_t weight_bytes() const { return weight_bytes_; }
+  bool decode_trace(long long *out25);
 
 private:
   bool decode_layers(std::string *err);
+  bool build_decode_plan(std::string *err);
   bool lm_head(const float *x_row, std::string *err);
   ModelConfig config_;
   std::vector<BlockBuffers> blocks_;
   ActivationBuffers activations_;
   gcore::rt::cuda::Buffer token_embd_, output_norm_, output_weight_, s_output_weight_, logits_;
+  gcore::rt::cuda::Buffer decode_plan_;   // persistent decode-step kernel: descriptors + barrier state
+  bool persistent_step_ = false;
   gcore::rt::GretaStream *stream_ = nullptr;
   gcore::rt::GretaGraph *graph_ = nullptr;
   bool graph_captured_ = false, initialized_ = false;

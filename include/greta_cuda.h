@@ -177,6 +177,44 @@ GRETA_API int greta_cuda_fused_ffn_front(greta_stream_t stream, int fmt, const f
                                          const void *w1_d, const void *w3_qs, const void *w3_d,
                                          float *y, uint32_t D, uint32_t F);
 
+/* ------------------------------------------------------------------ whole decode step, one launch
+ * All decoder layers of one batch-1 decode step as a single persistent kernel: the five operators
+ * above, per layer, as phases of one launch separated by grid-wide barriers, with the weight stream
+ * kept in flight across the phases.  Stands in for the per-layer loop of BlockScheduler::forward
+ * (src/inference/src/block_scheduler.cpp:4199-4202) replayed from a graph (:4186-4191).  Results are
+ * identical to calling the operators one by one.  Single GPU, Q4_0 / Q8_0 weights, M = 1.
+ * The caller describes the model once (greta_decode_desc + one greta_decode_layer per layer, all
+ * device pointers), provides greta_cuda_decode_plan_bytes() bytes of zeroed device memory for the plan,
+ * builds it, then calls greta_cuda_decode_layers once per token: it reads the token id from
+ * *d_token, writes its embedding to x, runs the layers at position *d_pos and leaves the final hidden
+ * state in x.  Every device-side wait is bounded; greta_cuda_decode_status returns a non-zero code if
+ * one ever gave up (the plan memory must then be zeroed and rebuilt). */
+typedef struct greta_decode_layer {
+  const void *wq_qs, *wq_d, *wk_qs, *wk_d, *wv_qs, *wv_d, *wo_qs, *wo_d, *w1_qs, *w1_d, *w2_qs, *w2_d, *w3_qs, *w3_d;
+  const float *attn_norm, *ffn_norm;
+  void *k_cache, *v_cache; /* fp16 [Hkv][max_seq][Dh] of this layer */
+} greta_decode_layer;
+typedef struct greta_decode_desc {
+  int weight_fmt;
+  uint32_t dim, num_heads, num_heads_kv, head_dim, hidden_dim, max_seq_len, num_layers, vocab_size;
+  float rope_base, rms_eps, attn_scale;
+  float *x, *q, *attn_out, *mlp_gate;      /* activations: [dim], [H*Dh], [H*Dh], [hidden] */
+  const uint32_t *d_pos;
+  const int32_t *d_token;
+  const void *tok_embd_f16;                /* [vocab][dim] */
+  void *attn_scratch;
+  size_t attn_scratch_bytes;
+} greta_decode_desc;
+GRETA_API size_t greta_cuda_decode_plan_bytes(uint32_t num_layers);
+GRETA_API int greta_cuda_decode_plan_build(greta_stream_t stream, const greta_decode_desc *desc,
+                                           const greta_decode_layer *layers_host, void *plan, size_t plan_bytes);
+GRETA_API int greta_cuda_decode_layers(greta_stream_t stream, const greta_decode_desc *desc, void *plan);
+GRETA_API int greta_cuda_decode_status(const void *plan, int *code);
+/* Timing probe: SM clock stamps taken by CTA 0 in layer 1 of the last step, 5 phases (QKV, attention, O,
+ * gate/up, down) x 5 marks (phase start, activations staged, weights consumed, epilogue done, barrier
+ * passed).  Synchronises. */
+GRETA_API int greta_cuda_decode_trace(const void *plan, long long *out25);
+
 /* ------------------------------------------------------------------ prefill GEMM
  * C[M x N] = half(A[M x K]) * half(dequant(W))^T, fp32 accumulation on the
  * tensor cores (tcgen05, TMEM accumulators); A fp32 or fp16, C fp32 or fp16.

@@ -69,6 +69,8 @@ GRETA_API int greta_model_decode_timed(greta_model_t m, uint32_t steps, float *m
  * to the host before the next step.  *ms = device time of the whole loop (events), copies included;
  * out receives the `steps` ids.  Bytes per step: 4 up, 4 down. */
 GRETA_API int greta_model_decode_e2e(greta_model_t m, int32_t first_token, uint32_t pos, uint32_t steps, int32_t *out, float *ms);
+/* greta_cuda_decode_trace of the model's persistent decode step (zeros when that path is off). */
+GRETA_API int greta_model_decode_trace(greta_model_t m, long long *out25);
 GRETA_API uint64_t greta_model_weight_bytes(greta_model_t m);
 GRETA_API void *greta_model_stream(greta_model_t m);
 /* Installs the tensor-parallel exchange: an NCCL communicator made with greta_cuda_comm_init. */

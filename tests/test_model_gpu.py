@@ -93,6 +93,27 @@ def test_long_prompt_takes_the_tensor_core_route_and_matches_oracle(pkg):
     m.close()
 
 
+def test_persistent_decode_step_gives_the_same_ids(pkg, monkeypatch):
+    """GRETA_PERSISTENT_STEP=1: all layers of a decode step in one persistent kernel (grid barriers between the
+    phases) - same greedy ids as the oracle and as the operator-by-operator graph."""
+    cfg, seed, n_new = SMALL_MHA, 13, 20
+    weights = pkg.model.synth_weights(cfg, seed)
+    prompt = pkg.model.synth_tokens(seed, 18, cfg["vocab"])
+    want, gaps = O.Model(cfg, weights).generate(prompt, n_new)
+    assert min(gaps) > 1e-6
+    monkeypatch.setenv("GRETA_PERSISTENT_STEP", "1")
+    m = pkg.model.Model(cfg)
+    m.load_synthetic(seed)
+    assert m.generate(prompt, n_new)[0] == want
+    assert m.generate(prompt, n_new)[0] == want      # barrier generation counter carries over between launches
+    m.close()
+    monkeypatch.setenv("GRETA_PERSISTENT_STEP", "0")
+    m = pkg.model.Model(cfg)
+    m.load_synthetic(seed)
+    assert m.generate(prompt, n_new)[0] == want
+    m.close()
+
+
 def test_forward_rejects_bad_ranges(pkg):
     m = pkg.model.Model(SMALL)
     m.load_synthetic(1)
