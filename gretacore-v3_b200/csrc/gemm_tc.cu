@@ -2,25 +2,30 @@
 //   C[M x N] = half(A[M x K]) * half(dequant(W[N x K]))^T, fp32 accumulation in TMEM.
 //
 // The weight side is the 128-row operand of the MMA and the tokens are its N
-// dimension ("swapped" roles): a CTA owns 128 weight rows and up to 256 tokens,
-// so each weight tile is dequantised once and its accumulator (128 lanes x TN
-// fp32 columns) lives in tensor memory for the whole K loop.
+// dimension ("swapped" roles): a CTA owns 128 weight rows and 128, 256 or 512
+// tokens, so each weight tile is dequantised once and its accumulator (128 lanes x
+// TN fp32 columns, up to all 512 columns of tensor memory) stays there for the
+// whole K loop.  A 512-token tile is two N=256 MMAs per K=16 step.
 //
-// Warp roles (192 threads):
-//   warp 0     producer: TMA loads of the activation tile (TN x 64 fp16, 128-byte
-//              swizzle) into a 4-stage ring, completion on an mbarrier;
+// Warp roles (320 threads):
+//   warp 0     producer: TMA loads of activation units (up to 256 tokens x 64 fp16,
+//              128-byte swizzle) into a ring, completion on an mbarrier per unit;
 //   warp 1     allocates TMEM, issues tcgen05.mma (one elected lane, 4 x K=16 per
-//              stage), commits each stage back to the producers, deallocates;
-//   warps 2-5  one thread per weight row: 128-bit loads of the quant payloads and
-//              scales (software-prefetched two stages ahead), in-register dequant to
-//              the exact fp16 value half((q - 8) * d), 128-bit stores into the
-//              swizzled K-major smem tile the tensor core reads; afterwards the
-//              epilogue: tcgen05.ld of the accumulator, conversion, stores to C.
+//              unit), commits each unit and each weight stage back to its producer,
+//              deallocates;
+//   warps 2-9  two threads per weight row, one 32-weight block each per stage:
+//              cp.async of the quant payload and scales into a raw ring several
+//              stages ahead of use, in-register dequant to the exact fp16 value
+//              half((q - 8) * d), 128-bit stores into the swizzled K-major smem tile
+//              the tensor core reads; afterwards the epilogue: tcgen05.ld of the
+//              accumulator, conversion, stores to C.
 // Every wait on an mbarrier is bounded: on a timeout the kernel raises a flag that
 // all roles poll, drains, frees its tensor memory and returns; the host reads the
 // flag with greta_cuda_gemm_status().
 #include <cuda.h>
 
+#include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 #include "greta_common.cuh"
@@ -30,10 +35,7 @@ using namespace greta;
 namespace {
 
 constexpr int BK = 64;          // K elements per stage (one 128-byte swizzle row of fp16)
-constexpr int TILE_N = 128;     // weight rows per CTA (the MMA's M)
-constexpr int STAGES = 4;
-constexpr int B_STAGE_BYTES = TILE_N * BK * 2;
-constexpr int NUM_THREADS = 192;
+constexpr int TILE_N = 128;     // weight rows per MMA (its M)
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // ~2 s at 2 GHz
 
 __device__ int g_gemm_error = 0;  // 0 ok; otherwise 100 * role + stage of the wait that gave up
@@ -61,9 +63,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  Returns false when the kernel is aborting (this wait timed out, or another role's did).
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int code) {
+// The common case, a barrier that has already completed, is one try_wait; the polling loop with its
+// clock reads is kept out of line so the issuing threads' instruction streams stay short.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code) {
   const long long t0 = clock64();
-  while (!mbar_try_wait(bar, parity)) {
+  for (;;) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
     if (*abort_flag) return false;
     if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
       *abort_flag = code;
@@ -71,7 +84,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
       return false;
     }
   }
-  return true;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(smem_u32(bar), parity, abort_flag, code);
 }
 __device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
@@ -89,13 +105,17 @@ __device__ __forceinline__ void tmem_relinquish() { asm volatile("tcgen05.relinq
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
 }
-// D[tmem] (+)= A[smem desc] * B[smem desc]^T, fp16 inputs, fp32 accumulate.
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+// D[tmem] (+)= A[smem desc] * B[smem desc]^T, fp16 inputs, fp32 accumulate.  The descriptors are passed as
+// their low words (start address and leading offset); the high word is the same for every tile.
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint32_t desc_a_lo, uint32_t desc_b_lo, uint32_t desc_hi, uint32_t idesc,
+                                         uint32_t accumulate) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}" ::"r"(tmem_d),
+      "r"(desc_a_lo), "r"(desc_b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 // Arrives on the mbarrier once every MMA issued so far by this thread has completed.
@@ -115,11 +135,12 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// Shared-memory matrix descriptor of a K-major tile with 128-byte rows and 128-byte swizzle:
-// 8-row groups 1024 bytes apart, descriptor version 1 (Blackwell), layout type 2 (SWIZZLE_128B).
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
-  return (uint64_t)((smem_addr >> 4) & 0x3FFF) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
+// Shared-memory matrix descriptor of a K-major tile with 128-byte rows and 128-byte swizzle: start address
+// and leading offset 1 in the low word; 8-row groups 1024 bytes apart, descriptor version 1 (Blackwell) and
+// layout type 2 (SWIZZLE_128B) in the high word.  Shared addresses are below 256 KB, so address / 16 fits
+// the 14-bit field and tiles are stepped by adding bytes / 16 to the low word.
+__device__ __forceinline__ uint32_t smem_desc_lo(uint32_t smem_addr) { return ((smem_addr >> 4) & 0x3FFFu) | (1u << 16); }
+constexpr uint32_t SMEM_DESC_HI_SW128 = (1024u >> 4) | (1u << 14) | (2u << 29);
 // Instruction descriptor: fp16 x fp16 -> fp32, both operands K-major, shape M x N.
 __host__ __device__ constexpr uint32_t instr_desc_f16(uint32_t M, uint32_t N) {
   return (1u << 4) | ((N >> 3) << 17) | ((M >> 4) << 24);
@@ -166,90 +187,129 @@ __device__ __forceinline__ void dq8_word(uint32_t w, uint32_t d2, uint32_t (&o)[
   o[1] = h2mul(h2sub(__byte_perm(t, 0x64646464u, 0x7362), C1152), d2);
 }
 
-template <int FMT>
-struct Raw {  // one thread's weights for one stage: 64 weights of its row
-  static constexpr int QV = (FMT == GRETA_FMT_Q4_0) ? 2 : 4;
-  uint4 q[QV];
-  uint32_t d;  // two fp16 scales
+// Tile shapes.  A CTA owns RT tiles of 128 weight rows and TN tokens, RT * TN <= 512 accumulator
+// columns of tensor memory.  An activation "unit" is (up to) 256 tokens x 64 K = 32 KB and feeds
+// 4 * RT MMAs, so with RT = 2 one unit carries twice the tensor-core time: a slot of the activation
+// ring is recycled through commit -> producer -> TMA -> issuer, about 2 us, and the ring has to hold
+// that much tensor-core time for the MMAs to run back to back.
+template <int FMT, int TN, int RT>
+struct Cfg {
+  static constexpr int ROWS = RT * TILE_N;
+  static constexpr int QV = (FMT == GRETA_FMT_Q4_0) ? 1 : 2;  // 16-byte payload pieces per 32-weight block
+  static constexpr int DEQ_THREADS = 2 * ROWS;                 // two threads per weight row: one block each per stage
+  static constexpr int THREADS = 64 + DEQ_THREADS;
+  static constexpr int RAW_SCALES = 2 * QV * ROWS * 16;        // raw stage: pieces [block][v][row], then one scale word per thread
+  static constexpr int RAW_STAGE = RAW_SCALES + 2 * ROWS * 4;
+  static constexpr int B_STAGE = ROWS * BK * 2;                // RT swizzled 128-row tiles back to back
+  static constexpr int UNIT_ROWS = TN < 256 ? TN : 256;
+  static constexpr int UPS = TN / UNIT_ROWS;  // units per stage
+  static constexpr int UNIT_BYTES = UNIT_ROWS * BK * 2;
+  static constexpr bool Q4 = FMT == GRETA_FMT_Q4_0;
+  static constexpr int AU = RT == 2 ? (TN == 256 ? (Q4 ? 4 : 3) : 6) : (TN == 128 ? 6 : (TN == 512 && Q4 ? 5 : 4));
+  static constexpr int BS = RT == 2 ? (TN == 256 || !Q4 ? 2 : 3) : ((TN == 256 && !Q4) || TN == 512 ? 3 : 4);
+  static constexpr int RS = RT == 2 ? 3 : (TN == 512 ? 3 : (TN == 256 ? (Q4 ? 6 : 4) : (Q4 ? 8 : 6)));
+  static constexpr int NBARS = 2 * AU + 2 * BS + 1;
+  static constexpr size_t SMEM = (size_t)AU * UNIT_BYTES + (size_t)BS * B_STAGE + (size_t)RS * RAW_STAGE + 1024 + 256;
+  static_assert(RT * TN <= 512, "accumulators exceed tensor memory");
+  static_assert(SMEM <= 232448, "tile configuration exceeds shared memory");
 };
 
-// Stage kt covers blocks 2kt and 2kt+1 of the row; when K is an odd number of blocks the last stage
-// has only the first one, and the missing half is made zero (the activations there are zero-filled
-// by TMA, but 0 * garbage must not produce a NaN).
-template <int FMT>
-__device__ __forceinline__ void load_raw(Raw<FMT> &r, const uint8_t *qs_row, const __half *d_row, uint32_t kt, uint32_t nb) {
-  constexpr int QV = Raw<FMT>::QV;
-  const uint8_t *p = qs_row + (size_t)kt * QV * 16;
-  const bool second = 2 * kt + 1 < nb;
-#pragma unroll
-  for (int v = 0; v < QV; ++v) r.q[v] = (v < QV / 2 || second) ? ld_stream(p + v * 16) : make_uint4(0, 0, 0, 0);
-  r.d = __ldg(reinterpret_cast<const uint32_t *>(d_row + 2 * kt));  // rows of the d plane are padded: always in bounds
-  if (!second) r.d &= 0xFFFFu;                                      // scale 0 for the absent block
+__device__ __forceinline__ void cp_async16(void *smem_dst, const void *gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void *smem_dst, const void *gsrc) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-// Dequantises the thread's 64 weights and writes its 128-byte row of the swizzled B tile.
-template <int FMT>
-__device__ __forceinline__ void dequant_store(const Raw<FMT> &r, uint8_t *row_base, int row_in_atom) {
-  uint4 chunk[8];  // chunk c = elements 8c .. 8c+7
-  const uint32_t d_lo = r.d & 0xFFFFu, d_hi = r.d >> 16;
-  const uint32_t d2[2] = {d_lo | (d_lo << 16), d_hi | (d_hi << 16)};
-  if (FMT == GRETA_FMT_Q4_0) {
+// Starts the copy of one thread's share of stage kt into the raw ring: block 2kt + hb of its row and the
+// 4-byte word holding both scales of the stage.  When K is an odd number of blocks the last stage has
+// only the first block; the thread of the absent one copies nothing and stores zeros.
+template <class C>
+__device__ __forceinline__ void raw_issue(uint8_t *stage, int row, int hb, const uint8_t *qs_row, const __half *d_row, uint32_t kt, uint32_t nb) {
+  if (2 * kt + hb >= nb) return;
+  const uint8_t *p = qs_row + ((size_t)2 * kt + hb) * C::QV * 16;
 #pragma unroll
-    for (int blk = 0; blk < 2; ++blk) {
-      const uint32_t w[4] = {r.q[blk].x, r.q[blk].y, r.q[blk].z, r.q[blk].w};
+  for (int v = 0; v < C::QV; ++v) cp_async16(stage + ((hb * C::QV + v) * C::ROWS + row) * 16, p + v * 16);
+  cp_async4(stage + C::RAW_SCALES + (hb * C::ROWS + row) * 4, d_row + 2 * kt);  // rows of the d plane are padded: always in bounds
+}
+
+// Dequantises the thread's block of one stage from the raw ring into four 16-byte chunks of fp16
+// (chunk c = elements 8c .. 8c+7 of the block).
+template <class C>
+__device__ __forceinline__ void dequant_block(const uint8_t *stage, int row, int hb, bool present, uint4 (&chunk)[4]) {
+  if (present) {
+    const uint32_t dw = *reinterpret_cast<const uint32_t *>(stage + C::RAW_SCALES + (hb * C::ROWS + row) * 4);
+    const uint32_t dh = hb ? (dw >> 16) : (dw & 0xFFFFu);
+    const uint32_t d2 = dh | (dh << 16);
+    if (C::Q4) {
+      const uint4 q = *reinterpret_cast<const uint4 *>(stage + (hb * C::ROWS + row) * 16);
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
       uint32_t lo[4][2], hi[4][2];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) dq4_word(w[i], d2[blk], lo[i], hi[i]);
-      chunk[4 * blk + 0] = make_uint4(lo[0][0], lo[0][1], lo[1][0], lo[1][1]);
-      chunk[4 * blk + 1] = make_uint4(lo[2][0], lo[2][1], lo[3][0], lo[3][1]);
-      chunk[4 * blk + 2] = make_uint4(hi[0][0], hi[0][1], hi[1][0], hi[1][1]);
-      chunk[4 * blk + 3] = make_uint4(hi[2][0], hi[2][1], hi[3][0], hi[3][1]);
+      for (int i = 0; i < 4; ++i) dq4_word(w[i], d2, lo[i], hi[i]);
+      chunk[0] = make_uint4(lo[0][0], lo[0][1], lo[1][0], lo[1][1]);
+      chunk[1] = make_uint4(lo[2][0], lo[2][1], lo[3][0], lo[3][1]);
+      chunk[2] = make_uint4(hi[0][0], hi[0][1], hi[1][0], hi[1][1]);
+      chunk[3] = make_uint4(hi[2][0], hi[2][1], hi[3][0], hi[3][1]);
+    } else {
+#pragma unroll
+      for (int v = 0; v < 2; ++v) {  // payload v: 16 int8 = elements 16v .. 16v+15 of the block
+        const uint4 q = *reinterpret_cast<const uint4 *>(stage + ((hb * C::QV + v) * C::ROWS + row) * 16);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+        uint32_t o[4][2];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) dq8_word(w[i], d2, o[i]);
+        chunk[2 * v + 0] = make_uint4(o[0][0], o[0][1], o[1][0], o[1][1]);
+        chunk[2 * v + 1] = make_uint4(o[2][0], o[2][1], o[3][0], o[3][1]);
+      }
     }
   } else {
 #pragma unroll
-    for (int v = 0; v < 4; ++v) {  // payload v: 16 int8 = elements 16v .. 16v+15 (block v / 2)
-      const uint32_t w[4] = {r.q[v].x, r.q[v].y, r.q[v].z, r.q[v].w};
-      uint32_t o[4][2];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) dq8_word(w[i], d2[v >> 1], o[i]);
-      chunk[2 * v + 0] = make_uint4(o[0][0], o[0][1], o[1][0], o[1][1]);
-      chunk[2 * v + 1] = make_uint4(o[2][0], o[2][1], o[3][0], o[3][1]);
-    }
+    for (int c = 0; c < 4; ++c) chunk[c] = make_uint4(0, 0, 0, 0);  // the activations there are zero-filled by TMA; 0 * 0, never 0 * garbage
   }
-#pragma unroll
-  for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4 *>(row_base + ((c ^ row_in_atom) << 4)) = chunk[c];
 }
 
-template <int FMT, int TN, bool OUT_F16>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+template <int FMT, int TN, int RT, bool OUT_F16>
+__global__ void __launch_bounds__(Cfg<FMT, TN, RT>::THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t *__restrict__ qs, const __half *__restrict__ dsc, void *__restrict__ Cout,
                uint32_t M, uint32_t N, uint32_t K) {
-  constexpr int A_STAGE_BYTES = TN * BK * 2;
+  using C = Cfg<FMT, TN, RT>;
+  constexpr int AU = C::AU, BS = C::BS, RS = C::RS, UPS = C::UPS, UNIT_BYTES = C::UNIT_BYTES, UNIT_ROWS = C::UNIT_ROWS;
+  constexpr int RAW_STAGE = C::RAW_STAGE, B_STAGE = C::B_STAGE, ROWS = C::ROWS, COLS = RT * TN;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);  // swizzle atoms need 1024-byte alignment
-  uint8_t *a_tiles = smem;                                  // [STAGES][TN][128 B]   tokens   (MMA operand B)
-  uint8_t *b_tiles = smem + STAGES * A_STAGE_BYTES;         // [STAGES][128][128 B]  weights  (MMA operand A)
-  uint64_t *bars = reinterpret_cast<uint64_t *>(b_tiles + STAGES * B_STAGE_BYTES);
-  uint64_t *a_full = bars, *b_full = bars + STAGES, *empty = bars + 2 * STAGES, *acc_full = bars + 3 * STAGES;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * STAGES + 1);
+  uint8_t *a_units = smem;                       // [AU][UNIT_ROWS][128 B]  tokens   (MMA operand B)
+  uint8_t *b_tiles = a_units + AU * UNIT_BYTES;  // [BS][RT][128][128 B]    weights  (MMA operand A)
+  uint8_t *raw = b_tiles + BS * B_STAGE;         // [RS] raw quantised stages
+  uint64_t *bars = reinterpret_cast<uint64_t *>(raw + RS * RAW_STAGE);
+  uint64_t *a_full = bars, *a_empty = bars + AU, *b_full = bars + 2 * AU, *b_empty = bars + 2 * AU + BS, *acc_full = bars + 2 * AU + 2 * BS;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + C::NBARS);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t n0 = blockIdx.x * TILE_N, m0 = blockIdx.y * TN;
+  const uint32_t n0 = blockIdx.x * ROWS, m0 = blockIdx.y * TN;
   const uint32_t KT = (K + BK - 1) / BK, nb = K / 32;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < AU; ++s) {
       mbar_init(&a_full[s], 1);
-      mbar_init(&b_full[s], 4);
-      mbar_init(&empty[s], 1);
+      mbar_init(&a_empty[s], 1);
+    }
+    for (int s = 0; s < BS; ++s) {
+      mbar_init(&b_full[s], C::DEQ_THREADS / 32);
+      mbar_init(&b_empty[s], 1);
     }
     mbar_init(acc_full, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, TN);
+    tmem_alloc(tmem_slot, COLS);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -260,18 +320,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t *__rest
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      uint32_t issued = 0;
+      uint32_t issued = 0, u = 0, ph = 1;
       for (uint32_t kt = 0; kt < KT; ++kt) {
-        const uint32_t s = kt % STAGES, ph = (kt / STAGES) & 1;
-        if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, 100 + s)) break;
-        mbar_arrive_expect_tx(&a_full[s], A_STAGE_BYTES);
-        tma_load_2d(a_tiles + s * A_STAGE_BYTES, &tmap_a, (int)(kt * BK), (int)m0, &a_full[s]);
-        ++issued;
+        bool ok = true;
+#pragma unroll
+        for (int h = 0; h < UPS; ++h) {
+          ok = mbar_wait(&a_empty[u], ph, abort_flag, 100 + u);
+          if (!ok) break;
+          mbar_arrive_expect_tx(&a_full[u], UNIT_BYTES);
+          tma_load_2d(a_units + u * UNIT_BYTES, &tmap_a, (int)(kt * BK), (int)(m0 + h * UNIT_ROWS), &a_full[u]);
+          ++issued;
+          if (++u == AU) {
+            u = 0;
+            ph ^= 1;
+          }
+        }
+        if (!ok) break;
       }
       if (*abort_flag) {  // give the copies still in flight a bounded chance to land before the CTA exits
-        for (uint32_t j = issued > (uint32_t)STAGES ? issued - STAGES : 0; j < issued; ++j) {
+        for (uint32_t j = issued > (uint32_t)AU ? issued - AU : 0; j < issued; ++j) {
           const long long t0 = clock64();
-          while (!mbar_try_wait(&a_full[j % STAGES], (j / STAGES) & 1) && clock64() - t0 < 20000000ll) {
+          while (!mbar_try_wait(&a_full[j % AU], (j / AU) & 1) && clock64() - t0 < 20000000ll) {
           }
         }
       }
@@ -279,62 +348,103 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t *__rest
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc_f16(TILE_N, TN);
+      constexpr uint32_t idesc = instr_desc_f16(TILE_N, UNIT_ROWS);
+      const uint32_t w_lo0 = smem_desc_lo(smem_u32(b_tiles)), a_lo0 = smem_desc_lo(smem_u32(a_units));
       bool ok = true;
+      uint32_t s = 0, sph = 0, u = 0, uph = 0, acc = 0;
       for (uint32_t kt = 0; kt < KT && ok; ++kt) {
-        const uint32_t s = kt % STAGES, ph = (kt / STAGES) & 1;
-        ok = mbar_wait(&a_full[s], ph, abort_flag, 200 + s) && mbar_wait(&b_full[s], ph, abort_flag, 300 + s);
+        ok = mbar_wait(&b_full[s], sph, abort_flag, 300 + s);
         if (!ok) break;
-        tc_fence_after();
-        const uint32_t wa = smem_u32(b_tiles + s * B_STAGE_BYTES), ta = smem_u32(a_tiles + s * A_STAGE_BYTES);
+        const uint32_t w_lo = w_lo0 + s * (B_STAGE >> 4);
 #pragma unroll
-        for (int k16 = 0; k16 < BK / 16; ++k16)
-          umma_f16(tmem_base, smem_desc_sw128(wa + k16 * 32), smem_desc_sw128(ta + k16 * 32), idesc, (kt | (uint32_t)k16) != 0);
-        umma_commit(&empty[s]);  // stage s may be refilled once these MMAs have read it
+        for (int h = 0; h < UPS; ++h) {
+          ok = mbar_wait(&a_full[u], uph, abort_flag, 200 + u);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_lo = a_lo0 + u * (UNIT_BYTES >> 4);
+#pragma unroll
+          for (int k16 = 0; k16 < BK / 16; ++k16) {  // accumulator (r, h) sits at column (r * UPS + h) * UNIT_ROWS
+#pragma unroll
+            for (int r = 0; r < RT; ++r)
+              umma_f16(tmem_base + (r * UPS + h) * UNIT_ROWS, w_lo + r * ((TILE_N * BK * 2) >> 4) + k16 * 2, a_lo + k16 * 2, SMEM_DESC_HI_SW128, idesc,
+                       k16 == 0 ? acc : 1u);
+          }
+          umma_commit(&a_empty[u]);  // the unit may be refilled once these MMAs have read it
+          if (++u == AU) {
+            u = 0;
+            uph ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&b_empty[s]);
+        acc = 1;
+        if (++s == BS) {
+          s = 0;
+          sph ^= 1;
+        }
       }
       if (ok) umma_commit(acc_full);
     }
   } else {
     // ---------------- dequant warps, then epilogue ----------------
-    const int t = threadIdx.x - 64;  // weight row inside the tile, 0..127
-    const uint32_t n = min(n0 + (uint32_t)t, N - 1);
-    const uint8_t *qs_row = qs + (size_t)n * nb * (FMT == GRETA_FMT_Q4_0 ? 16 : 32);
+    const int t = threadIdx.x - 64;
+    const int row = t % ROWS, hb = t / ROWS;  // weight row inside the CTA's rows, and which block of the stage
+    const uint32_t n = min(n0 + (uint32_t)row, N - 1);
+    const uint8_t *qs_row = qs + (size_t)n * nb * (C::Q4 ? 16 : 32);
     const __half *d_row = dsc + (size_t)n * d_row_stride(nb);
-    Raw<FMT> r0, r1, r2;
-    load_raw<FMT>(r0, qs_row, d_row, 0, nb);
-    if (KT > 1) load_raw<FMT>(r1, qs_row, d_row, 1, nb);
+#pragma unroll
+    for (int j = 0; j < RS - 1; ++j) {
+      if ((uint32_t)j < KT) raw_issue<C>(raw + j * RAW_STAGE, row, hb, qs_row, d_row, j, nb);
+      cp_async_commit();
+    }
+    // this thread's half (64 bytes) of its row in the swizzled tile of its 128-row group
+    const uint32_t row_off = (row >> 7) * (TILE_N * BK * 2) + (row & 127) * 128;
     bool ok = true;
+    uint32_t s = 0, sph = 1, rs_load = RS - 1, rs_use = 0;
     for (uint32_t kt = 0; kt < KT; ++kt) {
-      const uint32_t s = kt % STAGES, ph = (kt / STAGES) & 1;
-      if (kt + 2 < KT) load_raw<FMT>(r2, qs_row, d_row, kt + 2, nb);
-      ok = mbar_wait(&empty[s], ph ^ 1, abort_flag, 400 + s);
+      if (kt + RS - 1 < KT) raw_issue<C>(raw + rs_load * RAW_STAGE, row, hb, qs_row, d_row, kt + RS - 1, nb);
+      cp_async_commit();
+      cp_async_wait<RS - 1>();  // this thread's share of stage kt has landed (it reads only what it copied)
+      uint4 chunk[4];
+      dequant_block<C>(raw + rs_use * RAW_STAGE, row, hb, 2 * kt + hb < nb, chunk);  // the math does not wait for the slot
+      ok = mbar_wait(&b_empty[s], sph, abort_flag, 400 + s);
       if (!ok) break;
-      dequant_store<FMT>(r0, b_tiles + s * B_STAGE_BYTES + t * 128, t & 7);
+      uint8_t *row_base = b_tiles + s * B_STAGE + row_off;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4 *>(row_base + (((4 * hb + c) ^ (row & 7)) << 4)) = chunk[c];
       fence_proxy_async();  // make the generic-proxy stores visible to the tensor core's reads
       __syncwarp();
       if (lane == 0) mbar_arrive(&b_full[s]);
-      r0 = r1;
-      r1 = r2;
+      if (++s == BS) {
+        s = 0;
+        sph ^= 1;
+      }
+      if (++rs_load == RS) rs_load = 0;
+      if (++rs_use == RS) rs_use = 0;
     }
-    // epilogue: accumulator rows = weight rows (TMEM lanes), columns = tokens
+    cp_async_wait<0>();
+    // epilogue: accumulator rows = weight rows (TMEM lanes), columns = tokens.  A warp may only touch TMEM
+    // lanes 32 * (warp % 4) .. +31; the 2 * RT warps of a lane quadrant split row tiles and token halves.
     if (ok) ok = mbar_wait(acc_full, 0, abort_flag, 500);
     if (ok) {
       tc_fence_after();
-      const int quad = warp & 3;  // a warp may only touch TMEM lanes 32 * (warp % 4) .. +31
-      const uint32_t row = n0 + quad * 32 + lane;
-      for (int c = 0; c < TN; c += 32) {
+      const int quad = warp & 3, share = (warp - 2) >> 2;
+      const int r = share % RT, half = share / RT;
+      const uint32_t orow = n0 + r * TILE_N + quad * 32 + lane;
+      for (int c = half * (TN / 2); c < (half + 1) * (TN / 2); c += 32) {
+        if (m0 + c >= M) break;
         uint32_t v[32];
-        tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + c, v);
+        tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + r * TN + c, v);
         tmem_ld_wait();
-        if (row < N) {
+        if (orow < N) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const uint32_t m = m0 + c + j;
             if (m < M) {
               if (OUT_F16)
-                reinterpret_cast<__half *>(Cout)[(size_t)m * N + row] = __float2half_rn(__uint_as_float(v[j]));
+                reinterpret_cast<__half *>(Cout)[(size_t)m * N + orow] = __float2half_rn(__uint_as_float(v[j]));
               else
-                reinterpret_cast<float *>(Cout)[(size_t)m * N + row] = __uint_as_float(v[j]);
+                reinterpret_cast<float *>(Cout)[(size_t)m * N + orow] = __uint_as_float(v[j]);
             }
           }
         }
@@ -345,7 +455,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t *__rest
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, TN);
+    tmem_dealloc(tmem_base, COLS);
   }
 }
 
@@ -366,26 +476,56 @@ EncodeTiledFn encode_tiled() {
   return fn;
 }
 
-template <int FMT, int TN, bool OUT_F16>
+template <int FMT, int TN, int RT, bool OUT_F16>
 int launch_tc(cudaStream_t stream, const CUtensorMap &map, const void *qs, const void *d, void *C, uint32_t M, uint32_t N, uint32_t K) {
-  const size_t smem = (size_t)STAGES * (TN * BK * 2 + B_STAGE_BYTES) + 1024 + 256;
+  using Cf = Cfg<FMT, TN, RT>;
   static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    GRETA_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<FMT, TN, OUT_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    GRETA_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_kernel<FMT, TN, RT, OUT_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cf::SMEM));
     attr_set[dev] = true;
   }
-  dim3 grid((N + TILE_N - 1) / TILE_N, (M + TN - 1) / TN);
-  gemm_tc_kernel<FMT, TN, OUT_F16><<<grid, NUM_THREADS, smem, stream>>>(map, (const uint8_t *)qs, (const __half *)d, C, M, N, K);
+  dim3 grid((N + Cf::ROWS - 1) / Cf::ROWS, (M + TN - 1) / TN);
+  gemm_tc_kernel<FMT, TN, RT, OUT_F16><<<grid, Cf::THREADS, Cf::SMEM, stream>>>(map, (const uint8_t *)qs, (const __half *)d, C, M, N, K);
   return launched("gemm_tc_kernel");
 }
 
-template <int FMT>
-int dispatch_tc(cudaStream_t stream, const CUtensorMap &m128, const CUtensorMap &m256, bool wide, bool out_f16, const void *qs, const void *d,
-                void *C, uint32_t M, uint32_t N, uint32_t K) {
-  if (wide) return out_f16 ? launch_tc<FMT, 256, true>(stream, m256, qs, d, C, M, N, K) : launch_tc<FMT, 256, false>(stream, m256, qs, d, C, M, N, K);
-  return out_f16 ? launch_tc<FMT, 128, true>(stream, m128, qs, d, C, M, N, K) : launch_tc<FMT, 128, false>(stream, m128, qs, d, C, M, N, K);
+template <int FMT, bool OUT_F16>
+int dispatch_tile(cudaStream_t stream, const CUtensorMap &map, int tn, int rt, const void *qs, const void *d, void *C, uint32_t M, uint32_t N,
+                  uint32_t K) {
+  if (rt == 2) {
+    if (tn == 256) return launch_tc<FMT, 256, 2, OUT_F16>(stream, map, qs, d, C, M, N, K);
+    return launch_tc<FMT, 128, 2, OUT_F16>(stream, map, qs, d, C, M, N, K);
+  }
+  if (tn == 512) return launch_tc<FMT, 512, 1, OUT_F16>(stream, map, qs, d, C, M, N, K);
+  if (tn == 256) return launch_tc<FMT, 256, 1, OUT_F16>(stream, map, qs, d, C, M, N, K);
+  return launch_tc<FMT, 128, 1, OUT_F16>(stream, map, qs, d, C, M, N, K);
+}
+
+// Tile shape (tokens x 128-row tiles per CTA): the widest token tile that still leaves most SMs a CTA.
+// With one MMA row tile per CTA the token operand is written to shared memory once and read once per
+// stage, and together with the weight tile that traffic (about 185 KB per 64-K stage at 512 tokens), not
+// the tensor core, sets the pace; the two-row-tile shapes move no less of it and have a shallower
+// weight ring, so they are never picked here.  GRETA_GEMM_TILE=<tokens>x<row tiles> forces one
+// (512x1, 256x1, 128x1, 256x2, 128x2).
+void pick_tile(uint32_t M, uint32_t N, int *tn, int *rt) {
+  *rt = 1;
+  if (const char *e = getenv("GRETA_GEMM_TILE")) {
+    int a = 0, b = 0;
+    if (sscanf(e, "%dx%d", &a, &b) == 2 && (a == 128 || a == 256 || a == 512) && (b == 1 || b == 2) && a * b <= 512) {
+      *tn = a;
+      *rt = b;
+      return;
+    }
+  }
+  const uint32_t row_tiles = (N + TILE_N - 1) / TILE_N;
+  const int widths[3] = {512, 256, 128};
+  for (int w : widths) {
+    *tn = w;
+    if (w > 128 && M <= (uint32_t)w / 2) continue;  // would be mostly padding
+    if (row_tiles * ((M + w - 1) / w) >= 80) return;
+  }
 }
 
 }  // namespace
@@ -419,11 +559,12 @@ int greta_cuda_gemm(greta_stream_t stream, int fmt, const void *A, int a_is_f16,
     set_error("gemm: cuTensorMapEncodeTiled is not available from this driver");
     return GRETA_ERR_NOT_IMPLEMENTED;
   }
-  const bool wide = M > 128;
+  int tn = 128, rt = 1;
+  pick_tile(M, N, &tn, &rt);
   CUtensorMap map;
   const cuuint64_t dims[2] = {K, M};
   const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-  const cuuint32_t box[2] = {BK, wide ? 256u : 128u};
+  const cuuint32_t box[2] = {BK, tn >= 256 ? 256u : 128u};
   const cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(a16), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -431,8 +572,9 @@ int greta_cuda_gemm(greta_stream_t stream, int fmt, const void *A, int a_is_f16,
     set_error("gemm: cuTensorMapEncodeTiled failed with code %d", (int)r);
     return GRETA_ERR_INVALID_ARGS;
   }
-  if (fmt == GRETA_FMT_Q4_0) return dispatch_tc<GRETA_FMT_Q4_0>(s, map, map, wide, c_is_f16 != 0, qs, d, Cout, M, N, K);
-  return dispatch_tc<GRETA_FMT_Q8_0>(s, map, map, wide, c_is_f16 != 0, qs, d, Cout, M, N, K);
+  if (fmt == GRETA_FMT_Q4_0)
+    return c_is_f16 ? dispatch_tile<GRETA_FMT_Q4_0, true>(s, map, tn, rt, qs, d, Cout, M, N, K) : dispatch_tile<GRETA_FMT_Q4_0, false>(s, map, tn, rt, qs, d, Cout, M, N, K);
+  return c_is_f16 ? dispatch_tile<GRETA_FMT_Q8_0, true>(s, map, tn, rt, qs, d, Cout, M, N, K) : dispatch_tile<GRETA_FMT_Q8_0, false>(s, map, tn, rt, qs, d, Cout, M, N, K);
 }
 
 }  // extern "C"

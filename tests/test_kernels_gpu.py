@@ -410,6 +410,28 @@ def test_gemm_matches_oracle(g, name, M, N, K, a_f16, c_f16):
     assert err < TOL and err < bar, err
 
 
+@pytest.mark.parametrize("tile", ["128x1", "256x1", "512x1", "128x2", "256x2"])
+@pytest.mark.parametrize("name,M,N,K", [("q4_0", 600, 300, 1376), ("q8_0", 515, 260, 2048), ("q4_0", 100, 128, 4096)])
+def test_gemm_every_tile_shape(g, monkeypatch, name, M, N, K, tile):
+    """Every tile shape (tokens x 128-row tiles per CTA, normally chosen from the problem size) gives the same
+    product: ragged last token tile, ragged last row tile, odd number of blocks in K, more K stages than any ring is deep."""
+    monkeypatch.setenv("GRETA_GEMM_TILE", tile)
+    ofmt, gfmt = FMTS[name]
+    rng = np.random.default_rng(900 + M + len(tile))
+    blk = make_blocks(rng, ofmt, N, K)
+    a16 = rng.normal(0, 1, (M, K)).astype(np.float16).view(np.uint16)
+    w = g.Weight(blk, gfmt, N, K)
+    c = g.DeviceBuffer(M * N * 4)
+    _KEEP.append(c)
+    c.fill(0xFF)
+    g.check(g.cuda().greta_cuda_gemm(None, gfmt, _dev(g, a16).ptr, 1, w.qs.ptr, w.d.ptr, c.ptr, 0, M, N, K, None))
+    g.check(g.cuda().greta_cuda_device_synchronize())
+    assert _gemm_status(g) == 0
+    got = c.download(np.float32).reshape(M, N)
+    err = max_abs_rel(got, O.gemm(a16, blk, ofmt, N, K))
+    assert np.isfinite(got).all() and err < 1e-4, err
+
+
 def test_gemm_rejects_what_it_cannot_do(g):
     lib = g.cuda()
     buf = g.DeviceBuffer(1 << 16)
