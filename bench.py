@@ -165,6 +165,8 @@ def cpu_decode_layer_seconds(cfg, n_layers, reps):
     """Times the CPU port on `n_layers` decoder layers of the 7B shape at batch 1 (fp32 accumulation, OpenMP over
     output rows) and returns seconds per layer.  Weights are random GGUF Q4_0 blocks (values do not affect time)."""
     from oracle import oracle as O
+    if os.environ.get("TORCHELASTIC_RUN_ID"):        # torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU leg runs
+        O.set_num_threads(os.cpu_count() or 1)       # on rank 0 alone and may use the whole host
     rng = np.random.default_rng(0)
     D, F = cfg["dim"], cfg["hidden_dim"]
     shapes = [(D, D)] * 4 + [(F, D), (F, D), (D, F)]
@@ -445,7 +447,7 @@ def main():
         "step_hbm": {"bytes_per_step": step_bytes, "achieved_gbs": step_bytes / (ms / args.steps) / 1e6,
                      "frac_of_peak": step_bytes / (ms / args.steps) / 1e6 / peak},
     }
-    if not args.no_cpu_baseline:
+    if not args.no_cpu_baseline and tp == 1:                 # reported at N=1 only
         out["cpu_baseline"] = cpu_baseline(cfg)
     print(json.dumps(out))
 

@@ -11,9 +11,11 @@
 // scratch buffer: every CTA publishes its partial result, bumps a per-head
 // counter, and the CTA that sees the last ticket does the merge - no CTA ever
 // waits on another.
+#include <cooperative_groups.h>
 #include <math.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 
 #include "attention_device.cuh"
@@ -28,6 +30,55 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_kernel(const AttnParams p) {
   pdl_launch_dependents();
   pdl_wait();  // q, the position and the newest cache row come from the previous kernel
   attn_body<KV, DPL, ATT_WARPS, false>(p, blockIdx.x, blockIdx.y, blockIdx.z);
+}
+
+// The same work with the splits of one head in one thread-block cluster: every CTA leaves its partial
+// result in its own shared memory, the cluster meets at a hardware barrier and CTA 0 reads the others'
+// results through distributed shared memory.  No scratch, no fences, no atomics on the critical path.
+constexpr int CL_SPLITS = 8;
+constexpr int CL_WARPS = 8;
+
+template <typename KV, int DPL>
+__global__ void __launch_bounds__(CL_WARPS * 32) attn_cluster_kernel(const AttnParams p) {
+  namespace cg = cooperative_groups;
+  constexpr int Dh = DPL * 8;
+  __shared__ float res[Dh + 2];  // running maximum, normaliser, unnormalised output of this CTA's keys
+  cg::cluster_group cluster = cg::this_cluster();
+  pdl_launch_dependents();
+  pdl_wait();  // q, the position and the newest cache row come from the previous kernel
+  const uint32_t split = cluster.block_rank(), head = blockIdx.y, qi = blockIdx.z;
+  const uint32_t L = (p.d_pos ? __ldcg(p.d_pos) + 1 : p.len0) + qi;
+  const uint32_t chunk = (L + CL_SPLITS - 1) / CL_SPLITS;
+  const uint32_t k0 = split * chunk, k1 = min(L, k0 + chunk);
+  const int tid = threadIdx.x;
+  float fm, fl, fo;
+  attn_partial<KV, DPL, CL_WARPS, false>(p, min(k0, k1), k1, head, qi, fm, fl, fo);
+  if (tid < Dh) res[2 + tid] = fo;
+  if (tid == 0) {
+    res[0] = fm;
+    res[1] = fl;
+  }
+  cluster.sync();
+  if (split == 0 && tid < Dh) {
+    float rm[CL_SPLITS], rl[CL_SPLITS], ro[CL_SPLITS], gm = -INFINITY;
+#pragma unroll
+    for (int r = 0; r < CL_SPLITS; ++r) {
+      const float *rp = cluster.map_shared_rank(res, r);
+      rm[r] = rp[0];
+      rl[r] = rp[1];
+      ro[r] = rp[2 + tid];
+      gm = fmaxf(gm, rm[r]);
+    }
+    float gl = 0.f, go = 0.f;
+#pragma unroll
+    for (int r = 0; r < CL_SPLITS; ++r) {  // fixed order: the result does not depend on which CTA finished first
+      const float c = (rm[r] == -INFINITY) ? 0.f : expf(rm[r] - gm);
+      gl += rl[r] * c;
+      go += ro[r] * c;
+    }
+    p.o[((size_t)qi * p.H + head) * Dh + tid] = go / gl;
+  }
+  cluster.sync();  // a CTA's shared memory must outlive the reads of CTA 0
 }
 
 __global__ void rope_kernel(float *x, uint32_t S, uint32_t H, uint32_t Dh, float base, uint32_t pos_offset,
@@ -75,6 +126,26 @@ int launch_attn(cudaStream_t stream, AttnParams p, uint32_t nq, uint32_t Dh) {
 }
 
 template <typename KV>
+int launch_attn_cluster(cudaStream_t stream, AttnParams p, uint32_t Dh) {
+  dim3 grid(CL_SPLITS, p.H, 1);
+  if (Dh == 128)
+    GRETA_CUDA_TRY(launch_pdl_cluster(attn_cluster_kernel<KV, 16>, grid, dim3(CL_WARPS * 32), CL_SPLITS, 0, stream, p));
+  else if (Dh == 64)
+    GRETA_CUDA_TRY(launch_pdl_cluster(attn_cluster_kernel<KV, 8>, grid, dim3(CL_WARPS * 32), CL_SPLITS, 0, stream, p));
+  else {
+    set_error("attention: head_dim=%u is not supported (64 or 128)", Dh);
+    return GRETA_ERR_NOT_IMPLEMENTED;
+  }
+  return launched("attn_cluster_kernel");
+}
+
+// GRETA_ATTN_CLUSTER=0 keeps the splits on the scratch-buffer path.
+bool cluster_path_enabled() {
+  const char *e = getenv("GRETA_ATTN_CLUSTER");
+  return !(e && e[0] == '0');
+}
+
+template <typename KV>
 int attn_decode_impl(greta_stream_t stream, const float *q, const void *kc, const void *vc, float *o,
                      const uint32_t *d_pos, uint32_t seq_len, uint32_t H, uint32_t Hkv, uint32_t Dh, uint32_t max_seq,
                      float scale, void *scratch, size_t scratch_bytes) {
@@ -94,6 +165,7 @@ int attn_decode_impl(greta_stream_t stream, const float *q, const void *kc, cons
                   "attn_decode: scratch of %zu bytes needed, %zu given", greta_cuda_attn_decode_scratch_bytes(H, Dh), scratch_bytes);
     p.counters = reinterpret_cast<uint32_t *>(scratch);
     p.partial = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(scratch) + counters_bytes(H));
+    if (cluster_path_enabled()) return launch_attn_cluster<KV>((cudaStream_t)stream, p, Dh);
   }
   return launch_attn<KV>((cudaStream_t)stream, p, 1, Dh);
 }

@@ -63,22 +63,21 @@ __device__ __forceinline__ void merge(float &m, float &l, float (&o)[DPL], float
   m = mn;
 }
 
-// One (query qi, head, split) work item, executed by the NW warps of the calling CTA (all of them must call).
-// CG: read K/V through L2 only (needed when the newest cache row was written earlier in the same launch).
+// Online-softmax attention of one query head over keys [k0, k1), by the NW warps of the calling CTA (all of
+// them must call).  On return thread tid < Dh holds, for output dim tid, the CTA's running maximum, normaliser
+// and unnormalised output.  CG: read K/V through L2 only (needed when the newest cache row was written
+// earlier in the same launch).
 template <typename KV, int DPL, int NW, bool CG>
-__device__ void attn_body(const AttnParams &p, const uint32_t split, const uint32_t head, const uint32_t qi) {
+__device__ __forceinline__ void attn_partial(const AttnParams &p, const uint32_t k0, const uint32_t k1, const uint32_t head, const uint32_t qi,
+                                             float &fm, float &fl, float &fo) {
   constexpr int ATT_WARPS = NW;
   constexpr int Dh = DPL * 8;
   __shared__ float sm_m[ATT_WARPS], sm_l[ATT_WARPS];
   __shared__ float sm_o[ATT_WARPS][Dh];
-  __shared__ uint32_t sm_last;
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane & 7, grp = lane >> 3;  // 8 lanes per key, 4 keys per warp step
-  const uint32_t L = (p.d_pos ? __ldcg(p.d_pos) + 1 : p.len0) + qi;
   const uint32_t kvh = head / (p.H / p.Hkv);
-  const uint32_t chunk = (L + p.splits - 1) / p.splits;
-  const uint32_t k0 = split * chunk, k1 = min(L, k0 + chunk);
 
   const KV *kbase = reinterpret_cast<const KV *>(p.kc) + (size_t)kvh * p.max_seq * Dh + sub * DPL;
   const KV *vbase = reinterpret_cast<const KV *>(p.vc) + (size_t)kvh * p.max_seq * Dh + sub * DPL;
@@ -151,7 +150,7 @@ __device__ void attn_body(const AttnParams &p, const uint32_t split, const uint3
   }
   __syncthreads();
   const int tid = threadIdx.x;
-  float fm = -INFINITY, fl = 0.f, fo = 0.f;  // thread tid < Dh owns output dim tid
+  fm = -INFINITY, fl = 0.f, fo = 0.f;  // thread tid < Dh owns output dim tid
   if (tid < Dh) {
 #pragma unroll
     for (int w = 0; w < ATT_WARPS; ++w) fm = fmaxf(fm, sm_m[w]);
@@ -162,6 +161,20 @@ __device__ void attn_body(const AttnParams &p, const uint32_t split, const uint3
       fo += sm_o[w][tid] * c;
     }
   }
+}
+
+// One (query qi, head, split) work item: the CTA's share of the keys, then the merge of the splits through
+// the scratch buffer (every CTA publishes its partial result and takes a ticket; the last one merges).
+template <typename KV, int DPL, int NW, bool CG>
+__device__ void attn_body(const AttnParams &p, const uint32_t split, const uint32_t head, const uint32_t qi) {
+  constexpr int Dh = DPL * 8;
+  __shared__ uint32_t sm_last;
+  const uint32_t L = (p.d_pos ? __ldcg(p.d_pos) + 1 : p.len0) + qi;
+  const uint32_t chunk = (L + p.splits - 1) / p.splits;
+  const uint32_t k0 = split * chunk, k1 = min(L, k0 + chunk);
+  const int tid = threadIdx.x;
+  float fm, fl, fo;
+  attn_partial<KV, DPL, NW, CG>(p, k0, k1, head, qi, fm, fl, fo);
   float *out = p.o + ((size_t)qi * p.H + head) * Dh;
   if (p.splits == 1) {
     if (tid < Dh) out[tid] = fo / fl;

@@ -492,69 +492,93 @@ __device__ __forceinline__ void quantize_store(const float (&v)[4], uint32_t *xq
   }
 }
 
+// The four values of byte slots 4j..4j+3 of block b.  For Q4_0 and the int8 formats they are four
+// consecutive activations: one 128-bit load.
+template <int FMT>
+__device__ __forceinline__ void load_slot_values(const float *xf, const __half *xh, const float *gamma, uint32_t b, int j, float (&v)[4],
+                                                 float (&gm)[4]) {
+  if (FMT != GRETA_FMT_REF_INT4) {
+    const uint32_t idx = b * 32 + slot_element<FMT>(4 * j);
+    if (xf) {
+      const float4 t = __ldcg(reinterpret_cast<const float4 *>(xf + idx));  // bypass L1: another SM may have just written x
+      v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    } else {
+      const uint2 t = __ldcg(reinterpret_cast<const uint2 *>(xh + idx));
+      const float2 a = h2_to_f2(t.x), c = h2_to_f2(t.y);
+      v[0] = a.x; v[1] = a.y; v[2] = c.x; v[3] = c.y;
+    }
+    if (gamma) {
+      const float4 t = __ldg(reinterpret_cast<const float4 *>(gamma + idx));
+      gm[0] = t.x; gm[1] = t.y; gm[2] = t.z; gm[3] = t.w;
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint32_t idx = b * 32 + slot_element<FMT>(4 * j + k);
+      v[k] = xf ? __ldcg(xf + idx) : __half2float(__ldcg(xh + idx));
+      if (gamma) gm[k] = gamma[idx];
+    }
+  }
+}
+
 // Stages the (normalised) activations as block fixed point.  Thread t of each group of 8 owns byte
-// slots 4j..4j+3 (j = t & 7) of blocks (t >> 3) + 64 i.  For K <= 12288 every thread first loads all of
-// its values (one round trip to L2), the RMS comes from those registers, then the blocks are quantised.
+// slots 4j..4j+3 (j = t & 7) of blocks (t >> 3) + 64 i.
+//  - RMS-normalised input of up to 4096 values (the decode path of a 4096-wide model): every thread
+//    loads its two passes first (one round trip to L2), the RMS comes from those registers, then the
+//    blocks are quantised.
+//  - otherwise: the RMS, if any, in a pass of its own, then one rolled loop over the blocks.
+// The kernel's instruction count per warp is of the order of its code size, so code executed once is
+// kept small: two unrolled passes, not one per possible K.
 template <int FMT>
 __device__ void stage_fixed_point(const GemvParams &p, uint32_t m, uint32_t *xq, float *red) {
-  constexpr int MAXP = 6;
   const uint32_t K = p.K, nb = K / 32;
   const float *xf = p.x_is_f16 ? nullptr : reinterpret_cast<const float *>(p.x) + (size_t)m * K;
   const __half *xh = p.x_is_f16 ? reinterpret_cast<const __half *>(p.x) + (size_t)m * K : nullptr;
   const int j = threadIdx.x & 7;
-  const uint32_t b0 = threadIdx.x >> 3, passes = (nb + 63) / 64;
-  if (passes <= (uint32_t)MAXP) {
-    float v[MAXP][4], gm[MAXP][4];
+  const uint32_t b0 = threadIdx.x >> 3;
+  if (p.gamma && nb <= 128) {
+    float v[2][4], gm[2][4];
 #pragma unroll
-    for (int i = 0; i < MAXP; ++i) {
-      const uint32_t b = b0 + 64 * i;
+    for (int i = 0; i < 2; ++i) {
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        const uint32_t idx = b * 32 + slot_element<FMT>(4 * j + k);
         v[i][k] = 0.f;
         gm[i][k] = 0.f;
-        if (b < nb) {
-          v[i][k] = xf ? __ldcg(xf + idx) : __half2float(__ldcg(xh + idx));  // bypass L1: another SM may have just written x
-          if (p.gamma) gm[i][k] = p.gamma[idx];
-        }
       }
+      if (b0 + 64 * i < nb) load_slot_values<FMT>(xf, xh, p.gamma, b0 + 64 * i, j, v[i], gm[i]);
     }
-    if (p.gamma) {
-      const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-      float ss = 0.f;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float ss = 0.f;
 #pragma unroll
-      for (int i = 0; i < MAXP; ++i)
+    for (int i = 0; i < 2; ++i)
 #pragma unroll
-        for (int k = 0; k < 4; ++k) ss = fmaf(v[i][k], v[i][k], ss);
-      ss = warp_sum(ss);
-      if (lane == 0) red[warp] = ss;
-      __syncthreads();
-      float t = (lane < WARPS) ? red[lane] : 0.f;
-      t = warp_sum(t);
-      const float inv = rsqrtf(t / (float)K + p.eps);
+      for (int k = 0; k < 4; ++k) ss = fmaf(v[i][k], v[i][k], ss);
+    ss = warp_sum(ss);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    float t = (lane < WARPS) ? red[lane] : 0.f;
+    t = warp_sum(t);
+    const float inv = rsqrtf(t / (float)K + p.eps);
 #pragma unroll
-      for (int i = 0; i < MAXP; ++i)
+    for (int i = 0; i < 2; ++i) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) v[i][k] = (v[i][k] * inv) * gm[i][k];
+      for (int k = 0; k < 4; ++k) v[i][k] = (v[i][k] * inv) * gm[i][k];
+      if (i == 0 || nb > 64) quantize_store<FMT>(v[i], xq, b0 + 64 * i, j, b0 + 64 * i < nb);
     }
-#pragma unroll
-    for (int i = 0; i < MAXP; ++i)
-      if ((uint32_t)i < passes) quantize_store<FMT>(v[i], xq, b0 + 64 * i, j, b0 + 64 * i < nb);
     return;
   }
   const float inv = p.gamma ? cta_inv_rms(xf, xh, K, p.eps, red) : 1.0f;
-  for (uint32_t b = b0; b < passes * 64; b += THREADS / 8) {  // uniform trip count for the shuffles
+  const uint32_t bend = (nb + 63) / 64 * 64;  // uniform trip count for the shuffles
+#pragma unroll 1
+  for (uint32_t b = b0; b < bend; b += THREADS / 8) {
     const bool live = b < nb;
-    float v[4];
+    float v[4] = {0.f, 0.f, 0.f, 0.f}, gm[4] = {1.f, 1.f, 1.f, 1.f};
+    if (live) {
+      load_slot_values<FMT>(xf, xh, p.gamma, b, j, v, gm);
+      if (p.gamma) {
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const uint32_t idx = b * 32 + slot_element<FMT>(4 * j + k);
-      float t = 0.f;
-      if (live) {
-        t = xf ? __ldcg(xf + idx) : __half2float(__ldcg(xh + idx));
-        if (p.gamma) t = (t * inv) * p.gamma[idx];
+        for (int k = 0; k < 4; ++k) v[k] = (v[k] * inv) * gm[k];
       }
-      v[k] = t;
     }
     quantize_store<FMT>(v, xq, b, j, live);
   }

@@ -234,6 +234,15 @@ OAPI int oracle_num_threads() {
 #endif
 }
 
+// Thread count of the parallel loops (a launcher may have exported OMP_NUM_THREADS=1 for its workers).
+OAPI void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 OAPI float oracle_fp16_to_fp32(uint16_t h) { return h2f(h); }
 OAPI uint16_t oracle_fp32_to_fp16(float f) { return f2h(f); }
 

@@ -64,6 +64,12 @@ def num_threads():
     return lib().oracle_num_threads()
 
 
+def set_num_threads(n):
+    lib().oracle_set_num_threads.argtypes = [C.c_int]
+    lib().oracle_set_num_threads.restype = None
+    lib().oracle_set_num_threads(int(n))
+
+
 # --------------------------------------------------------------------------- formats
 def f16_bits_to_f32(h):
     h = np.ascontiguousarray(h, dtype=np.uint16)

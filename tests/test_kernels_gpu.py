@@ -264,7 +264,11 @@ def test_fused_ffn_front(g, name, D, F):
 @pytest.mark.parametrize("H,Hkv,Dh,L,max_seq", [(4, 4, 128, 1, 8), (4, 4, 128, 63, 64), (8, 2, 64, 200, 256),
                                                 (32, 32, 128, 2049, 2304), (64, 8, 128, 777, 1024)])
 @pytest.mark.parametrize("use_dpos", [False, True])
-def test_attn_decode_matches_oracle(g, H, Hkv, Dh, L, max_seq, use_dpos):
+@pytest.mark.parametrize("cluster", ["1", "0"])
+def test_attn_decode_matches_oracle(g, monkeypatch, H, Hkv, Dh, L, max_seq, use_dpos, cluster):
+    """Both ways of merging the sequence splits: inside a thread-block cluster through distributed shared memory
+    (the default) and through the scratch buffer with tickets (GRETA_ATTN_CLUSTER=0)."""
+    monkeypatch.setenv("GRETA_ATTN_CLUSTER", cluster)
     rng = np.random.default_rng(40 + L)
     q = rng.normal(0, 1, H * Dh).astype(np.float32)
     kc = rng.normal(0, 1, (Hkv, max_seq, Dh)).astype(np.float16)
