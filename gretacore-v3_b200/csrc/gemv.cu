@@ -164,7 +164,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_simple_kernel(const GemvParam
   }
 }
 
-template <int FMT, int EPI, int R>
+// DT: ring depth fixed at compile time (waits and stage wrap-arounds fold to constants), 0 = taken from p.stages.
+template <int FMT, int EPI, int R, int DT>
 __global__ void __launch_bounds__(THREADS, 1) gemv_pipe_kernel(const GemvParams p) {
   using F = Fmt<FMT>;
   constexpr int QV = F::QV, PB = QV * 16;
@@ -177,15 +178,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pipe_kernel(const GemvParams 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const uint32_t nb = p.K / 32, C = (nb + 31) / 32;               // chunks (cells) per row group
   const uint32_t m = blockIdx.y;
-  const uint32_t D = p.stages;
+  const uint32_t D = DT ? (uint32_t)DT : p.stages;
   const size_t xs_bytes = F::INTEGER ? (size_t)nb * XQ_WORDS * 4 : (size_t)nb * XPAD * 4;
   uint8_t *ring = smem + ((xs_bytes + 15) & ~(size_t)15) + (size_t)warp * D * STAGE_BYTES;
   float *part = reinterpret_cast<float *>(smem + ((xs_bytes + 15) & ~(size_t)15) + (size_t)WARPS * D * STAGE_BYTES);
   // part[warp][slot][R]
 
   // This CTA's row groups and this warp's cells.
-  const uint32_t g0 = (uint32_t)((uint64_t)blockIdx.x * p.groups / gridDim.x);
-  const uint32_t g1 = (uint32_t)((uint64_t)(blockIdx.x + 1) * p.groups / gridDim.x);
+  const uint32_t g0 = blockIdx.x * p.gq + min(blockIdx.x, p.gr);
+  const uint32_t g1 = g0 + p.gq + (blockIdx.x < p.gr ? 1u : 0u);
   const uint32_t T = (g1 - g0) * C;
   const uint32_t c0 = (uint32_t)((uint64_t)warp * T / WARPS), c1 = (uint32_t)((uint64_t)(warp + 1) * T / WARPS);
 
@@ -278,7 +279,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pipe_kernel(const GemvParams 
   constexpr uint32_t X_BLOCK_BYTES = F::INTEGER ? XQ_WORDS * 4 : XPAD * 4;
   const uint8_t *xrun = smem + (size_t)(ck * 32 + lane) * X_BLOCK_BYTES;  // this lane's activation block, runs along K
   for (uint32_t c = c0; c < c1; ++c) {
-    cp_async_wait((int)D - 2);
+    if (DT)
+      cp_async_wait_c<(DT ? DT : 2) - 2>();
+    else
+      cp_async_wait((int)D - 2);
     __syncwarp();
     const uint8_t *st = ring + cstage * STAGE_BYTES;
     cstage = (cstage + 1 == D) ? 0 : cstage + 1;
@@ -394,12 +398,23 @@ int launch_pipe(cudaStream_t stream, GemvParams p) {
   uint32_t stages = (uint32_t)((SMEM_LIMIT - xs_bytes - part_bytes) / (WARPS * stage_bytes));
   stages = std::min<uint32_t>(stages, MAX_STAGES);
   stages = std::min<uint32_t>(stages, std::max(2u, cells_per_warp + 1));     // no deeper than the work
+  p.gq = p.groups / ctas;
+  p.gr = p.groups % ctas;
+  dim3 grid(ctas, p.M ? p.M : 1);
+  constexpr uint32_t DFIX = 5;  // the usual depth: room for it up to K of about 20000
+  if (F::INTEGER && (SMEM_LIMIT - xs_bytes - part_bytes) / (WARPS * stage_bytes) >= DFIX) {
+    p.stages = DFIX;  // deeper than the work is harmless: requests past the last cell are empty groups
+    const size_t smem = xs_bytes + (size_t)WARPS * DFIX * stage_bytes + part_bytes;
+    static bool attr_set_fixed[64] = {};
+    if (int rc = ensure_smem_attr(gemv_pipe_kernel<FMT, EPI, R, F::INTEGER ? DFIX : 0>, attr_set_fixed)) return rc;
+    GRETA_CUDA_TRY(launch_pdl(gemv_pipe_kernel<FMT, EPI, R, F::INTEGER ? DFIX : 0>, grid, dim3(THREADS), smem, stream, p));
+    return launched("gemv_pipe_kernel");
+  }
   p.stages = stages;
   const size_t smem = xs_bytes + (size_t)WARPS * stages * stage_bytes + part_bytes;
   static bool attr_set[64] = {};
-  if (int rc = ensure_smem_attr(gemv_pipe_kernel<FMT, EPI, R>, attr_set)) return rc;
-  dim3 grid(ctas, p.M ? p.M : 1);
-  GRETA_CUDA_TRY(launch_pdl(gemv_pipe_kernel<FMT, EPI, R>, grid, dim3(THREADS), smem, stream, p));
+  if (int rc = ensure_smem_attr(gemv_pipe_kernel<FMT, EPI, R, 0>, attr_set)) return rc;
+  GRETA_CUDA_TRY(launch_pdl(gemv_pipe_kernel<FMT, EPI, R, 0>, grid, dim3(THREADS), smem, stream, p));
   return launched("gemv_pipe_kernel");
 }
 

@@ -44,6 +44,7 @@ struct GemvParams {
   uint32_t kw, iters;
   // pipelined kernel
   uint32_t stages, slots;
+  uint32_t gq, gr;  // row groups per CTA: CTA b owns gq (+1 when b < gr) groups
 };
 
 template <int FMT>
@@ -390,6 +391,10 @@ __device__ __forceinline__ void cp_async4(void *smem_dst, const void *gsrc) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(s), "l"(gsrc) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait_c() {  // at most N groups still in flight
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
 __device__ __forceinline__ void cp_async_wait(int pending) {  // at most `pending` groups still in flight
   switch (pending) {
     case 0: asm volatile("cp.async.wait_group 0;" ::: "memory"); break;
