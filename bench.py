@@ -159,6 +159,47 @@ class Ranks:
         self.gather_max(0.0)
         self.bcast(b"go!!", 4)
 
+    def allgather(self, data):
+        """Every rank contributes len(data) bytes; returns the list of all ranks' contributions."""
+        n = len(data)
+        if self.world == 1:
+            return [data]
+        if self.rank == 0:
+            parts = [data] + [self._recv(c, n) for c in self.peers]
+            self.bcast(b"".join(parts), n * self.world)
+            return parts
+        self.sock.sendall(data)
+        blob = self._recv(self.sock, n * self.world)
+        return [blob[i * n:(i + 1) * n] for i in range(self.world)]
+
+
+def install_peer_exchange(pkg, model, ranks, dim):
+    """Sets up the fused tensor-parallel exchange: every rank allocates its slot buffer, the processes swap the
+    64-byte IPC handles over the rendezvous sockets, map each other's buffers and hand the table to the model.
+    Returns the objects that must stay alive (and the mapped pointers to close)."""
+    import ctypes as C
+    g = pkg.ffi
+    lib = g.cuda()
+    nbytes = lib.greta_cuda_peer_slot_bytes(ranks.world, dim)
+    local = g.DeviceBuffer(nbytes, zero=True)
+    handle = C.create_string_buffer(64)
+    g.check(lib.greta_cuda_ipc_export(local.ptr, handle), "ipc_export")
+    handles = ranks.allgather(bytes(handle.raw))
+    ex = pkg.model.PeerExchange()
+    ex.tp, ex.rank = ranks.world, ranks.rank
+    mapped = []
+    for r, h in enumerate(handles):
+        if r == ranks.rank:
+            ex.slots[r] = local.ptr
+        else:
+            ptr = C.c_void_p()
+            g.check(lib.greta_cuda_ipc_open(C.create_string_buffer(h, 64), C.byref(ptr)), "ipc_open")
+            ex.slots[r] = ptr.value
+            mapped.append(ptr.value)
+    ranks.barrier()                                   # every buffer is cleared and mapped before anyone stores into it
+    model.set_peer_exchange(ex)
+    return local, ex, mapped
+
 
 # ----------------------------------------------------------------------------- CPU baseline (oracle port)
 def cpu_decode_layer_seconds(cfg, n_layers, reps):
@@ -352,6 +393,8 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
     ap.add_argument("--prefill-chunk", type=int, default=0, help="tokens per prefill call (0 = the whole prompt at once)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", choices=["fused", "nccl"], default="fused",
+                    help="tensor-parallel exchange of the decode step: fused into the GEMV kernels over peer memory, or NCCL all-reduce")
     ap.add_argument("--case", default=None, help="run a small single-kernel case (gemv_swiglu, gemv_plain, gemm_c2, attn_decode, decode_step) and exit")
     args = ap.parse_args()
     ranks = Ranks()
@@ -384,6 +427,8 @@ def main():
         idbuf = C.create_string_buffer(raw, 128)
         g.check(lib.greta_cuda_comm_init(C.byref(comm), idbuf, tp, ranks.rank), "comm_init")
         model.set_comm(comm)
+        if args.exchange == "fused":
+            peer_keep = install_peer_exchange(pkg, model, ranks, cfg["dim"])
     model.load_synthetic(SEED)
     prompt = pkg.model.synth_tokens(SEED, args.prompt_len, cfg["vocab"])
     chunk = args.prefill_chunk or args.prompt_len           # prefill (not timed): one tensor-core pass by default
@@ -441,7 +486,7 @@ def main():
         "data": "synthetic",
         "config": {"workload": "Llama-2-7B-shaped model (32 layers, hidden 4096, 32 heads x 128, FFN 11008, vocab 32000), random-init "
                                "Q4_0 weights, fp16 LM head, 512-token random prompt then greedy decode at batch 1 (BASELINE config 4)",
-                   "prompt_len": args.prompt_len, "parallelism": f"tp{tp}" if tp > 1 else "single GPU",
+                   "prompt_len": args.prompt_len, "parallelism": (f"tp{tp}, exchange {args.exchange}" if tp > 1 else "single GPU"),
                    "l2_defeat": "every step streams 3.9 GB of distinct weights (L2 is 126 MB)", "seed": SEED},
         "clocks": clocks, "gpu_launches": int(launches),
         "e2e": {"value": 1e3 * args.steps / ms_e2e, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4,

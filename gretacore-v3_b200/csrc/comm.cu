@@ -51,4 +51,27 @@ int greta_cuda_comm_allreduce_f32(void *comm, float *buf, size_t count, greta_st
   return GRETA_OK;
 }
 
+// Shares a device allocation with the other ranks' processes (slot buffers of the fused exchange).
+int greta_cuda_ipc_export(void *device_ptr, void *handle64) {
+  GRETA_REQUIRE(device_ptr && handle64, "ipc_export: null argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "cudaIpcMemHandle_t is expected to be 64 bytes");
+  cudaIpcMemHandle_t h;
+  GRETA_CUDA_TRY(cudaIpcGetMemHandle(&h, device_ptr));
+  std::memcpy(handle64, &h, sizeof(h));
+  return GRETA_OK;
+}
+
+int greta_cuda_ipc_open(const void *handle64, void **device_ptr) {
+  GRETA_REQUIRE(handle64 && device_ptr, "ipc_open: null argument");
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle64, sizeof(h));
+  GRETA_CUDA_TRY(cudaIpcOpenMemHandle(device_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return GRETA_OK;
+}
+
+int greta_cuda_ipc_close(void *device_ptr) {
+  if (device_ptr) GRETA_CUDA_TRY(cudaIpcCloseMemHandle(device_ptr));
+  return GRETA_OK;
+}
+
 }  // extern "C"

@@ -224,7 +224,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_layers_kernel(const StepPla
         const uint32_t gi = layer * 4 + (sub == 0 ? 0 : sub - 1);
         const GemvParams &P = *gemv_phase(plan.layers, gi);
         const Geom g = geom_of(P, warp);
-        stage_fixed_point<FMT>(P, 0, reinterpret_cast<uint32_t *>(smem), red);
+        stage_fixed_point<FMT, false>(P, 0, reinterpret_cast<uint32_t *>(smem), red);
         __syncthreads();
         if (tr) plan.trace[sub * 5 + 1] = clock64();
         float acc[R];

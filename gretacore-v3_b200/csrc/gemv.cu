@@ -165,7 +165,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_simple_kernel(const GemvParam
 }
 
 // DT: ring depth fixed at compile time (waits and stage wrap-arounds fold to constants), 0 = taken from p.stages.
-template <int FMT, int EPI, int R, int DT>
+// PEER: the activations are the residual stream plus the tensor-parallel partials waiting in this rank's slots.
+template <int FMT, int EPI, int R, int DT, bool PEER>
 __global__ void __launch_bounds__(THREADS, 1) gemv_pipe_kernel(const GemvParams p) {
   using F = Fmt<FMT>;
   constexpr int QV = F::QV, PB = QV * 16;
@@ -254,7 +255,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pipe_kernel(const GemvParams 
 
   // ---- stage activations ----
   if (F::INTEGER) {
-    stage_fixed_point<FMT>(p, m, reinterpret_cast<uint32_t *>(smem), red);
+    stage_fixed_point<FMT, PEER>(p, m, reinterpret_cast<uint32_t *>(smem), red);
   } else {
     float *xs = reinterpret_cast<float *>(smem);
     const uint32_t K = p.K;
@@ -342,7 +343,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pipe_kernel(const GemvParams 
   __syncthreads();
 
   // ---- epilogue: one warp per row group ----
-  const uint32_t pos = (EPI == EPI_QKV && p.d_pos) ? __ldcg(p.d_pos) : 0u;
+  const uint32_t pos = (EPI == EPI_QKV && p.d_pos) ? __ldcg(p.d_pos) : (EPI == EPI_PEER ? peer_tag(p) : 0u);
   cta_epilogue<EPI, R>(p, part, p.slots, g0, g1, C, T, m, pos, (EPI == EPI_QKV && p.d_pos) ? rope_cs : nullptr);
 }
 
@@ -382,7 +383,7 @@ int launch_simple(cudaStream_t stream, GemvParams p) {
   return launched("gemv_simple_kernel");
 }
 
-template <int FMT, int EPI, int R>
+template <int FMT, int EPI, int R, bool PEER = false>
 int launch_pipe(cudaStream_t stream, GemvParams p) {
   using F = Fmt<FMT>;
   const uint32_t nb = p.K / 32, C = (nb + 31) / 32;
@@ -394,7 +395,10 @@ int launch_pipe(cudaStream_t stream, GemvParams p) {
   const uint32_t cells_per_warp = (uint32_t)(((uint64_t)gmax * C + WARPS - 1) / WARPS);
   p.slots = cells_per_warp / C + 2;                                          // groups one warp can touch
   const size_t part_bytes = (size_t)WARPS * p.slots * R * sizeof(float);
-  if (xs_bytes + part_bytes + 2 * WARPS * stage_bytes > SMEM_LIMIT) return launch_simple<FMT, EPI, R>(stream, p);
+  if (xs_bytes + part_bytes + 2 * WARPS * stage_bytes > SMEM_LIMIT) {
+    GRETA_REQUIRE(!PEER && EPI != EPI_PEER, "gemv: K=%u is too large for the tensor-parallel exchange form", p.K);
+    return launch_simple<FMT, EPI == EPI_PEER ? EPI_PLAIN : EPI, R>(stream, p);
+  }
   uint32_t stages = (uint32_t)((SMEM_LIMIT - xs_bytes - part_bytes) / (WARPS * stage_bytes));
   stages = std::min<uint32_t>(stages, MAX_STAGES);
   stages = std::min<uint32_t>(stages, std::max(2u, cells_per_warp + 1));     // no deeper than the work
@@ -406,39 +410,66 @@ int launch_pipe(cudaStream_t stream, GemvParams p) {
     p.stages = DFIX;  // deeper than the work is harmless: requests past the last cell are empty groups
     const size_t smem = xs_bytes + (size_t)WARPS * DFIX * stage_bytes + part_bytes;
     static bool attr_set_fixed[64] = {};
-    if (int rc = ensure_smem_attr(gemv_pipe_kernel<FMT, EPI, R, F::INTEGER ? DFIX : 0>, attr_set_fixed)) return rc;
-    GRETA_CUDA_TRY(launch_pdl(gemv_pipe_kernel<FMT, EPI, R, F::INTEGER ? DFIX : 0>, grid, dim3(THREADS), smem, stream, p));
+    if (int rc = ensure_smem_attr(gemv_pipe_kernel<FMT, EPI, R, F::INTEGER ? DFIX : 0, PEER>, attr_set_fixed)) return rc;
+    GRETA_CUDA_TRY(launch_pdl(gemv_pipe_kernel<FMT, EPI, R, F::INTEGER ? DFIX : 0, PEER>, grid, dim3(THREADS), smem, stream, p));
     return launched("gemv_pipe_kernel");
   }
   p.stages = stages;
   const size_t smem = xs_bytes + (size_t)WARPS * stages * stage_bytes + part_bytes;
   static bool attr_set[64] = {};
-  if (int rc = ensure_smem_attr(gemv_pipe_kernel<FMT, EPI, R, 0>, attr_set)) return rc;
-  GRETA_CUDA_TRY(launch_pdl(gemv_pipe_kernel<FMT, EPI, R, 0>, grid, dim3(THREADS), smem, stream, p));
+  if (int rc = ensure_smem_attr(gemv_pipe_kernel<FMT, EPI, R, 0, PEER>, attr_set)) return rc;
+  GRETA_CUDA_TRY(launch_pdl(gemv_pipe_kernel<FMT, EPI, R, 0, PEER>, grid, dim3(THREADS), smem, stream, p));
   return launched("gemv_pipe_kernel");
 }
 
 // Row groups of R rows for an operator with `rows` output rows per matrix.
 template <int EPI, int R>
 uint32_t count_groups(const GemvParams &p) {
-  if (EPI == EPI_PLAIN || EPI == EPI_RESIDUAL) return (p.N + R - 1) / R;
+  if (EPI == EPI_PLAIN || EPI == EPI_RESIDUAL || EPI == EPI_PEER) return (p.N + R - 1) / R;
   if (EPI == EPI_SWIGLU) return (p.N + R / 2 - 1) / (R / 2);
   return (p.H + p.Hkv) * ((p.Dh / 2) / (R / 2)) + (p.Hkv * p.Dh + R - 1) / R;
 }
 
-template <int FMT, int EPI, int R>
+template <int FMT, int EPI, int R, bool PEER = false>
 int launch_any(cudaStream_t stream, GemvParams p) {
   p.groups = count_groups<EPI, R>(p);
-  return launch_pipe<FMT, EPI, R>(stream, p);  // falls back to the simple kernel when K does not fit in shared memory
+  return launch_pipe<FMT, EPI, R, PEER>(stream, p);  // falls back to the simple kernel when K does not fit in shared memory
 }
 
 // Few rows: groups of 2 give twice as many cells to balance over the warps.
-template <int FMT, int EPI>
+template <int FMT, int EPI, bool PEER = false>
 int launch_quant(cudaStream_t stream, const GemvParams &p, uint64_t total_rows) {
   const uint64_t cells4 = (total_rows / 4) * ((p.K / 32 + 31) / 32);
-  if (EPI == EPI_QKV && (p.Dh / 2) % 2 != 0) return launch_any<FMT, EPI, 2>(stream, p);
-  if (cells4 < (uint64_t)sm_count() * WARPS * 4) return launch_any<FMT, EPI, 2>(stream, p);
-  return launch_any<FMT, EPI, 4>(stream, p);
+  if (EPI == EPI_QKV && (p.Dh / 2) % 2 != 0) return launch_any<FMT, EPI, 2, PEER>(stream, p);
+  if (cells4 < (uint64_t)sm_count() * WARPS * 4) return launch_any<FMT, EPI, 2, PEER>(stream, p);
+  return launch_any<FMT, EPI, 4, PEER>(stream, p);
+}
+
+// The operators of the tensor-parallel exchange exist for the GGUF formats only.
+template <int EPI, bool PEER>
+int dispatch_peer(cudaStream_t stream, int fmt, const GemvParams &p, uint64_t total_rows) {
+  if (fmt == GRETA_FMT_Q4_0) return launch_quant<GRETA_FMT_Q4_0, EPI, PEER>(stream, p, total_rows);
+  if (fmt == GRETA_FMT_Q8_0) return launch_quant<GRETA_FMT_Q8_0, EPI, PEER>(stream, p, total_rows);
+  set_error("tensor-parallel exchange: format %d is not supported (Q4_0 or Q8_0)", fmt);
+  return GRETA_ERR_INVALID_ARGS;
+}
+
+int fill_exchange(GemvParams &p, const greta_peer_exchange *ex, uint32_t exch_idx, const uint32_t *d_pos, uint32_t dim, bool as_producer) {
+  GRETA_REQUIRE(ex && d_pos, "tensor-parallel exchange: null exchange descriptor or position");
+  GRETA_REQUIRE(ex->tp >= 1 && ex->tp <= (uint32_t)MAX_TP && ex->rank < ex->tp, "tensor-parallel exchange: rank %u of %u", ex->rank, ex->tp);
+  GRETA_REQUIRE(exch_idx < 256, "tensor-parallel exchange: index %u out of range (256 per step)", exch_idx);
+  GRETA_REQUIRE(dim % 32 == 0 && dim <= 8192, "tensor-parallel exchange: dim=%u must be a multiple of 32, at most 8192", dim);
+  const size_t parity_words = (size_t)ex->tp * dim;  // {value, tag} words per parity
+  for (uint32_t j = 0; j < ex->tp; ++j) {
+    GRETA_REQUIRE(ex->slots[j] && aligned16(ex->slots[j]), "tensor-parallel exchange: slot buffer %u is null or misaligned", j);
+    p.peer_out[j] = as_producer ? static_cast<uint2 *>(ex->slots[j]) + (exch_idx & 1) * parity_words : nullptr;
+  }
+  p.peer_in = as_producer ? nullptr : static_cast<const uint2 *>(ex->slots[ex->rank]) + (exch_idx & 1) * parity_words;
+  p.tp = ex->tp;
+  p.rank = ex->rank;
+  p.exch_idx = exch_idx;
+  p.d_pos = d_pos;
+  return GRETA_OK;
 }
 
 template <int EPI>
@@ -588,6 +619,85 @@ int greta_cuda_fused_ffn_front(greta_stream_t stream, int fmt, const float *x, c
   p.M = 1;
   p.y = y;
   return dispatch_quant<EPI_SWIGLU>((cudaStream_t)stream, fmt, p, (uint64_t)2 * F);
+}
+
+// ---- tensor-parallel exchange over peer memory ---------------------------------------------------
+size_t greta_cuda_peer_slot_bytes(uint32_t tp, uint32_t dim) { return (size_t)2 * tp * dim * sizeof(uint2); }
+
+int greta_cuda_peer_status(int *code) {
+  GRETA_REQUIRE(code, "peer_status: null out pointer");
+  GRETA_CUDA_TRY(cudaMemcpyFromSymbol(code, g_peer_error, sizeof(int)));
+  return GRETA_OK;
+}
+
+int greta_cuda_gemv_peer_scatter(greta_stream_t stream, int fmt, const float *x, const void *qs, const void *d,
+                                 const greta_peer_exchange *ex, uint32_t exch_idx, const uint32_t *d_pos, uint32_t N, uint32_t K) {
+  GRETA_REQUIRE(N && K && K % 32 == 0, "gemv_peer_scatter: N=%u, K=%u (K must be a positive multiple of 32)", N, K);
+  GRETA_REQUIRE(x, "gemv_peer_scatter: null activation pointer");
+  if (int rc = check_plane("gemv_peer_scatter", qs, d, fmt)) return rc;
+  GemvParams p{};
+  p.x = x;
+  p.w[0] = {(const uint8_t *)qs, d};
+  p.K = K;
+  p.N = N;
+  p.M = 1;
+  if (int rc = fill_exchange(p, ex, exch_idx, d_pos, N, true)) return rc;
+  return dispatch_peer<EPI_PEER, false>((cudaStream_t)stream, fmt, p, N);
+}
+
+int greta_cuda_fused_rmsnorm_qkv_rope_kv_peer(greta_stream_t stream, int fmt, const float *x_in, float *x_out,
+                                              const greta_peer_exchange *ex, uint32_t exch_idx, const float *gamma, float eps,
+                                              const void *wq_qs, const void *wq_d, const void *wk_qs, const void *wk_d,
+                                              const void *wv_qs, const void *wv_d, float *q_out, void *k_cache, void *v_cache,
+                                              const uint32_t *d_pos, uint32_t H, uint32_t Hkv, uint32_t Dh, uint32_t max_seq,
+                                              float rope_base, uint32_t D) {
+  GRETA_REQUIRE(D && H && Hkv && Dh && Dh % 2 == 0 && H % Hkv == 0, "fused_qkv_peer: bad dimensions");
+  GRETA_REQUIRE(x_in && x_out && x_in != x_out && gamma && q_out && k_cache && v_cache, "fused_qkv_peer: null pointer, or x_out aliases x_in");
+  if (int rc = check_plane("fused_qkv_peer(wq)", wq_qs, wq_d, fmt)) return rc;
+  if (int rc = check_plane("fused_qkv_peer(wk)", wk_qs, wk_d, fmt)) return rc;
+  if (int rc = check_plane("fused_qkv_peer(wv)", wv_qs, wv_d, fmt)) return rc;
+  GemvParams p{};
+  p.x = x_in;
+  p.x_out = x_out;
+  p.gamma = gamma;
+  p.eps = eps;
+  p.w[0] = {(const uint8_t *)wq_qs, wq_d};
+  p.w[1] = {(const uint8_t *)wk_qs, wk_d};
+  p.w[2] = {(const uint8_t *)wv_qs, wv_d};
+  p.K = D;
+  p.M = 1;
+  p.q_out = q_out;
+  p.k_cache = (__half *)k_cache;
+  p.v_cache = (__half *)v_cache;
+  p.H = H;
+  p.Hkv = Hkv;
+  p.Dh = Dh;
+  p.max_seq = max_seq;
+  p.rope_base = rope_base;
+  if (int rc = fill_exchange(p, ex, exch_idx, d_pos, D, false)) return rc;
+  return dispatch_peer<EPI_QKV, true>((cudaStream_t)stream, fmt, p, (uint64_t)(H + 2 * Hkv) * Dh);
+}
+
+int greta_cuda_fused_ffn_front_peer(greta_stream_t stream, int fmt, const float *x_in, float *x_out, const greta_peer_exchange *ex,
+                                    uint32_t exch_idx, const uint32_t *d_pos, const float *gamma, float eps, const void *w1_qs,
+                                    const void *w1_d, const void *w3_qs, const void *w3_d, float *y, uint32_t D, uint32_t F) {
+  GRETA_REQUIRE(D && F, "fused_ffn_front_peer: zero dimension");
+  GRETA_REQUIRE(x_in && x_out && x_in != x_out && gamma && y, "fused_ffn_front_peer: null pointer, or x_out aliases x_in");
+  if (int rc = check_plane("fused_ffn_front_peer(w1)", w1_qs, w1_d, fmt)) return rc;
+  if (int rc = check_plane("fused_ffn_front_peer(w3)", w3_qs, w3_d, fmt)) return rc;
+  GemvParams p{};
+  p.x = x_in;
+  p.x_out = x_out;
+  p.gamma = gamma;
+  p.eps = eps;
+  p.w[0] = {(const uint8_t *)w1_qs, w1_d};
+  p.w[1] = {(const uint8_t *)w3_qs, w3_d};
+  p.K = D;
+  p.N = F;
+  p.M = 1;
+  p.y = y;
+  if (int rc = fill_exchange(p, ex, exch_idx, d_pos, D, false)) return rc;
+  return dispatch_peer<EPI_SWIGLU, true>((cudaStream_t)stream, fmt, p, (uint64_t)2 * F);
 }
 
 }  // extern "C"

@@ -18,7 +18,8 @@ constexpr int XQ_WORDS = 28;   // 32-bit words per staged fixed-point block: 3 p
 constexpr int MAX_STAGES = 8;
 constexpr size_t SMEM_LIMIT = 220 * 1024;
 
-enum { EPI_PLAIN = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_QKV = 3 };
+enum { EPI_PLAIN = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_QKV = 3, EPI_PEER = 4 };
+constexpr int MAX_TP = 8;
 
 struct WPlane {
   const uint8_t *qs;
@@ -45,7 +46,51 @@ struct GemvParams {
   // pipelined kernel
   uint32_t stages, slots;
   uint32_t gq, gr;  // row groups per CTA: CTA b owns gq (+1 when b < gr) groups
+  // Tensor-parallel exchange over peer memory.  A slot buffer holds [tp][dim] words {value bits, tag}; a
+  // row-parallel projection (EPI_PEER) stores its partial product, tagged, into slot `rank` of every rank's
+  // buffer; the next operator's staging waits for the tp tagged partials, adds them to the residual stream
+  // in rank order and (CTA 0) writes the new stream to x_out.
+  uint2 *peer_out[MAX_TP];
+  const uint2 *peer_in;
+  float *x_out;
+  uint32_t tp, rank, exch_idx;
 };
+
+// Tag of exchange number exch_idx at the current position: strictly increasing within a decode session.
+__device__ __forceinline__ uint32_t peer_tag(const GemvParams &p) { return ((__ldcg(p.d_pos) + 1u) << 8) | p.exch_idx; }
+
+__device__ int g_peer_error = 0;  // set when a wait for a peer's partial gave up
+constexpr uint32_t PEER_POLL_LIMIT = 1u << 22;
+
+__device__ __forceinline__ void st_peer(uint2 *dst, uint2 v) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(v.x), "r"(v.y) : "memory");
+}
+__device__ __forceinline__ uint4 ld_peer16(const void *src) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src) : "memory");
+  return v;
+}
+// Adds the tp partials of elements idx .. idx+3 to v, in rank order, waiting (bounded) for their tags.
+__device__ __forceinline__ void add_peer_partials(const GemvParams &p, uint32_t idx, uint32_t tag, float (&v)[4]) {
+  for (uint32_t r = 0; r < p.tp; ++r) {
+    const uint2 *src = p.peer_in + (size_t)r * p.K + idx;
+    uint4 a, b;
+    uint32_t polls = 0;
+    for (;;) {
+      a = ld_peer16(src);
+      b = ld_peer16(src + 2);
+      if (a.y == tag && a.w == tag && b.y == tag && b.w == tag) break;
+      if (++polls > PEER_POLL_LIMIT) {
+        g_peer_error = 1;
+        break;
+      }
+    }
+    v[0] += __uint_as_float(a.x);
+    v[1] += __uint_as_float(a.z);
+    v[2] += __uint_as_float(b.x);
+    v[3] += __uint_as_float(b.z);
+  }
+}
 
 template <int FMT>
 struct Fmt;
@@ -83,7 +128,7 @@ struct Fmt<GRETA_FMT_F16> {
 template <int EPI, int R>
 __device__ __forceinline__ bool resolve(const GemvParams &p, uint32_t grp, int slot, int *mat, uint32_t *row) {
   constexpr int PAIRS = R / 2;
-  if (EPI == EPI_PLAIN || EPI == EPI_RESIDUAL) {
+  if (EPI == EPI_PLAIN || EPI == EPI_RESIDUAL || EPI == EPI_PEER) {
     *mat = 0;
     *row = grp * R + slot;
     return *row < p.N;
@@ -119,6 +164,13 @@ __device__ __forceinline__ void epilogue(const GemvParams &p, uint32_t grp, uint
     for (int r = 0; r < R; ++r) {
       uint32_t row = grp * R + r;
       if (row < p.N) p.y[row] = __ldcg(p.resid + row) + v[r];
+    }
+  } else if (EPI == EPI_PEER) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      uint32_t row = grp * R + r;
+      if (row < p.N)
+        for (uint32_t j = 0; j < p.tp; ++j) st_peer(p.peer_out[j] + (size_t)p.rank * p.N + row, make_uint2(__float_as_uint(v[r]), pos));
     }
   } else if (EPI == EPI_SWIGLU) {
 #pragma unroll
@@ -192,6 +244,10 @@ __device__ __forceinline__ void epilogue_lane(const GemvParams &p, uint32_t grp,
   } else if (EPI == EPI_RESIDUAL) {
     const uint32_t row = grp * R + lane;
     if (lane < R && row < p.N) p.y[row] = __ldcg(p.resid + row) + mine;
+  } else if (EPI == EPI_PEER) {  // pos carries the tag
+    const uint32_t row = grp * R + lane;
+    if (lane < R && row < p.N)
+      for (uint32_t j = 0; j < p.tp; ++j) st_peer(p.peer_out[j] + (size_t)p.rank * p.N + row, make_uint2(__float_as_uint(mine), pos));
   } else if (EPI == EPI_SWIGLU) {
     const uint32_t o = grp * PAIRS + lane;
     if (lane < PAIRS && o < p.N) p.y[o] = (mine / (1.0f + expf(-mine))) * partner;
@@ -534,28 +590,36 @@ __device__ __forceinline__ void load_slot_values(const float *xf, const __half *
 //  - otherwise: the RMS, if any, in a pass of its own, then one rolled loop over the blocks.
 // The kernel's instruction count per warp is of the order of its code size, so code executed once is
 // kept small: two unrolled passes, not one per possible K.
-template <int FMT>
+template <int FMT, bool PEER>
 __device__ void stage_fixed_point(const GemvParams &p, uint32_t m, uint32_t *xq, float *red) {
   const uint32_t K = p.K, nb = K / 32;
   const float *xf = p.x_is_f16 ? nullptr : reinterpret_cast<const float *>(p.x) + (size_t)m * K;
   const __half *xh = p.x_is_f16 ? reinterpret_cast<const __half *>(p.x) + (size_t)m * K : nullptr;
   const int j = threadIdx.x & 7;
   const uint32_t b0 = threadIdx.x >> 3;
-  if (p.gamma && nb <= 128) {
-    float v[2][4], gm[2][4];
+  constexpr int NPR = PEER ? 4 : 2;  // passes kept in registers (the peer form has no other path: K <= 8192)
+  if ((p.gamma && nb <= 64 * NPR) || PEER) {
+    float v[NPR][4], gm[NPR][4];
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < NPR; ++i) {
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         v[i][k] = 0.f;
         gm[i][k] = 0.f;
       }
-      if (b0 + 64 * i < nb) load_slot_values<FMT>(xf, xh, p.gamma, b0 + 64 * i, j, v[i], gm[i]);
+      if (b0 + 64 * i < nb) {
+        load_slot_values<FMT>(xf, xh, p.gamma, b0 + 64 * i, j, v[i], gm[i]);
+        if (PEER) {
+          const uint32_t idx = (b0 + 64 * i) * 32 + slot_element<FMT>(4 * j);
+          add_peer_partials(p, idx, peer_tag(p), v[i]);
+          if (blockIdx.x == 0) *reinterpret_cast<float4 *>(p.x_out + idx) = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+        }
+      }
     }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < 2; ++i)
+    for (int i = 0; i < NPR; ++i)
 #pragma unroll
       for (int k = 0; k < 4; ++k) ss = fmaf(v[i][k], v[i][k], ss);
     ss = warp_sum(ss);
@@ -565,10 +629,10 @@ __device__ void stage_fixed_point(const GemvParams &p, uint32_t m, uint32_t *xq,
     t = warp_sum(t);
     const float inv = rsqrtf(t / (float)K + p.eps);
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < NPR; ++i) {
 #pragma unroll
       for (int k = 0; k < 4; ++k) v[i][k] = (v[i][k] * inv) * gm[i][k];
-      if (i == 0 || nb > 64) quantize_store<FMT>(v[i], xq, b0 + 64 * i, j, b0 + 64 * i < nb);
+      if ((uint32_t)(64 * i) < nb) quantize_store<FMT>(v[i], xq, b0 + 64 * i, j, b0 + 64 * i < nb);
     }
     return;
   }

@@ -304,8 +304,22 @@ bool BlockScheduler::lm_head(const float *x_row, std::string *err) {
   return true;
 }
 
-// The five decode kernels of every layer, reading the position from d_pos.
-bool BlockScheduler::decode_layers(std::string *err) {
+bool BlockScheduler::set_peer_exchange(const greta_peer_exchange &ex, std::string *err) {
+  const ModelConfig &c = config_;
+  if (ex.tp != c.tp_size || ex.rank != c.tp_rank) return fail(err, "set_peer_exchange: group does not match the model's tensor-parallel rank");
+  if (c.dim > 8192 || 2 * c.num_layers > 256) return fail(err, "set_peer_exchange: model too large for the exchange tags");
+  if (!all_reduce_) return fail(err, "set_peer_exchange: install the all-reduce hook first (barriers, last layer, logits)");
+  if (!x_alt_.allocate((size_t)c.dim * 4, BufferUsage::DeviceOnly, GretaDataType::FP32, err)) return false;
+  peer_ = ex;
+  return true;
+}
+
+// The five decode kernels of every layer, reading the position from d_pos.  With fused_exchange the
+// row-parallel projections scatter their partial products into every rank's slots and the next operator
+// sums them while it stages its input; the residual stream then alternates between two buffers and
+// *x_final tells where the last layer left it.  The last down-projection keeps the all-reduce: the LM head
+// that follows is not an exchange consumer.
+bool BlockScheduler::decode_layers(std::string *err, bool fused_exchange, const float **x_final) {
   const ModelConfig &c = config_;
   ActivationBuffers &a = activations_;
   cudaStream_t s = H(stream_);
@@ -316,6 +330,55 @@ bool BlockScheduler::decode_layers(std::string *err) {
   const uint32_t *dpos = static_cast<const uint32_t *>(a.d_pos.data());
   float *x = static_cast<float *>(a.x.data());
   const bool tp = c.tp_size > 1;
+  if (fused_exchange) {
+    if (!tp || peer_.tp != c.tp_size) return fail(err, "decode_layers: no peer exchange installed");
+    float *cur = x, *other = static_cast<float *>(x_alt_.data());
+    for (uint32_t l = 0; l < c.num_layers; ++l) {
+      BlockBuffers &b = blocks_[l];
+      uint16_t *kc = static_cast<uint16_t *>(a.kv_cache_k.data()) + l * cache_l;
+      uint16_t *vc = static_cast<uint16_t *>(a.kv_cache_v.data()) + l * cache_l;
+      if (l == 0) {
+        GRETA_TRY(greta_cuda_fused_rmsnorm_qkv_rope_kv(s, fmt, cur, static_cast<const float *>(b.attn_norm.data()), c.rms_eps, b.wq.data(),
+                                                       b.s_wq.data(), b.wk.data(), b.s_wk.data(), b.wv.data(), b.s_wv.data(),
+                                                       static_cast<float *>(a.q.data()), nullptr, nullptr, kc, vc, dpos, heads_l_, kv_heads_l_,
+                                                       Dh, (uint32_t)max_seq_, c.rope_base, D),
+                  "fused qkv");
+      } else {  // consumes the down-projection partials of layer l - 1
+        GRETA_TRY(greta_cuda_fused_rmsnorm_qkv_rope_kv_peer(s, fmt, cur, other, &peer_, 2 * l - 1, static_cast<const float *>(b.attn_norm.data()),
+                                                            c.rms_eps, b.wq.data(), b.s_wq.data(), b.wk.data(), b.s_wk.data(), b.wv.data(),
+                                                            b.s_wv.data(), static_cast<float *>(a.q.data()), kc, vc, dpos, heads_l_, kv_heads_l_,
+                                                            Dh, (uint32_t)max_seq_, c.rope_base, D),
+                  "fused qkv (exchange)");
+        std::swap(cur, other);
+      }
+      GRETA_TRY(greta_cuda_attn_decode(s, static_cast<const float *>(a.q.data()), kc, vc, static_cast<float *>(a.attn_out.data()), dpos, 0, heads_l_,
+                                       kv_heads_l_, Dh, (uint32_t)max_seq_, scale, a.attn_scratch.data(), a.attn_scratch.size()),
+                "attention decode");
+      GRETA_TRY(greta_cuda_gemv_peer_scatter(s, fmt, static_cast<const float *>(a.attn_out.data()), b.wo.data(), b.s_wo.data(), &peer_, 2 * l, dpos, D,
+                                             ql),
+                "wo (exchange)");
+      GRETA_TRY(greta_cuda_fused_ffn_front_peer(s, fmt, cur, other, &peer_, 2 * l, dpos, static_cast<const float *>(b.ffn_norm.data()), c.rms_eps,
+                                                b.w1.data(), b.s_w1.data(), b.w3.data(), b.s_w3.data(), static_cast<float *>(a.mlp_gate.data()), D,
+                                                hidden_l_),
+                "ffn front (exchange)");
+      std::swap(cur, other);
+      if (l + 1 < c.num_layers) {
+        GRETA_TRY(greta_cuda_gemv_peer_scatter(s, fmt, static_cast<const float *>(a.mlp_gate.data()), b.w2.data(), b.s_w2.data(), &peer_, 2 * l + 1,
+                                               dpos, D, hidden_l_),
+                  "w2 (exchange)");
+      } else {
+        if (c.tp_rank == 0)
+          GRETA_TRY(greta_cuda_gemv_residual(s, fmt, static_cast<const float *>(a.mlp_gate.data()), b.w2.data(), b.s_w2.data(), cur, cur, D, hidden_l_),
+                    "w2");
+        else
+          GRETA_TRY(greta_cuda_gemv(s, fmt, a.mlp_gate.data(), 0, b.w2.data(), b.s_w2.data(), cur, 1, D, hidden_l_), "w2");
+        if (all_reduce_(cur, D, s) != 0) return fail(err, "all-reduce after the last down-projection failed");
+      }
+    }
+    if (x_final) *x_final = cur;
+    return true;
+  }
+  if (x_final) *x_final = x;
   for (uint32_t l = 0; l < c.num_layers; ++l) {
     BlockBuffers &b = blocks_[l];
     uint16_t *kc = static_cast<uint16_t *>(a.kv_cache_k.data()) + l * cache_l;
@@ -479,6 +542,14 @@ bool BlockScheduler::begin_decode(int32_t first_token, size_t pos, std::string *
   GRETA_TRY(greta_cuda_memcpy_h2d_sync(a.d_pos.data(), init, 16), "begin_decode");
   GRETA_TRY(greta_cuda_memcpy_h2d_sync(a.d_next.data(), tok, 16), "begin_decode");
   decode_steps_ = 0;
+  if (peer_.tp > 1) {
+    // Exchange tags grow with the position: a session that restarts earlier must not meet the tags of the
+    // last one.  Every rank clears its slots, then a collective keeps anyone from storing into a buffer
+    // that is still being cleared.
+    GRETA_TRY(greta_cuda_memset(peer_.slots[peer_.rank], 0, greta_cuda_peer_slot_bytes(peer_.tp, config_.dim), s), "exchange reset");
+    if (all_reduce_(static_cast<float *>(logits_.data()), 1, s) != 0) return fail(err, "begin_decode: barrier failed");
+    GRETA_TRY(greta_cuda_stream_synchronize(s), "begin_decode");
+  }
   if (!graph_captured_) {
     const ModelConfig &c = config_;
     // The step is a graph of the per-layer operators chained by programmatic dependent launch.
@@ -493,6 +564,7 @@ bool BlockScheduler::begin_decode(int32_t first_token, size_t pos, std::string *
     graph_ = gcore::rt::GretaContext::instance().create_graph();
     graph_->capture_start(stream_);
     bool ok;
+    const float *x_last = static_cast<const float *>(a.x.data());
     if (persistent_step_) {
       ok = greta_cuda_decode_layers(s, &desc, decode_plan_.data()) == GRETA_OK;
       if (!ok && err) *err = gcore::host::cuda_error("decode_layers");
@@ -500,9 +572,9 @@ bool BlockScheduler::begin_decode(int32_t first_token, size_t pos, std::string *
       ok = greta_cuda_embedding(s, static_cast<const int32_t *>(a.d_next.data()), token_embd_.data(), 1, static_cast<float *>(a.x.data()), 1,
                                 c.dim, c.vocab_size) == GRETA_OK;
       if (ok && c.tp_size > 1) ok = greta_cuda_memset(logits_.data(), 0, logits_.size(), s) == GRETA_OK;
-      ok = ok && decode_layers(err);
+      ok = ok && decode_layers(err, peer_.tp > 1, &x_last);
     }
-    ok = ok && lm_head(static_cast<const float *>(a.x.data()), err);
+    ok = ok && lm_head(x_last, err);
     uint32_t *dp = static_cast<uint32_t *>(a.d_pos.data());
     ok = ok && greta_cuda_argmax_advance(s, static_cast<const float *>(logits_.data()), c.vocab_size, static_cast<int32_t *>(a.d_next.data()), dp,
                                          static_cast<int32_t *>(a.out_tokens.data()), dp + 1, (uint32_t)max_seq_) == GRETA_OK;

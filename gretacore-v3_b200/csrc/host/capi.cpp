@@ -174,6 +174,12 @@ int greta_model_decode_e2e(greta_model_t m, int32_t first_token, uint32_t pos, u
 int greta_model_decode_trace(greta_model_t m, long long *out25) { return done(M(m)->sched.decode_trace(out25), "decode_trace failed"); }
 uint64_t greta_model_weight_bytes(greta_model_t m) { return M(m)->sched.weight_bytes(); }
 void *greta_model_stream(greta_model_t m) { return static_cast<gcore::rt::cuda::GretaStreamCuda *>(M(m)->sched.stream())->handle(); }
+int greta_model_set_peer_exchange(greta_model_t m, const greta_peer_exchange *ex) {
+  if (!ex) return done(false, "model_set_peer_exchange: null descriptor");
+  std::string err;
+  return done(M(m)->sched.set_peer_exchange(*ex, &err), err);
+}
+
 int greta_model_set_comm(greta_model_t m, void *comm) {
   if (!comm) return done(false, "model_set_comm: null communicator");
   M(m)->sched.set_all_reduce([comm](float *buf, size_t count, cudaStream_t stream) { return greta_cuda_comm_allreduce_f32(comm, buf, count, stream); });

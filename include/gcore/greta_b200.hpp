@@ -21,6 +21,8 @@
 #include <string>
 #include <vector>
 
+#include "../greta_cuda.h"
+
 struct CUstream_st;
 typedef CUstream_st *cudaStream_t;  // same declaration as the CUDA runtime's
 
@@ -416,11 +418,14 @@ public:
   size_t num_layers() const { return blocks_.size(); }
   gcore::rt::GretaStream *stream() { return stream_; }
   void set_all_reduce(AllReduceFn fn) { all_reduce_ = std::move(fn); }
+  // Tensor-parallel decode with the exchange fused into the operators over peer memory (greta_cuda.h,
+  // greta_peer_exchange): used by the captured decode step; forward() keeps the all-reduce hook.
+  bool set_peer_exchange(const greta_peer_exchange &ex, std::string *err);
   uint64_t weight_bytes() const { return weight_bytes_; }
   bool decode_trace(long long *out25);
 
 private:
-  bool decode_layers(std::string *err);
+  bool decode_layers(std::string *err, bool fused_exchange = false, const float **x_final = nullptr);
   bool build_decode_plan(std::string *err);
   bool lm_head(const float *x_row, std::string *err);
   ModelConfig config_;
@@ -434,6 +439,8 @@ private:
   bool graph_captured_ = false, initialized_ = false;
   size_t decode_steps_ = 0, max_seq_ = 0;
   AllReduceFn all_reduce_;
+  greta_peer_exchange peer_{};            // tp == 0: not installed
+  gcore::rt::cuda::Buffer x_alt_;         // second copy of the residual stream for the fused exchange
   uint64_t weight_bytes_ = 0;
   // local (per-rank) shapes
   uint32_t heads_l_ = 0, kv_heads_l_ = 0, hidden_l_ = 0, vocab_l_ = 0;

@@ -327,6 +327,44 @@ GRETA_API int greta_cuda_comm_destroy(void *comm);
 /* In-place sum over ranks of `count` floats, enqueued on `stream` (capturable into a graph). */
 GRETA_API int greta_cuda_comm_allreduce_f32(void *comm, float *buf, size_t count, greta_stream_t stream);
 
+/* ---- Tensor-parallel exchange fused into the operators, over peer memory (NVLink) ----------------
+ * The reference has no counterpart (it is single-GPU); this replaces "row-parallel projection, then
+ * all-reduce, then the next operator's RMSNorm" of a Megatron-sharded decoder layer (SURVEY hot-path row e)
+ * by two kernels and no collective launch:
+ *   producer  greta_cuda_gemv_peer_scatter: y_r = x W_r^T, every element stored as {value, tag} straight into
+ *             slot r of EVERY rank's slot buffer (plain 8-byte stores over NVLink; no flag, no fence: the tag
+ *             travels with the value);
+ *   consumer  ..._peer forms of the fused QKV and FFN-front operators: the activation staging waits (bounded)
+ *             for the tp tagged partials in the local slot buffer, adds them to the residual stream x_in in
+ *             rank order (bit-identical on every rank), normalises and goes on; CTA 0 writes the new stream
+ *             to x_out (a different buffer from x_in).
+ * Tags are ((*d_pos + 1) << 8) | exch_idx: they grow with the position, so a slot buffer must be zeroed,
+ * on every rank and with a barrier after it, whenever a decode session restarts at an earlier position.
+ * Consecutive exchanges must alternate exch_idx parity (two halves of the slot buffer), or be separated by
+ * a collective.  A wait that gives up sets a status word (greta_cuda_peer_status) and uses what it has.
+ * Slot buffers are plain device allocations shared between the processes with the ipc calls below. */
+typedef struct greta_peer_exchange {
+  uint32_t tp, rank; /* ranks of the group (<= 8), this rank */
+  void *slots[8];    /* slot buffer of every rank, greta_cuda_peer_slot_bytes(tp, dim) each; slots[rank] is local */
+} greta_peer_exchange;
+GRETA_API size_t greta_cuda_peer_slot_bytes(uint32_t tp, uint32_t dim);
+GRETA_API int greta_cuda_peer_status(int *code);
+GRETA_API int greta_cuda_ipc_export(void *device_ptr, void *handle64);         /* 64-byte handle of a greta_cuda_malloc block */
+GRETA_API int greta_cuda_ipc_open(const void *handle64, void **device_ptr);    /* maps another process's block */
+GRETA_API int greta_cuda_ipc_close(void *device_ptr);
+GRETA_API int greta_cuda_gemv_peer_scatter(greta_stream_t stream, int fmt, const float *x, const void *qs, const void *d,
+                                           const greta_peer_exchange *ex, uint32_t exch_idx, const uint32_t *d_pos, uint32_t N, uint32_t K);
+GRETA_API int greta_cuda_fused_rmsnorm_qkv_rope_kv_peer(greta_stream_t stream, int fmt, const float *x_in, float *x_out,
+                                                        const greta_peer_exchange *ex, uint32_t exch_idx, const float *gamma, float eps,
+                                                        const void *wq_qs, const void *wq_d, const void *wk_qs, const void *wk_d,
+                                                        const void *wv_qs, const void *wv_d, float *q_out, void *k_cache, void *v_cache,
+                                                        const uint32_t *d_pos, uint32_t H, uint32_t Hkv, uint32_t Dh, uint32_t max_seq,
+                                                        float rope_base, uint32_t D);
+GRETA_API int greta_cuda_fused_ffn_front_peer(greta_stream_t stream, int fmt, const float *x_in, float *x_out,
+                                              const greta_peer_exchange *ex, uint32_t exch_idx, const uint32_t *d_pos, const float *gamma,
+                                              float eps, const void *w1_qs, const void *w1_d, const void *w3_qs, const void *w3_d, float *y,
+                                              uint32_t D, uint32_t F);
+
 #ifdef __cplusplus
 }
 #endif

@@ -13,6 +13,8 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#include "greta_cuda.h"
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -75,6 +77,9 @@ GRETA_API uint64_t greta_model_weight_bytes(greta_model_t m);
 GRETA_API void *greta_model_stream(greta_model_t m);
 /* Installs the tensor-parallel exchange: an NCCL communicator made with greta_cuda_comm_init. */
 GRETA_API int greta_model_set_comm(greta_model_t m, void *comm);
+/* Installs the fused tensor-parallel exchange for the decode step (greta_cuda.h: greta_peer_exchange); call after
+ * greta_model_set_comm, whose all-reduce still serves prefill, the last layer, the logits and the session barrier. */
+GRETA_API int greta_model_set_peer_exchange(greta_model_t m, const greta_peer_exchange *ex);
 
 #ifdef __cplusplus
 }

@@ -1,6 +1,7 @@
 """One rank of the tensor-parallel check (launched by test_tp_gpu.py under torch.distributed.run).
-Each rank holds its shard of a small Llama-shaped model, runs prefill + greedy decode with the NCCL
-exchange installed, and rank 0 compares the ids with the CPU oracle's."""
+Each rank holds its shard of a small Llama-shaped model and runs prefill + greedy decode twice: with the NCCL
+all-reduce, and with the exchange fused into the GEMV kernels over peer memory; rank 0 compares the ids of both
+with the CPU oracle's and reads the exchange's time-out status."""
 import ctypes as C
 import json
 import os
@@ -31,15 +32,27 @@ def main():
     comm = C.c_void_p()
     g.check(lib.greta_cuda_comm_init(C.byref(comm), C.create_string_buffer(raw, 128), ranks.world, ranks.rank), "comm_init")
     seed, n_new = 9, 16
-    m = pkg.model.Model(CFG, tp_rank=ranks.rank, tp_size=ranks.world)
-    m.set_comm(comm)
-    m.load_synthetic(seed)
     out = {}
-    for plen in (12, 40):                       # GEMV-route prefill and tensor-core prefill
-        prompt = pkg.model.synth_tokens(seed, plen, CFG["vocab"])
-        ids, _ = m.generate(prompt, n_new)
-        out[str(plen)] = ids
-    ranks.barrier()
+    for mode in ("nccl", "fused"):
+        m = pkg.model.Model(CFG, tp_rank=ranks.rank, tp_size=ranks.world)
+        m.set_comm(comm)
+        keep = bench.install_peer_exchange(pkg, m, ranks, CFG["dim"]) if mode == "fused" else None
+        m.load_synthetic(seed)
+        for plen in (12, 40, 12):               # GEMV-route prefill, tensor-core prefill, and a session that restarts earlier
+            prompt = pkg.model.synth_tokens(seed, plen, CFG["vocab"])
+            ids, _ = m.generate(prompt, n_new)
+            if out.setdefault(mode + str(plen), ids) != ids:
+                out["repeat_mismatch"] = True
+        ranks.barrier()
+        m.close()
+        if keep:
+            code = C.c_int(-1)
+            g.check(lib.greta_cuda_peer_status(C.byref(code)))
+            out["peer_status"] = code.value
+            for ptr in keep[2]:
+                g.check(lib.greta_cuda_ipc_close(ptr))
+            ranks.barrier()
+            keep[0].free()
     if ranks.rank == 0:
         from oracle import oracle as O
         weights = pkg.model.synth_weights(CFG, seed)
@@ -47,11 +60,10 @@ def main():
         for plen in (12, 40):
             prompt = pkg.model.synth_tokens(seed, plen, CFG["vocab"])
             want, gaps = O.Model(CFG, weights).generate(prompt, n_new)
-            ok = ok and out[str(plen)] == want and min(gaps) > 1e-6
+            ok = ok and out["nccl" + str(plen)] == want and out["fused" + str(plen)] == want and min(gaps) > 1e-6
             out["want" + str(plen)] = want
-        out["ok"] = bool(ok)
+        out["ok"] = bool(ok) and out.get("peer_status") == 0 and not out.get("repeat_mismatch")
         print("TP_RESULT " + json.dumps(out), flush=True)
-    m.close()
     g.check(lib.greta_cuda_comm_destroy(comm))
 
 
