@@ -278,7 +278,7 @@ def time_dominant_kernel(pkg, cfg, tp, reps=4):
     qs_h = rng.integers(0, 256, nb * 16, dtype=np.uint8)
     d_h = (np.abs(rng.normal(0, 0.02, nb)) / 8).astype(np.float16).view(np.uint16)
     sets = [(g.DeviceBuffer.from_numpy(qs_h), g.DeviceBuffer.from_numpy(d_h), g.DeviceBuffer.from_numpy(qs_h),
-             g.DeviceBuffer.from_numpy(d_h)) for _ in range(L)]
+             g.DeviceBuffer.from_numpy(d_h)) for _ in range(max(4, min(L, int(4e9 // (2 * nb * 18)))))]   # >> L2, at most ~4 GB
     x = g.DeviceBuffer.from_numpy(rng.normal(0, 1, D).astype(np.float32))
     gam = g.DeviceBuffer.from_numpy(np.ones(D, np.float32))
     y = g.DeviceBuffer(F * 4)
@@ -308,7 +308,7 @@ def time_dominant_kernel(pkg, cfg, tp, reps=4):
     lib.greta_cuda_event_synchronize(e1)
     ms = C.c_float()
     lib.greta_cuda_event_elapsed_ms(e0, e1, C.byref(ms))
-    us = ms.value * 1e3 / (reps * L)
+    us = ms.value * 1e3 / (reps * len(sets))
     alg_bytes = 2 * nb * 18 + 2 * D * 4 + F * 4          # both weight matrices + x + gamma in, y out
     for s in sets:
         for b in s:
@@ -393,6 +393,9 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
     ap.add_argument("--prefill-chunk", type=int, default=0, help="tokens per prefill call (0 = the whole prompt at once)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", choices=["c4", "c5-batch1"], default="c4",
+                    help="c4: BASELINE config 4 (7B shape, the metric's workload); c5-batch1: the 70B shape of config 5 at batch 1 "
+                         "(config 5 itself is batch 16, which this path does not have)")
     ap.add_argument("--exchange", choices=["fused", "nccl"], default="fused",
                     help="tensor-parallel exchange of the decode step: fused into the GEMV kernels over peer memory, or NCCL all-reduce")
     ap.add_argument("--case", default=None, help="run a small single-kernel case (gemv_swiglu, gemv_plain, gemm_c2, attn_decode, decode_step) and exit")
@@ -405,8 +408,8 @@ def main():
     if args.case:
         run_case(pkg, args.case)
         return
-    from gretacore_v3_b200.model import LLAMA2_7B
-    cfg = dict(LLAMA2_7B)
+    from gretacore_v3_b200.model import LLAMA2_7B, LLAMA3_70B
+    cfg = dict(LLAMA2_7B if args.workload == "c4" else LLAMA3_70B)
     if args.impl == "reference":
         run_reference(args, ranks, cfg)
         return
@@ -480,14 +483,19 @@ def main():
     # whole-step view of the same bound: bytes one decode step must read
     step_bytes = model_step_bytes(cfg, pos + args.steps // 2)
     out = {
-        "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "metric": METRIC if args.workload == "c4" else "decode_tokens_per_s_llama3_70b_shape_q4_0_batch1",
+        "value": tok_s, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "q4_0 weights (int8 dot products on 23-bit fixed-point activations), fp32 accumulation, fp16 KV cache",
         "data": "synthetic",
-        "config": {"workload": "Llama-2-7B-shaped model (32 layers, hidden 4096, 32 heads x 128, FFN 11008, vocab 32000), random-init "
-                               "Q4_0 weights, fp16 LM head, 512-token random prompt then greedy decode at batch 1 (BASELINE config 4)",
+        "config": {"workload": ("Llama-2-7B-shaped model (32 layers, hidden 4096, 32 heads x 128, FFN 11008, vocab 32000), random-init "
+                                "Q4_0 weights, fp16 LM head, 512-token random prompt then greedy decode at batch 1 (BASELINE config 4)"
+                                if args.workload == "c4" else
+                                "Llama-3-70B-shaped model (80 layers, hidden 8192, GQA 64/8 heads x 128, FFN 28672, vocab 128256), random-init "
+                                "Q4_0 weights, fp16 LM head, random prompt then greedy decode at BATCH 1 (the shape of BASELINE config 5, "
+                                "not its batch of 16)"),
                    "prompt_len": args.prompt_len, "parallelism": (f"tp{tp}, exchange {args.exchange}" if tp > 1 else "single GPU"),
-                   "l2_defeat": "every step streams 3.9 GB of distinct weights (L2 is 126 MB)", "seed": SEED},
+                   "l2_defeat": f"every step streams {model_step_bytes(cfg, pos) / 1e9:.1f} GB of distinct weights (L2 is 126 MB)", "seed": SEED},
         "clocks": clocks, "gpu_launches": int(launches),
         "e2e": {"value": 1e3 * args.steps / ms_e2e, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4,
                 "ids_match_device_loop": bool(same)},

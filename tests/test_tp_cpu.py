@@ -36,8 +36,10 @@ def _rank_main(rank, world, port, q):
     uid = bytes(range(128)) if rank == 0 else b"\0" * 128
     got = ranks.bcast(uid, 128)
     ranks.barrier()
-    # 2. max over ranks lands on rank 0
+    # 2. max over ranks lands on rank 0; the all-gather that swaps the exchange buffers' IPC handles
     mx = ranks.gather_max(10.0 + rank)
+    handles = ranks.allgather(bytes([rank + 1]) * 64)
+    assert handles == [bytes([r + 1]) * 64 for r in range(world)]
     # 3. column-parallel gate (rows split) then row-parallel down (K split), partial sums exchanged through rank 0
     rng = np.random.default_rng(5)
     D, F = CFG["dim"], CFG["hidden_dim"]
@@ -81,6 +83,18 @@ def test_two_rank_rendezvous_and_tensor_parallel_algebra():
     F, D = CFG["hidden_dim"], CFG["dim"]
     assert a1[:4] == [F // 2, D, F, D] and b1[4] == F // 2 and a1[4] == 0            # gate: rows split
     assert a2[:4] == [D, F // 2, D, F] and b2[5] == F // 2 and a2[5] == 0            # down: whole blocks of K split
+
+
+def test_exchange_tags_grow_and_halves_alternate():
+    """The rules the fused tensor-parallel exchange relies on (include/greta_cuda.h): tags ((pos + 1) << 8) | idx are
+    never zero (a cleared slot matches nothing), grow strictly along a decode session, and the exchanges of a step
+    (O-projection 2l, down-projection 2l + 1, the last down-projection left to the all-reduce) alternate slot halves."""
+    layers = 32
+    seq = [((pos + 1) << 8) | idx for pos in range(510, 520) for idx in range(2 * layers - 1)]
+    assert all(t > 0 for t in seq) and all(b > a for a, b in zip(seq, seq[1:]))
+    step = list(range(2 * layers - 1))
+    assert all((a & 1) != (b & 1) for a, b in zip(step, step[1:]))
+    assert max(step) < 256 and ((2047 + 1) << 8 | 255) < 2 ** 32
 
 
 def test_shards_tile_every_projection():
