@@ -260,6 +260,99 @@ def test_fused_ffn_front(g, name, D, F):
     assert max_abs_rel(y.download(np.float32), want) < TIGHT
 
 
+# ----------------------------------------------------------------------------- tensor-parallel exchange (one GPU)
+def _exchange(g, tp, rank, slot_ptrs):
+    from gretacore_v3_b200.model import PeerExchange
+    ex = PeerExchange()
+    ex.tp, ex.rank = tp, rank
+    for j, ptr in enumerate(slot_ptrs):
+        ex.slots[j] = ptr
+    return ex
+
+
+@pytest.mark.parametrize("name", ["q4_0", "q8_0"])
+@pytest.mark.parametrize("tp", [1, 2, 3])
+def test_fused_exchange_operators_on_one_gpu(g, name, tp):
+    """The fused tensor-parallel exchange with every 'rank' on this GPU: tp row-parallel projections (columns of W
+    split in whole blocks) scatter their tagged partials into tp slot buffers, one after the other; then each
+    rank's consumer (fused FFN front, fused QKV) must see x + the sum of the partials, write it to x_out, and
+    compute on it what the plain operators compute.  Two exchanges (both halves of the slot buffer) at one position."""
+    lib = g.cuda()
+    ofmt, gfmt = FMTS[name]
+    rng = np.random.default_rng(70 + tp)
+    D, Kfull, F, H, Hkv, Dh, pos, max_seq = 512, 96 * tp, 200, 4, 2, 64, 5, 8
+    x = rng.normal(0, 1, D).astype(np.float32)
+    a = rng.normal(0, 1, Kfull).astype(np.float32)
+    gamma = rng.normal(1, 0.1, D).astype(np.float32)
+    wo = make_blocks(rng, ofmt, D, Kfull)
+    b1, b3 = make_blocks(rng, ofmt, F, D), make_blocks(rng, ofmt, F, D)
+    bq, bk, bv = (make_blocks(rng, ofmt, n, D) for n in (H * Dh, Hkv * Dh, Hkv * Dh))
+    bb = wo.size // (D * (Kfull // 32))                       # bytes per GGUF block
+    shards = [np.ascontiguousarray(wo.reshape(D, Kfull // 32, bb)[:, r * 3:(r + 1) * 3]).reshape(-1) for r in range(tp)]
+    slots = [g.DeviceBuffer(lib.greta_cuda_peer_slot_bytes(tp, D), zero=True) for _ in range(tp)]
+    _KEEP.extend(slots)
+    dpos = _dev(g, np.array([pos], np.uint32))
+    xd, gd = _dev(g, x), _dev(g, gamma)
+    w1, w3 = g.Weight(b1, gfmt, F, D), g.Weight(b3, gfmt, F, D)
+    wq, wk, wv = g.Weight(bq, gfmt, H * Dh, D), g.Weight(bk, gfmt, Hkv * Dh, D), g.Weight(bv, gfmt, Hkv * Dh, D)
+    keep = [w1, w3, wq, wk, wv]                               # weights stay alive until the end of the test
+    x_sum = x.astype(np.float64) + O.gemv(a, wo, ofmt, D, Kfull)[0]
+    for idx in (0, 1):                                        # exchange 0 feeds the FFN front, exchange 1 the QKV operator
+        for r in range(tp):                                   # the producers of all ranks, one after the other
+            ws = g.Weight(shards[r], gfmt, D, 96)
+            keep.append(ws)
+            ex = _exchange(g, tp, r, [b.ptr for b in slots])
+            g.check(lib.greta_cuda_gemv_peer_scatter(None, gfmt, _dev(g, a[r * 96:(r + 1) * 96]).ptr, ws.qs.ptr, ws.d.ptr, C.byref(ex), idx,
+                                                     dpos.ptr, D, 96))
+        for r in range(tp):                                   # every rank's consumer reads its own slot buffer
+            ex = _exchange(g, tp, r, [b.ptr for b in slots])
+            x_out = _nan_buffer(g, D)
+            _KEEP.append(x_out)
+            if idx == 0:
+                y = _nan_buffer(g, F)
+                g.check(lib.greta_cuda_fused_ffn_front_peer(None, gfmt, xd.ptr, x_out.ptr, C.byref(ex), idx, dpos.ptr, gd.ptr, 1e-5, w1.qs.ptr,
+                                                            w1.d.ptr, w3.qs.ptr, w3.d.ptr, y.ptr, D, F))
+                got_x = x_out.download(np.float32)
+                xn = O.rmsnorm(got_x.reshape(1, D), gamma, 1e-5)
+                want = O.silu_mul(O.gemv(xn, b1, ofmt, F, D), O.gemv(xn, b3, ofmt, F, D)).ravel()
+                assert max_abs_rel(y.download(np.float32), want) < TIGHT
+            else:
+                q_out = _nan_buffer(g, H * Dh)
+                kc = g.DeviceBuffer(Hkv * max_seq * Dh * 2, zero=True)
+                vc = g.DeviceBuffer(Hkv * max_seq * Dh * 2, zero=True)
+                g.check(lib.greta_cuda_fused_rmsnorm_qkv_rope_kv_peer(
+                    None, gfmt, xd.ptr, x_out.ptr, C.byref(ex), idx, gd.ptr, 1e-5, wq.qs.ptr, wq.d.ptr, wk.qs.ptr, wk.d.ptr, wv.qs.ptr,
+                    wv.d.ptr, q_out.ptr, kc.ptr, vc.ptr, dpos.ptr, H, Hkv, Dh, max_seq, 10000.0, D))
+                got_x = x_out.download(np.float32)
+                xn = O.rmsnorm(got_x.reshape(1, D), gamma, 1e-5)
+                q = O.rope(O.gemv(xn, bq, ofmt, H * Dh, D), 1, H, Dh, 10000.0, pos).ravel()
+                assert max_abs_rel(q_out.download(np.float32), q) < 5e-4
+                v = O.gemv(xn, bv, ofmt, Hkv * Dh, D).ravel()
+                assert max_abs_rel(O.f16_bits_to_f32(vc.download(np.uint16).reshape(Hkv, max_seq, Dh)[:, pos, :].ravel()), v) < 1e-3   # fp16 cache row
+            assert max_abs_rel(got_x, x_sum) < TIGHT           # residual stream + sum of the partials
+            if r:
+                assert np.array_equal(got_x, first_x)          # bit-identical on every rank
+            first_x = got_x
+    code = C.c_int(-1)
+    g.check(lib.greta_cuda_peer_status(C.byref(code)))
+    assert code.value == 0
+
+
+def test_fused_exchange_rejects_bad_descriptors(g):
+    lib = g.cuda()
+    buf = g.DeviceBuffer(1 << 16, zero=True)
+    ok = _exchange(g, 1, 0, [buf.ptr])
+    args = (None, g.FMT_Q4_0, buf.ptr, buf.ptr, buf.ptr)
+    assert lib.greta_cuda_gemv_peer_scatter(*args, None, 0, buf.ptr, 64, 64) == 4                              # no descriptor
+    assert lib.greta_cuda_gemv_peer_scatter(*args, C.byref(ok), 0, None, 64, 64) == 4                          # no position
+    assert lib.greta_cuda_gemv_peer_scatter(*args, C.byref(_exchange(g, 9, 0, [buf.ptr])), 0, buf.ptr, 64, 64) == 4   # tp > 8
+    assert lib.greta_cuda_gemv_peer_scatter(*args, C.byref(_exchange(g, 2, 0, [buf.ptr])), 0, buf.ptr, 64, 64) == 4   # missing slot buffer
+    assert lib.greta_cuda_gemv_peer_scatter(*args, C.byref(ok), 256, buf.ptr, 64, 64) == 4                     # exchange index
+    assert lib.greta_cuda_gemv_peer_scatter(None, g.FMT_F16, buf.ptr, buf.ptr, None, C.byref(ok), 0, buf.ptr, 64, 64) == 4   # format
+    assert lib.greta_cuda_fused_ffn_front_peer(None, g.FMT_Q4_0, buf.ptr, buf.ptr, C.byref(ok), 0, buf.ptr, buf.ptr, 1e-5, buf.ptr, buf.ptr,
+                                               buf.ptr, buf.ptr, buf.ptr, 64, 64) == 4                         # x_out aliases x_in
+
+
 # ----------------------------------------------------------------------------- attention
 @pytest.mark.parametrize("H,Hkv,Dh,L,max_seq", [(4, 4, 128, 1, 8), (4, 4, 128, 63, 64), (8, 2, 64, 200, 256),
                                                 (32, 32, 128, 2049, 2304), (64, 8, 128, 777, 1024)])
