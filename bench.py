@@ -316,6 +316,73 @@ def time_dominant_kernel(pkg, cfg, tp, reps=4):
     return us, alg_bytes
 
 
+# ----------------------------------------------------------------------------- GEMV bandwidth per projection shape
+def gemv_shapes(pkg):
+    """Times the plain Q4_0 / Q8_0 GEMV on every projection shape of the 7B and 70B models (batch 1): distinct weight
+    copies totalling ~600 MB rotate so nothing is served from L2, launches are captured in one CUDA graph, CUDA events
+    on the launching stream.  Prints one JSON line per shape with GB/s of algorithmic bytes and the fraction of the
+    measured HBM peak."""
+    import ctypes as C
+    g = pkg.ffi
+    lib = g.cuda()
+    peak, peak_src = measured_peak_gbs()
+    stream = C.c_void_p()
+    g.check(lib.greta_cuda_stream_create(C.byref(stream)))
+    e0, e1 = C.c_void_p(), C.c_void_p()
+    lib.greta_cuda_event_create(C.byref(e0))
+    lib.greta_cuda_event_create(C.byref(e1))
+    rng = np.random.default_rng(0)
+    shapes = [("q4_0", g.FMT_Q4_0, n, k) for n, k in [(4096, 4096), (11008, 4096), (4096, 11008), (12288, 4096), (22016, 4096),
+                                                      (8192, 8192), (28672, 8192), (8192, 28672)]]
+    shapes += [("q8_0", g.FMT_Q8_0, 4096, 4096), ("q8_0", g.FMT_Q8_0, 11008, 4096)]
+    for name, fmt, N, K in shapes:
+        pb = g.PAYLOAD_BYTES[fmt]
+        nb = N * (K // 32)
+        wbytes = nb * (pb + 2)
+        copies = max(2, int(600e6 // wbytes))
+        qs_h = rng.integers(0, 256, nb * pb, dtype=np.uint8)
+        d_h = (np.abs(rng.normal(0, 0.02, nb)) / 8).astype(np.float16).view(np.uint16)
+        planes = [(g.DeviceBuffer.from_numpy(qs_h), g.DeviceBuffer.from_numpy(d_h)) for _ in range(copies)]
+        x = g.DeviceBuffer.from_numpy(rng.normal(0, 1, K).astype(np.float32))
+        y = g.DeviceBuffer(N * 4)
+
+        def one_pass():
+            for qs, d in planes:
+                g.check(lib.greta_cuda_gemv(stream, fmt, x.ptr, 0, qs.ptr, d.ptr, y.ptr, 1, N, K))
+
+        one_pass()
+        g.check(lib.greta_cuda_stream_synchronize(stream))
+        graph, ex = C.c_void_p(), C.c_void_p()
+        g.check(lib.greta_cuda_graph_capture_begin(stream))
+        for _ in range(4):
+            one_pass()
+        g.check(lib.greta_cuda_graph_capture_end(stream, C.byref(graph)))
+        g.check(lib.greta_cuda_graph_instantiate(graph, C.byref(ex)))
+        lib.greta_cuda_graph_launch(ex, stream)
+        lib.greta_cuda_stream_synchronize(stream)
+        best = 1e30
+        for _ in range(3):
+            lib.greta_cuda_event_record(e0, stream)
+            lib.greta_cuda_graph_launch(ex, stream)
+            lib.greta_cuda_event_record(e1, stream)
+            lib.greta_cuda_event_synchronize(e1)
+            ms = C.c_float()
+            lib.greta_cuda_event_elapsed_ms(e0, e1, C.byref(ms))
+            best = min(best, ms.value)
+        us = best * 1e3 / (4 * copies)
+        alg = wbytes + K * 4 + N * 4
+        print(json.dumps({"case": "gemv_shapes", "format": name, "N": N, "K": K, "us_per_launch": round(us, 2),
+                          "algorithmic_bytes": alg, "gb_per_s": round(alg / us / 1e3, 1), "frac_of_peak": round(alg / us / 1e3 / peak, 3),
+                          "peak_gb_per_s": peak, "peak_source": f"of {peak_src}"}), flush=True)
+        lib.greta_cuda_graph_exec_destroy(ex)
+        lib.greta_cuda_graph_destroy(graph)
+        for qs, d in planes:
+            qs.free()
+            d.free()
+        x.free()
+        y.free()
+
+
 # ----------------------------------------------------------------------------- small single-kernel cases (for ncu)
 def run_case(pkg, name):
     """A few launches of one kernel on a small case whose data is larger than L2, for profiler captures
@@ -398,13 +465,18 @@ def main():
                          "(config 5 itself is batch 16, which this path does not have)")
     ap.add_argument("--exchange", choices=["fused", "nccl"], default="fused",
                     help="tensor-parallel exchange of the decode step: fused into the GEMV kernels over peer memory, or NCCL all-reduce")
-    ap.add_argument("--case", default=None, help="run a small single-kernel case (gemv_swiglu, gemv_plain, gemm_c2, attn_decode, decode_step) and exit")
+    ap.add_argument("--case", default=None, help="run a small single-kernel case (gemv_swiglu, gemv_plain, gemm_c2, attn_decode, decode_step) and exit; "
+                         "gemv_shapes prints the GEMV bandwidth of every projection shape")
     args = ap.parse_args()
     ranks = Ranks()
     if ranks.world != args.gpus and ranks.world > 1:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={ranks.world}")
 
     pkg = load_pkg()
+    if args.case == "gemv_shapes":
+        pkg.ffi.require_device()
+        gemv_shapes(pkg)
+        return
     if args.case:
         run_case(pkg, args.case)
         return
@@ -501,7 +573,8 @@ def main():
                 "ids_match_device_loop": bool(same)},
         "roofline": roofline,
         "step_hbm": {"bytes_per_step": step_bytes, "achieved_gbs": step_bytes / (ms / args.steps) / 1e6,
-                     "frac_of_peak": step_bytes / (ms / args.steps) / 1e6 / peak},
+                     "frac_of_peak": step_bytes / (ms / args.steps) / 1e6 / (peak * tp),
+                     "note": "aggregate over the N GPUs; the fraction is of N x the measured per-GPU peak"},
     }
     if not args.no_cpu_baseline and tp == 1:                 # reported at N=1 only
         out["cpu_baseline"] = cpu_baseline(cfg)

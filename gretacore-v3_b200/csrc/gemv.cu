@@ -323,13 +323,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemv_pipe_kernel(const GemvParams 
     }
     xrun += 32 * X_BLOCK_BYTES;
     if (++ck == C || c + 1 == c1) {  // group finished for this warp: reduce and publish
-#pragma unroll
-      for (int r = 0; r < R; ++r) acc[r] = warp_sum(acc[r]);
-      if (lane == 0) {
-        float *dst = part + ((size_t)warp * p.slots + (cg - first_grp)) * R;
-#pragma unroll
-        for (int r = 0; r < R; ++r) dst[r] = acc[r];
-      }
+      const float total = warp_sum_rows<R>(acc, lane);  // lanes 0, 8, 16, 24 end up with rows 0..R-1 between them
+      if ((lane & (R == 4 ? 7 : (R == 2 ? 15 : 31))) == 0)
+        part[((size_t)warp * p.slots + (cg - first_grp)) * R + warp_sum_rows_index<R>(lane)] = total;
 #pragma unroll
       for (int r = 0; r < R; ++r) acc[r] = 0.f;
       if (ck == C) {

@@ -116,6 +116,36 @@ __device__ __forceinline__ float warp_sum(float v) {
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
 }
+// Sums R per-lane values (R = 2 or 4) over the warp with a butterfly that halves the number of live values at
+// each of the first log2(R) steps: R + 3 (R = 4: 6) shuffles instead of 5 R.  On return lane L holds the total of
+// value index warp_sum_rows_index<R>(L); the lanes with (L & 7) == 0 cover every index once.
+template <int R>
+__device__ __forceinline__ int warp_sum_rows_index(int lane) {
+  return R == 4 ? ((lane >> 4) & 1) * 2 + ((lane >> 3) & 1) : (R == 2 ? (lane >> 4) & 1 : 0);
+}
+template <int R>
+__device__ __forceinline__ float warp_sum_rows(const float (&v)[R], int lane) {
+  static_assert(R == 1 || R == 2 || R == 4, "warp_sum_rows: 1, 2 or 4 values");
+  float k0 = v[0];
+  if (R == 4) {
+    const bool up = lane & 16;
+    float a = up ? v[2] : v[0], b = up ? v[3] : v[1];
+    a += __shfl_xor_sync(0xffffffffu, up ? v[0] : v[2], 16);
+    b += __shfl_xor_sync(0xffffffffu, up ? v[1] : v[3], 16);
+    const bool up2 = lane & 8;
+    k0 = (up2 ? b : a) + __shfl_xor_sync(0xffffffffu, up2 ? a : b, 8);
+  } else if (R == 2) {
+    const bool up = lane & 16;
+    k0 = (up ? v[1] : v[0]) + __shfl_xor_sync(0xffffffffu, up ? v[0] : v[1], 16);
+    k0 += __shfl_xor_sync(0xffffffffu, k0, 8);
+  } else {
+    k0 += __shfl_xor_sync(0xffffffffu, k0, 16);
+    k0 += __shfl_xor_sync(0xffffffffu, k0, 8);
+  }
+#pragma unroll
+  for (int o = 4; o > 0; o >>= 1) k0 += __shfl_xor_sync(0xffffffffu, k0, o);
+  return k0;
+}
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
