@@ -176,27 +176,40 @@ class Ranks:
 def install_peer_exchange(pkg, model, ranks, dim):
     """Sets up the fused tensor-parallel exchange: every rank allocates its slot buffer, the processes swap the
     64-byte IPC handles over the rendezvous sockets, map each other's buffers and hand the table to the model.
-    Returns the objects that must stay alive (and the mapped pointers to close)."""
+    Returns the objects that must stay alive (local buffer, descriptor, mapped pointers), or None - on every rank
+    alike - when any rank could not export or map a buffer (the model then keeps the all-reduce)."""
     import ctypes as C
     g = pkg.ffi
     lib = g.cuda()
-    nbytes = lib.greta_cuda_peer_slot_bytes(ranks.world, dim)
-    local = g.DeviceBuffer(nbytes, zero=True)
-    handle = C.create_string_buffer(64)
-    g.check(lib.greta_cuda_ipc_export(local.ptr, handle), "ipc_export")
-    handles = ranks.allgather(bytes(handle.raw))
+    local, handle, ok = None, C.create_string_buffer(64), True
+    try:
+        local = g.DeviceBuffer(lib.greta_cuda_peer_slot_bytes(ranks.world, dim), zero=True)
+        g.check(lib.greta_cuda_ipc_export(local.ptr, handle), "ipc_export")
+    except Exception as e:                                            # noqa: BLE001 - reported, then agreed on by all ranks
+        print(f"rank {ranks.rank}: peer exchange unavailable: {e}", file=sys.stderr)
+        ok = False
+    got = ranks.allgather(bytes(handle.raw) + (b"\1" if ok else b"\0"))
+    if not all(h[64:] == b"\1" for h in got):
+        return None
     ex = pkg.model.PeerExchange()
     ex.tp, ex.rank = ranks.world, ranks.rank
     mapped = []
-    for r, h in enumerate(handles):
-        if r == ranks.rank:
-            ex.slots[r] = local.ptr
-        else:
-            ptr = C.c_void_p()
-            g.check(lib.greta_cuda_ipc_open(C.create_string_buffer(h, 64), C.byref(ptr)), "ipc_open")
-            ex.slots[r] = ptr.value
-            mapped.append(ptr.value)
-    ranks.barrier()                                   # every buffer is cleared and mapped before anyone stores into it
+    try:
+        for r, h in enumerate(got):
+            if r == ranks.rank:
+                ex.slots[r] = local.ptr
+            else:
+                ptr = C.c_void_p()
+                g.check(lib.greta_cuda_ipc_open(C.create_string_buffer(h[:64], 64), C.byref(ptr)), "ipc_open")
+                ex.slots[r] = ptr.value
+                mapped.append(ptr.value)
+    except Exception as e:                                            # noqa: BLE001
+        print(f"rank {ranks.rank}: peer exchange unavailable: {e}", file=sys.stderr)
+        ok = False
+    if not all(f == b"\1" for f in ranks.allgather(b"\1" if ok else b"\0")):   # also: every buffer is cleared and mapped from here on
+        for ptr in mapped:
+            lib.greta_cuda_ipc_close(ptr)
+        return None
     model.set_peer_exchange(ex)
     return local, ex, mapped
 
@@ -504,6 +517,8 @@ def main():
         model.set_comm(comm)
         if args.exchange == "fused":
             peer_keep = install_peer_exchange(pkg, model, ranks, cfg["dim"])
+            if peer_keep is None:
+                args.exchange = "nccl (peer memory could not be mapped)"
     model.load_synthetic(SEED)
     prompt = pkg.model.synth_tokens(SEED, args.prompt_len, cfg["vocab"])
     chunk = args.prefill_chunk or args.prompt_len           # prefill (not timed): one tensor-core pass by default

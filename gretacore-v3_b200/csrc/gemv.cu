@@ -26,6 +26,17 @@
 //   * Lanes accumulate in fp32 across the cells of a row group; a butterfly
 //     shuffle reduction runs once per group and warp; partial sums of a group
 //     that spans warps meet in shared memory in a fixed order (deterministic).
+//   * A warp executes only a few thousand instructions per launch, about as many
+//     as the kernel has: code that runs once (staging, epilogue, set-up) is kept
+//     compact, and the ring depth is a template parameter (5 or 3 stages) so
+//     that waits and wrap-arounds are constants.
+//   * Launches are chained by programmatic dependent launch: the ring is filled
+//     before the kernel waits for its predecessor, everything that reads the
+//     predecessor's output comes after the wait.
+//   * Tensor parallelism: the row-parallel projections (EPI_PEER) store their
+//     partial products, tagged, straight into every rank's slot buffer over
+//     NVLink, and the consuming kernel (PEER staging) adds the partials to the
+//     residual stream while it stages its input - no collective in between.
 //
 // fp16 weights (the LM head) use the same pipeline with fp32 activations and
 // packed fp32 FMAs.  A simpler kernel (direct loads, float math) remains for K so
@@ -379,6 +390,16 @@ int launch_simple(cudaStream_t stream, GemvParams p) {
   return launched("gemv_simple_kernel");
 }
 
+template <int FMT, int EPI, int R, bool PEER, int DFIX>
+int launch_pipe_fixed(cudaStream_t stream, GemvParams p, dim3 grid, size_t xs_bytes, size_t stage_bytes, size_t part_bytes) {
+  p.stages = DFIX;
+  const size_t smem = xs_bytes + (size_t)WARPS * DFIX * stage_bytes + part_bytes;
+  static bool attr_set[64] = {};
+  if (int rc = ensure_smem_attr(gemv_pipe_kernel<FMT, EPI, R, DFIX, PEER>, attr_set)) return rc;
+  GRETA_CUDA_TRY(launch_pdl(gemv_pipe_kernel<FMT, EPI, R, DFIX, PEER>, grid, dim3(THREADS), smem, stream, p));
+  return launched("gemv_pipe_kernel");
+}
+
 template <int FMT, int EPI, int R, bool PEER = false>
 int launch_pipe(cudaStream_t stream, GemvParams p) {
   using F = Fmt<FMT>;
@@ -401,15 +422,11 @@ int launch_pipe(cudaStream_t stream, GemvParams p) {
   p.gq = p.groups / ctas;
   p.gr = p.groups % ctas;
   dim3 grid(ctas, p.M ? p.M : 1);
-  constexpr uint32_t DFIX = 5;  // the usual depth: room for it up to K of about 20000
-  if (F::INTEGER && (SMEM_LIMIT - xs_bytes - part_bytes) / (WARPS * stage_bytes) >= DFIX) {
-    p.stages = DFIX;  // deeper than the work is harmless: requests past the last cell are empty groups
-    const size_t smem = xs_bytes + (size_t)WARPS * DFIX * stage_bytes + part_bytes;
-    static bool attr_set_fixed[64] = {};
-    if (int rc = ensure_smem_attr(gemv_pipe_kernel<FMT, EPI, R, F::INTEGER ? DFIX : 0, PEER>, attr_set_fixed)) return rc;
-    GRETA_CUDA_TRY(launch_pdl(gemv_pipe_kernel<FMT, EPI, R, F::INTEGER ? DFIX : 0, PEER>, grid, dim3(THREADS), smem, stream, p));
-    return launched("gemv_pipe_kernel");
-  }
+  // The usual depths, fixed at compile time: 5 stages (room for it up to K of about 20000), else 3.
+  // Deeper than the work is harmless: requests past the last cell are empty groups.
+  const size_t room = (SMEM_LIMIT - xs_bytes - part_bytes) / (WARPS * stage_bytes);
+  if (F::INTEGER && room >= 5) return launch_pipe_fixed<FMT, EPI, R, PEER, F::INTEGER ? 5 : 0>(stream, p, grid, xs_bytes, stage_bytes, part_bytes);
+  if (F::INTEGER && room >= 3) return launch_pipe_fixed<FMT, EPI, R, PEER, F::INTEGER ? 3 : 0>(stream, p, grid, xs_bytes, stage_bytes, part_bytes);
   p.stages = stages;
   const size_t smem = xs_bytes + (size_t)WARPS * stages * stage_bytes + part_bytes;
   static bool attr_set[64] = {};

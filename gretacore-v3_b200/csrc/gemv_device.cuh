@@ -312,19 +312,27 @@ __device__ __forceinline__ void fill_rope_table(const GemvParams &p, uint32_t po
 template <int EPI, int R>
 __device__ __forceinline__ void cta_epilogue(const GemvParams &p, const float *part, uint32_t slots, uint32_t g0, uint32_t g1, uint32_t C,
                                              uint32_t T, uint32_t m, uint32_t pos, const float2 *rope_cs) {
+  // Two groups per warp iteration, one per half-warp: lane hl of a half fetches the contribution of source warp hl.
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const uint32_t wc0 = (uint32_t)((uint64_t)(lane & (WARPS - 1)) * T / WARPS), wc1 = (uint32_t)((uint64_t)((lane & (WARPS - 1)) + 1) * T / WARPS);
+  const int half = lane >> 4, hl = lane & 15;
+  static_assert(WARPS == 16, "one source warp per lane of a half-warp");
+  const uint32_t wc0 = (uint32_t)((uint64_t)hl * T / WARPS), wc1 = (uint32_t)((uint64_t)(hl + 1) * T / WARPS);
   const uint32_t wfirst = wc0 / C;  // first group (relative to g0) the source warp touched
-  for (uint32_t grp = g0 + warp; grp < g1; grp += WARPS) {
+  for (uint32_t gbase = g0 + 2 * warp; gbase < g1; gbase += 2 * WARPS) {
+    const uint32_t grp = gbase + half;
+    const bool valid = grp < g1;
     const uint32_t lo = (grp - g0) * C, hi = lo + C;
     float v[R];
-    const bool has = lane < WARPS && wc0 < hi && wc1 > lo && wc1 > wc0;
-    const float *src = part + ((size_t)lane * slots + (grp - g0 - wfirst)) * R;
+    const bool has = valid && wc0 < hi && wc1 > lo && wc1 > wc0;
+    const float *src = part + ((size_t)hl * slots + (grp - g0 - wfirst)) * R;
 #pragma unroll
     for (int r = 0; r < R; ++r) v[r] = has ? src[r] : 0.f;
 #pragma unroll
-    for (int r = 0; r < R; ++r) v[r] = warp_sum(v[r]);
-    epilogue_lane<EPI, R>(p, grp, m, pos, v, lane, rope_cs);
+    for (int o = 8; o > 0; o >>= 1) {  // sums within each half-warp, in a fixed order
+#pragma unroll
+      for (int r = 0; r < R; ++r) v[r] += __shfl_xor_sync(0xffffffffu, v[r], o);
+    }
+    if (valid) epilogue_lane<EPI, R>(p, grp, m, pos, v, hl, rope_cs);
   }
 }
 

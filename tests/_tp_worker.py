@@ -45,6 +45,8 @@ def main():
                 out["repeat_mismatch"] = True
         ranks.barrier()
         m.close()
+        if mode == "fused" and keep is None:
+            out["peer_setup_failed"] = True
         if keep:
             code = C.c_int(-1)
             g.check(lib.greta_cuda_peer_status(C.byref(code)))
