@@ -426,17 +426,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t *__rest
     // epilogue: accumulator rows = weight rows (TMEM lanes), columns = tokens.  A warp may only touch TMEM
     // lanes 32 * (warp % 4) .. +31; the 2 * RT warps of a lane quadrant split row tiles and token halves.
     if (ok) ok = mbar_wait(acc_full, 0, abort_flag, 500);
+    const int quad = warp & 3, share = (warp - 2) >> 2;
+    const int r = share % RT, half = share / RT;
+    // fp16 output of a whole row tile goes through shared memory (the rings are idle by now): the TMEM
+    // layout gives a lane one row and 32 tokens, i.e. 2-byte stores 2N bytes apart; transposed in shared
+    // memory the tile leaves as 16-byte stores, 256 contiguous bytes per token.
+    const bool staged = OUT_F16 && n0 + ROWS <= N && N % 8 == 0;
     if (ok) {
       tc_fence_after();
-      const int quad = warp & 3, share = (warp - 2) >> 2;
-      const int r = share % RT, half = share / RT;
       const uint32_t orow = n0 + r * TILE_N + quad * 32 + lane;
       for (int c = half * (TN / 2); c < (half + 1) * (TN / 2); c += 32) {
         if (m0 + c >= M) break;
         uint32_t v[32];
         tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + r * TN + c, v);
         tmem_ld_wait();
-        if (orow < N) {
+        if (staged) {
+          __half *tile = reinterpret_cast<__half *>(smem) + (size_t)c * ROWS + r * TILE_N + quad * 32 + lane;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) tile[(size_t)j * ROWS] = __float2half_rn(__uint_as_float(v[j]));
+        } else if (orow < N) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const uint32_t m = m0 + c + j;
@@ -447,6 +455,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t *__rest
                 reinterpret_cast<float *>(Cout)[(size_t)m * N + orow] = __uint_as_float(v[j]);
             }
           }
+        }
+      }
+    }
+    if (staged) {  // uniform over the CTA; every dequant thread arrives, whatever `ok` says
+      asm volatile("bar.sync 1, %0;" ::"n"(C::DEQ_THREADS) : "memory");
+      if (ok) {
+        constexpr uint32_t PIECES_PER_TOKEN = ROWS / 8;  // 16-byte pieces
+        const uint32_t tokens = min((uint32_t)TN, M - m0);
+        for (uint32_t piece = t; piece < tokens * PIECES_PER_TOKEN; piece += C::DEQ_THREADS) {
+          const uint32_t tok = piece / PIECES_PER_TOKEN, off = piece % PIECES_PER_TOKEN;
+          const uint4 val = *reinterpret_cast<const uint4 *>(smem + ((size_t)tok * ROWS + off * 8) * 2);
+          *reinterpret_cast<uint4 *>(reinterpret_cast<__half *>(Cout) + (size_t)(m0 + tok) * N + n0 + off * 8) = val;
         }
       }
     }
