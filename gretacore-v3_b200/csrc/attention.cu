@@ -128,6 +128,16 @@ int launch_attn(cudaStream_t stream, AttnParams p, uint32_t nq, uint32_t Dh) {
 template <typename KV>
 int launch_attn_cluster(cudaStream_t stream, AttnParams p, uint32_t Dh) {
   dim3 grid(CL_SPLITS, p.H, 1);
+  // Same shared-memory / L1 split as the GEMV kernels on either side of it in the decode step: an SM does
+  // not have to be reconfigured (and drained for it) at every kernel boundary.
+  static bool carveout_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !carveout_set[dev]) {
+    cudaFuncSetAttribute(attn_cluster_kernel<KV, 16>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(attn_cluster_kernel<KV, 8>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    carveout_set[dev] = true;
+  }
   if (Dh == 128)
     GRETA_CUDA_TRY(launch_pdl_cluster(attn_cluster_kernel<KV, 16>, grid, dim3(CL_WARPS * 32), CL_SPLITS, 0, stream, p));
   else if (Dh == 64)
