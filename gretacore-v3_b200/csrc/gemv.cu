@@ -43,6 +43,7 @@
 // large that the staged activations leave no room for the ring.
 #include <math.h>
 #include <algorithm>
+#include <cstdlib>
 
 #include "gemv_device.cuh"
 
@@ -449,12 +450,14 @@ int launch_any(cudaStream_t stream, GemvParams p) {
   return launch_pipe<FMT, EPI, R, PEER>(stream, p);  // falls back to the simple kernel when K does not fit in shared memory
 }
 
-// Few rows: groups of 2 give twice as many cells to balance over the warps.
+// Groups of 2 rows give twice as many cells to balance over the warps: measured faster in the decode step up to
+// about ten 4-row cells per warp (all 7B-shape projections); above that the 4-row cell's lower overhead wins.
 template <int FMT, int EPI, bool PEER = false>
 int launch_quant(cudaStream_t stream, const GemvParams &p, uint64_t total_rows) {
   const uint64_t cells4 = (total_rows / 4) * ((p.K / 32 + 31) / 32);
   if (EPI == EPI_QKV && (p.Dh / 2) % 2 != 0) return launch_any<FMT, EPI, 2, PEER>(stream, p);
-  if (cells4 < (uint64_t)sm_count() * WARPS * 4) return launch_any<FMT, EPI, 2, PEER>(stream, p);
+  static const uint64_t r2_cells = getenv("GRETA_GEMV_R2_CELLS") ? (uint64_t)atoll(getenv("GRETA_GEMV_R2_CELLS")) : (uint64_t)sm_count() * WARPS * 10;
+  if (cells4 < r2_cells) return launch_any<FMT, EPI, 2, PEER>(stream, p);
   return launch_any<FMT, EPI, 4, PEER>(stream, p);
 }
 
