@@ -52,7 +52,12 @@ __global__ void __launch_bounds__(CL_WARPS * 32) attn_cluster_kernel(const AttnP
   const uint32_t k0 = split * chunk, k1 = min(L, k0 + chunk);
   const int tid = threadIdx.x;
   float fm, fl, fo;
-  attn_partial<KV, DPL, CL_WARPS, false>(p, min(k0, k1), k1, head, qi, fm, fl, fo);
+  if (sizeof(KV) == 2) {
+    extern __shared__ __align__(16) uint8_t stage[];
+    attn_partial_staged<DPL, CL_WARPS>(p, min(k0, k1), k1, head, qi, stage, fm, fl, fo);
+  } else {
+    attn_partial<KV, DPL, CL_WARPS, false>(p, min(k0, k1), k1, head, qi, fm, fl, fo);
+  }
   if (tid < Dh) res[2 + tid] = fo;
   if (tid == 0) {
     res[0] = fm;
@@ -130,18 +135,21 @@ int launch_attn_cluster(cudaStream_t stream, AttnParams p, uint32_t Dh) {
   dim3 grid(CL_SPLITS, p.H, 1);
   // Same shared-memory / L1 split as the GEMV kernels on either side of it in the decode step: an SM does
   // not have to be reconfigured (and drained for it) at every kernel boundary.
-  static bool carveout_set[64] = {};
+  static bool attr_set[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !carveout_set[dev]) {
+  const size_t s16 = sizeof(KV) == 2 ? attn_stage_bytes<16>() : 0, s8 = sizeof(KV) == 2 ? attn_stage_bytes<8>() : 0;  // fp16 cache: staged tiles
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    GRETA_CUDA_TRY(cudaFuncSetAttribute(attn_cluster_kernel<KV, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)s16));
+    GRETA_CUDA_TRY(cudaFuncSetAttribute(attn_cluster_kernel<KV, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)s8));
     cudaFuncSetAttribute(attn_cluster_kernel<KV, 16>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     cudaFuncSetAttribute(attn_cluster_kernel<KV, 8>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-    carveout_set[dev] = true;
+    attr_set[dev] = true;
   }
   if (Dh == 128)
-    GRETA_CUDA_TRY(launch_pdl_cluster(attn_cluster_kernel<KV, 16>, grid, dim3(CL_WARPS * 32), CL_SPLITS, 0, stream, p));
+    GRETA_CUDA_TRY(launch_pdl_cluster(attn_cluster_kernel<KV, 16>, grid, dim3(CL_WARPS * 32), CL_SPLITS, s16, stream, p));
   else if (Dh == 64)
-    GRETA_CUDA_TRY(launch_pdl_cluster(attn_cluster_kernel<KV, 8>, grid, dim3(CL_WARPS * 32), CL_SPLITS, 0, stream, p));
+    GRETA_CUDA_TRY(launch_pdl_cluster(attn_cluster_kernel<KV, 8>, grid, dim3(CL_WARPS * 32), CL_SPLITS, s8, stream, p));
   else {
     set_error("attention: head_dim=%u is not supported (64 or 128)", Dh);
     return GRETA_ERR_NOT_IMPLEMENTED;

@@ -63,6 +63,44 @@ __device__ __forceinline__ void merge(float &m, float &l, float (&o)[DPL], float
   m = mn;
 }
 
+// Merges the per-lane-group running (max, sum, output slice) of all NW warps of the CTA.  On return thread
+// tid < Dh holds the CTA's maximum, normaliser and unnormalised output for dim tid.
+template <int DPL, int NW>
+__device__ __forceinline__ void attn_merge_cta(float m, float l, float (&o)[DPL], float &fm, float &fl, float &fo) {
+  constexpr int Dh = DPL * 8;
+  __shared__ float sm_m[NW], sm_l[NW];
+  __shared__ float sm_o[NW][Dh];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane & 7, grp = lane >> 3;
+  // merge the four lane groups of the warp (same dims, different keys)
+#pragma unroll
+  for (int off = 8; off <= 16; off <<= 1) {
+    float m2 = __shfl_xor_sync(0xffffffffu, m, off), l2 = __shfl_xor_sync(0xffffffffu, l, off), o2[DPL];
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) o2[i] = __shfl_xor_sync(0xffffffffu, o[i], off);
+    merge<DPL>(m, l, o, m2, l2, o2);
+  }
+  // merge warps through shared memory
+  if (grp == 0) {
+    if (sub == 0) { sm_m[warp] = m; sm_l[warp] = l; }
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) sm_o[warp][sub * DPL + i] = o[i];
+  }
+  __syncthreads();
+  const int tid = threadIdx.x;
+  fm = -INFINITY, fl = 0.f, fo = 0.f;  // thread tid < Dh owns output dim tid
+  if (tid < Dh) {
+#pragma unroll
+    for (int w = 0; w < NW; ++w) fm = fmaxf(fm, sm_m[w]);
+#pragma unroll
+    for (int w = 0; w < NW; ++w) {
+      float c = (sm_m[w] == -INFINITY) ? 0.f : expf(sm_m[w] - fm);
+      fl += sm_l[w] * c;
+      fo += sm_o[w][tid] * c;
+    }
+  }
+}
+
 // Online-softmax attention of one query head over keys [k0, k1), by the NW warps of the calling CTA (all of
 // them must call).  On return thread tid < Dh holds, for output dim tid, the CTA's running maximum, normaliser
 // and unnormalised output.  CG: read K/V through L2 only (needed when the newest cache row was written
@@ -72,9 +110,6 @@ __device__ __forceinline__ void attn_partial(const AttnParams &p, const uint32_t
                                              float &fm, float &fl, float &fo) {
   constexpr int ATT_WARPS = NW;
   constexpr int Dh = DPL * 8;
-  __shared__ float sm_m[ATT_WARPS], sm_l[ATT_WARPS];
-  __shared__ float sm_o[ATT_WARPS][Dh];
-
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int sub = lane & 7, grp = lane >> 3;  // 8 lanes per key, 4 keys per warp step
   const uint32_t kvh = head / (p.H / p.Hkv);
@@ -134,33 +169,96 @@ __device__ __forceinline__ void attn_partial(const AttnParams &p, const uint32_t
     }
   }
 
-  // merge the four lane groups of the warp (same dims, different keys)
+  attn_merge_cta<DPL, NW>(m, l, o, fm, fl, fo);
+}
+
+// The same for an fp16 cache, with the K and V rows travelling global -> shared by cp.async in tiles of 64
+// keys, three tiles in flight: every byte of the CTA's share (up to 192 keys) is requested before the first
+// one is used, so a CTA pays one HBM latency where the register-staged loop pays one per 64 keys.
+constexpr int ATT_TILE_KEYS = 64, ATT_TILES_IN_FLIGHT = 3;
+template <int DPL>
+constexpr size_t attn_stage_bytes() { return (size_t)ATT_TILES_IN_FLIGHT * ATT_TILE_KEYS * DPL * 8 * 2 * 2; }
+
+template <int DPL, int NW>
+__device__ __forceinline__ void attn_partial_staged(const AttnParams &p, const uint32_t k0, const uint32_t k1, const uint32_t head,
+                                                    const uint32_t qi, uint8_t *stage, float &fm, float &fl, float &fo) {
+  constexpr int Dh = DPL * 8, ROW = Dh * 2, TK = ATT_TILE_KEYS, NT = ATT_TILES_IN_FLIGHT, TILE_BYTES = TK * ROW * 2;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int sub = lane & 7, grp = lane >> 3;
+  const uint32_t kvh = head / (p.H / p.Hkv);
+  const uint8_t *kg = reinterpret_cast<const uint8_t *>(p.kc) + (size_t)kvh * p.max_seq * ROW;
+  const uint8_t *vg = reinterpret_cast<const uint8_t *>(p.vc) + (size_t)kvh * p.max_seq * ROW;
+  const uint32_t n_tiles = k1 > k0 ? (k1 - k0 + TK - 1) / TK : 0;
+  auto issue = [&](uint32_t t) {
+    if (t < n_tiles) {
+      const uint32_t key0 = k0 + t * TK, nk = min((uint32_t)TK, k1 - key0);
+      uint8_t *slot = stage + (t % NT) * TILE_BYTES;
+      for (uint32_t piece = tid; piece < nk * 32; piece += NW * 32) {  // 16 K pieces and 16 V pieces of 16 bytes per key
+        const uint32_t row = piece >> 5, c = piece & 31, is_v = c >> 4, cc = c & 15;
+        const uint8_t *src = (is_v ? vg : kg) + (size_t)(key0 + row) * ROW + cc * 16;
+        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(slot + is_v * (TK * ROW) + row * ROW + cc * 16);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
 #pragma unroll
-  for (int off = 8; off <= 16; off <<= 1) {
-    float m2 = __shfl_xor_sync(0xffffffffu, m, off), l2 = __shfl_xor_sync(0xffffffffu, l, off), o2[DPL];
+  for (int t = 0; t < NT; ++t) issue(t);
+
+  float qv[DPL];
+  {
+    const float *qp = p.q + ((size_t)qi * p.H + head) * Dh + sub * DPL;
 #pragma unroll
-    for (int i = 0; i < DPL; ++i) o2[i] = __shfl_xor_sync(0xffffffffu, o[i], off);
-    merge<DPL>(m, l, o, m2, l2, o2);
-  }
-  // merge warps through shared memory
-  if (grp == 0) {
-    if (sub == 0) { sm_m[warp] = m; sm_l[warp] = l; }
-#pragma unroll
-    for (int i = 0; i < DPL; ++i) sm_o[warp][sub * DPL + i] = o[i];
-  }
-  __syncthreads();
-  const int tid = threadIdx.x;
-  fm = -INFINITY, fl = 0.f, fo = 0.f;  // thread tid < Dh owns output dim tid
-  if (tid < Dh) {
-#pragma unroll
-    for (int w = 0; w < ATT_WARPS; ++w) fm = fmaxf(fm, sm_m[w]);
-#pragma unroll
-    for (int w = 0; w < ATT_WARPS; ++w) {
-      float c = (sm_m[w] == -INFINITY) ? 0.f : expf(sm_m[w] - fm);
-      fl += sm_l[w] * c;
-      fo += sm_o[w][tid] * c;
+    for (int i = 0; i < DPL; i += 4) {
+      float4 t = __ldcg(reinterpret_cast<const float4 *>(qp + i));
+      qv[i] = t.x * p.scale; qv[i + 1] = t.y * p.scale; qv[i + 2] = t.z * p.scale; qv[i + 3] = t.w * p.scale;
     }
   }
+  float m = -INFINITY, l = 0.f, o[DPL];
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) o[i] = 0.f;
+
+  for (uint32_t t = 0; t < n_tiles; ++t) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(NT - 1) : "memory");
+    __syncthreads();  // every thread's pieces of tile t have landed
+    const uint32_t nk = min((uint32_t)TK, k1 - (k0 + t * TK));
+    const uint8_t *slot = stage + (t % NT) * TILE_BYTES;
+    for (uint32_t base = 4 * warp; base < nk; base += 4 * NW) {  // one key per lane group and step
+      const uint32_t j = base + grp;
+      const bool valid = j < nk;
+      float kf[DPL], vf[DPL];
+      if (valid) {
+#pragma unroll
+        for (int v = 0; v < DPL / 8; ++v) {
+          const uint4 ku = *reinterpret_cast<const uint4 *>(slot + j * ROW + sub * (DPL * 2) + v * 16);
+          const uint4 vu = *reinterpret_cast<const uint4 *>(slot + TK * ROW + j * ROW + sub * (DPL * 2) + v * 16);
+          float2 a = h2_to_f2(ku.x), b = h2_to_f2(ku.y), c = h2_to_f2(ku.z), d = h2_to_f2(ku.w);
+          kf[8 * v + 0] = a.x; kf[8 * v + 1] = a.y; kf[8 * v + 2] = b.x; kf[8 * v + 3] = b.y;
+          kf[8 * v + 4] = c.x; kf[8 * v + 5] = c.y; kf[8 * v + 6] = d.x; kf[8 * v + 7] = d.y;
+          a = h2_to_f2(vu.x); b = h2_to_f2(vu.y); c = h2_to_f2(vu.z); d = h2_to_f2(vu.w);
+          vf[8 * v + 0] = a.x; vf[8 * v + 1] = a.y; vf[8 * v + 2] = b.x; vf[8 * v + 3] = b.y;
+          vf[8 * v + 4] = c.x; vf[8 * v + 5] = c.y; vf[8 * v + 6] = d.x; vf[8 * v + 7] = d.y;
+        }
+      }
+      float sc = 0.f;
+      if (valid) {
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) sc = fmaf(qv[i], kf[i], sc);
+      }
+#pragma unroll
+      for (int off = 4; off > 0; off >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, off);  // the 8 lanes that share a key
+      if (valid) {
+        float mn = fmaxf(m, sc), c = expf(m - mn), pe = expf(sc - mn);
+        l = l * c + pe;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) o[i] = fmaf(pe, vf[i], o[i] * c);
+        m = mn;
+      }
+    }
+    __syncthreads();  // the slot is free again
+    issue(t + NT);
+  }
+  attn_merge_cta<DPL, NW>(m, l, o, fm, fl, fo);
 }
 
 // One (query qi, head, split) work item: the CTA's share of the keys, then the merge of the splits through
