@@ -294,6 +294,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t *__rest
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t n0 = blockIdx.x * ROWS, m0 = blockIdx.y * TN;
   const uint32_t KT = (K + BK - 1) / BK, nb = K / 32;
+  const uint32_t G_PRE = min((uint32_t)AU, KT * UPS);  // activation units requested before the set-up barrier
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < AU; ++s) {
@@ -307,10 +308,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t *__rest
     mbar_init(acc_full, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // The thread that made the barriers is the TMA producer: the first ring-full of activation units goes out
+    // now, under the TMEM allocation and the set-up barrier (a_empty needs no wait the first time round).
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
+    for (uint32_t g = 0; g < G_PRE; ++g) {
+      mbar_arrive_expect_tx(&a_full[g], UNIT_BYTES);
+      tma_load_2d(a_units + g * UNIT_BYTES, &tmap_a, (int)((g / UPS) * BK), (int)(m0 + (g % UPS) * UNIT_ROWS), &a_full[g]);
+    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, COLS);
     tmem_relinquish();
+  }
+  // Dequant threads: the first raw-weight stages are requested before the set-up barrier as well.
+  const int t = (int)threadIdx.x - 64;
+  const int row = t >= 0 ? t % ROWS : 0, hb = t >= 0 ? t / ROWS : 0;  // weight row inside the CTA's rows, and which block of the stage
+  const uint32_t n_row = min(n0 + (uint32_t)row, N - 1);
+  const uint8_t *qs_row = qs + (size_t)n_row * nb * (C::Q4 ? 16 : 32);
+  const __half *d_row = dsc + (size_t)n_row * d_row_stride(nb);
+  if (warp >= 2) {
+#pragma unroll
+    for (int j = 0; j < RS - 1; ++j) {
+      if ((uint32_t)j < KT) raw_issue<C>(raw + j * RAW_STAGE, row, hb, qs_row, d_row, j, nb);
+      cp_async_commit();
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -320,22 +341,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t *__rest
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      uint32_t issued = 0, u = 0, ph = 1;
-      for (uint32_t kt = 0; kt < KT; ++kt) {
-        bool ok = true;
-#pragma unroll
-        for (int h = 0; h < UPS; ++h) {
-          ok = mbar_wait(&a_empty[u], ph, abort_flag, 100 + u);
-          if (!ok) break;
-          mbar_arrive_expect_tx(&a_full[u], UNIT_BYTES);
-          tma_load_2d(a_units + u * UNIT_BYTES, &tmap_a, (int)(kt * BK), (int)(m0 + h * UNIT_ROWS), &a_full[u]);
-          ++issued;
-          if (++u == AU) {
-            u = 0;
-            ph ^= 1;
-          }
+      uint32_t issued = G_PRE, u = G_PRE % AU, ph = G_PRE == (uint32_t)AU ? 0u : 1u;
+      for (uint32_t g = G_PRE; g < KT * UPS; ++g) {
+        if (!mbar_wait(&a_empty[u], ph, abort_flag, 100 + u)) break;
+        mbar_arrive_expect_tx(&a_full[u], UNIT_BYTES);
+        tma_load_2d(a_units + u * UNIT_BYTES, &tmap_a, (int)((g / UPS) * BK), (int)(m0 + (g % UPS) * UNIT_ROWS), &a_full[u]);
+        ++issued;
+        if (++u == AU) {
+          u = 0;
+          ph ^= 1;
         }
-        if (!ok) break;
       }
       if (*abort_flag) {  // give the copies still in flight a bounded chance to land before the CTA exits
         for (uint32_t j = issued > (uint32_t)AU ? issued - AU : 0; j < issued; ++j) {
@@ -387,16 +402,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t *__rest
     }
   } else {
     // ---------------- dequant warps, then epilogue ----------------
-    const int t = threadIdx.x - 64;
-    const int row = t % ROWS, hb = t / ROWS;  // weight row inside the CTA's rows, and which block of the stage
-    const uint32_t n = min(n0 + (uint32_t)row, N - 1);
-    const uint8_t *qs_row = qs + (size_t)n * nb * (C::Q4 ? 16 : 32);
-    const __half *d_row = dsc + (size_t)n * d_row_stride(nb);
-#pragma unroll
-    for (int j = 0; j < RS - 1; ++j) {
-      if ((uint32_t)j < KT) raw_issue<C>(raw + j * RAW_STAGE, row, hb, qs_row, d_row, j, nb);
-      cp_async_commit();
-    }
     // this thread's half (64 bytes) of its row in the swizzled tile of its 128-row group
     const uint32_t row_off = (row >> 7) * (TILE_N * BK * 2) + (row & 127) * 128;
     bool ok = true;
