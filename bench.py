@@ -564,7 +564,7 @@ def main():
                 "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": f"of {peak_src}",
                 "us_per_launch": us, "algorithmic_bytes_per_launch": alg,
                 # dram__bytes_read + write of one launch from the ncu capture of the 7B-sized kernel (50.83 MB for 50.80 MB
-                # algorithmic, profiles/gemv_q4_0_swiglu_7b.md); a tensor-parallel shard moves proportionally less
+                # algorithmic; the summary is under profiles/); a tensor-parallel shard moves proportionally less
                 "traffic": int(alg * 50830848 / 50801664)}
     tok_s = 1e3 * args.steps / ms
     # whole-step view of the same bound: bytes one decode step must read

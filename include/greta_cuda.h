@@ -329,7 +329,7 @@ GRETA_API int greta_cuda_comm_allreduce_f32(void *comm, float *buf, size_t count
 
 /* ---- Tensor-parallel exchange fused into the operators, over peer memory (NVLink) ----------------
  * The reference has no counterpart (it is single-GPU); this replaces "row-parallel projection, then
- * all-reduce, then the next operator's RMSNorm" of a Megatron-sharded decoder layer (SURVEY hot-path row e)
+ * all-reduce, then the next operator's RMSNorm" of a Megatron-sharded decoder layer
  * by two kernels and no collective launch:
  *   producer  greta_cuda_gemv_peer_scatter: y_r = x W_r^T, every element stored as {value, tag} straight into
  *             slot r of EVERY rank's slot buffer (plain 8-byte stores over NVLink; no flag, no fence: the tag
