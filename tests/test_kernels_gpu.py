@@ -271,7 +271,7 @@ def _exchange(g, tp, rank, slot_ptrs):
 
 
 @pytest.mark.parametrize("name", ["q4_0", "q8_0"])
-@pytest.mark.parametrize("tp", [1, 2, 3])
+@pytest.mark.parametrize("tp", [1, 2, 3, 8])
 def test_fused_exchange_operators_on_one_gpu(g, name, tp):
     """The fused tensor-parallel exchange with every 'rank' on this GPU: tp row-parallel projections (columns of W
     split in whole blocks) scatter their tagged partials into tp slot buffers, one after the other; then each
