@@ -23,8 +23,6 @@ path and its GPU kernels are HIP/gfx942 only) on the host cores.
 import argparse
 import json
 import os
-import socket
-import struct
 import subprocess
 import sys
 import threading
@@ -34,7 +32,6 @@ import numpy as np
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
-sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 PROMPT_LEN = 512
 SEED = 3
@@ -42,7 +39,7 @@ METRIC = "decode_tokens_per_s_llama2_7b_shape_q4_0_batch1"
 
 
 def load_pkg():
-    from _support import load_package
+    from __graft_entry__ import load_package
     return load_package()
 
 
@@ -89,129 +86,6 @@ class ClockSampler:
                 if r[col].lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(rows[0][2]), "reasons": sorted(reasons), "samples": len(rows)}
-
-
-# ----------------------------------------------------------------------------- rendezvous (N > 1)
-class Ranks:
-    """Tiny TCP star on MASTER_ADDR for the NCCL id hand-out and for gathering per-rank timings."""
-
-    def __init__(self):
-        self.rank = int(os.environ.get("RANK", "0"))
-        self.world = int(os.environ.get("WORLD_SIZE", "1"))
-        self.local = int(os.environ.get("LOCAL_RANK", str(self.rank)))
-        self.addr = os.environ.get("MASTER_ADDR", "127.0.0.1")
-        self.port = int(os.environ.get("MASTER_PORT", "29500")) + 1000
-        self.peers = []
-        if self.world > 1:
-            if self.rank == 0:
-                srv = socket.socket()
-                srv.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
-                srv.bind((self.addr, self.port))
-                srv.listen(self.world)
-                conns = {}
-                while len(conns) < self.world - 1:
-                    c, _ = srv.accept()
-                    r = struct.unpack("<i", self._recv(c, 4))[0]
-                    conns[r] = c
-                self.peers = [conns[r] for r in sorted(conns)]
-                srv.close()
-            else:
-                for _ in range(600):
-                    try:
-                        self.sock = socket.create_connection((self.addr, self.port), timeout=5)
-                        break
-                    except OSError:
-                        time.sleep(0.1)
-                else:
-                    raise RuntimeError("rank 0 not reachable")
-                self.sock.settimeout(None)
-                self.sock.sendall(struct.pack("<i", self.rank))
-
-    @staticmethod
-    def _recv(c, n):
-        buf = b""
-        while len(buf) < n:
-            chunk = c.recv(n - len(buf))
-            if not chunk:
-                raise RuntimeError("peer closed")
-            buf += chunk
-        return buf
-
-    def bcast(self, data, n):
-        if self.world == 1:
-            return data
-        if self.rank == 0:
-            for c in self.peers:
-                c.sendall(data)
-            return data
-        return self._recv(self.sock, n)
-
-    def gather_max(self, value):
-        if self.world == 1:
-            return value
-        if self.rank == 0:
-            vals = [value] + [struct.unpack("<d", self._recv(c, 8))[0] for c in self.peers]
-            return max(vals)
-        self.sock.sendall(struct.pack("<d", value))
-        return value
-
-    def barrier(self):
-        self.gather_max(0.0)
-        self.bcast(b"go!!", 4)
-
-    def allgather(self, data):
-        """Every rank contributes len(data) bytes; returns the list of all ranks' contributions."""
-        n = len(data)
-        if self.world == 1:
-            return [data]
-        if self.rank == 0:
-            parts = [data] + [self._recv(c, n) for c in self.peers]
-            self.bcast(b"".join(parts), n * self.world)
-            return parts
-        self.sock.sendall(data)
-        blob = self._recv(self.sock, n * self.world)
-        return [blob[i * n:(i + 1) * n] for i in range(self.world)]
-
-
-def install_peer_exchange(pkg, model, ranks, dim):
-    """Sets up the fused tensor-parallel exchange: every rank allocates its slot buffer, the processes swap the
-    64-byte IPC handles over the rendezvous sockets, map each other's buffers and hand the table to the model.
-    Returns the objects that must stay alive (local buffer, descriptor, mapped pointers), or None - on every rank
-    alike - when any rank could not export or map a buffer (the model then keeps the all-reduce)."""
-    import ctypes as C
-    g = pkg.ffi
-    lib = g.cuda()
-    local, handle, ok = None, C.create_string_buffer(64), True
-    try:
-        local = g.DeviceBuffer(lib.greta_cuda_peer_slot_bytes(ranks.world, dim), zero=True)
-        g.check(lib.greta_cuda_ipc_export(local.ptr, handle), "ipc_export")
-    except Exception as e:                                            # noqa: BLE001 - reported, then agreed on by all ranks
-        print(f"rank {ranks.rank}: peer exchange unavailable: {e}", file=sys.stderr)
-        ok = False
-    got = ranks.allgather(bytes(handle.raw) + (b"\1" if ok else b"\0"))
-    if not all(h[64:] == b"\1" for h in got):
-        return None
-    ex = pkg.model.PeerExchange()
-    ex.tp, ex.rank = ranks.world, ranks.rank
-    mapped = []
-    try:
-        for r, h in enumerate(got):
-            if r == ranks.rank:
-                ex.slots[r] = local.ptr
-            else:
-                ptr = C.c_void_p()
-                g.check(lib.greta_cuda_ipc_open(C.create_string_buffer(h[:64], 64), C.byref(ptr)), "ipc_open")
-                ex.slots[r] = ptr.value
-                mapped.append(ptr.value)
-    except Exception as e:                                            # noqa: BLE001
-        print(f"rank {ranks.rank}: peer exchange unavailable: {e}", file=sys.stderr)
-        ok = False
-    if not all(f == b"\1" for f in ranks.allgather(b"\1" if ok else b"\0")):   # also: every buffer is cleared and mapped from here on
-        for ptr in mapped:
-            lib.greta_cuda_ipc_close(ptr)
-        return None
-    model.set_peer_exchange(ex)
-    return local, ex, mapped
 
 
 # ----------------------------------------------------------------------------- CPU baseline (oracle port)
@@ -271,7 +145,7 @@ def run_reference(args, ranks, cfg):
         "impl": "reference", "metric": METRIC, "value": val, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "q4_0 weights, fp32 activations/accumulation", "data": "synthetic",
-        "config": {"workload": "Llama-2-7B-shaped decode, batch 1, Q4_0 (BASELINE config 4 shape), CPU port of the reference kernel math",
+        "config": {"workload": "Llama-2-7B-shaped decode, batch 1, Q4_0, CPU port of the reference kernel math",
                    "note": "the reference has no CPU implementation of this path and its GPU kernels are HIP/gfx942 only"},
         "cpu_baseline": {"value": val, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -428,7 +302,7 @@ def run_case(pkg, name):
         y = g.DeviceBuffer(N * 4)
         for i in range(12):
             g.check(lib.greta_cuda_gemv(None, g.FMT_Q4_0, x.ptr, 0, w[i][0].ptr, w[i][1].ptr, y.ptr, 1, N, K))
-    elif name == "gemm_c2":          # BASELINE config 2: 512 x 4096 -> 11008, fp16 in / out
+    elif name == "gemm_c2":          # the prefill GEMM benchmark shape: 512 x 4096 -> 11008, fp16 in / out
         M, N, K = 512, 11008, 4096
         w = planes(N, K, 6)
         a = g.DeviceBuffer.from_numpy(rng.normal(0, 1, (M, K)).astype(np.float16).view(np.uint16))
@@ -474,18 +348,17 @@ def main():
     ap.add_argument("--prefill-chunk", type=int, default=0, help="tokens per prefill call (0 = the whole prompt at once)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--workload", choices=["c4", "c5-batch1"], default="c4",
-                    help="c4: BASELINE config 4 (7B shape, the metric's workload); c5-batch1: the 70B shape of config 5 at batch 1 "
-                         "(config 5 itself is batch 16, which this path does not have)")
+                    help="c4: the 7B shape at batch 1 (the metric's workload); c5-batch1: the 70B shape at batch 1")
     ap.add_argument("--exchange", choices=["fused", "nccl"], default="fused",
                     help="tensor-parallel exchange of the decode step: fused into the GEMV kernels over peer memory, or NCCL all-reduce")
     ap.add_argument("--case", default=None, help="run a small single-kernel case (gemv_swiglu, gemv_plain, gemm_c2, attn_decode, decode_step) and exit; "
                          "gemv_shapes prints the GEMV bandwidth of every projection shape")
     args = ap.parse_args()
-    ranks = Ranks()
+    pkg = load_pkg()
+    ranks = pkg.rendezvous.Ranks()
     if ranks.world != args.gpus and ranks.world > 1:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={ranks.world}")
 
-    pkg = load_pkg()
     if args.case == "gemv_shapes":
         pkg.ffi.require_device()
         gemv_shapes(pkg)
@@ -516,7 +389,7 @@ def main():
         g.check(lib.greta_cuda_comm_init(C.byref(comm), idbuf, tp, ranks.rank), "comm_init")
         model.set_comm(comm)
         if args.exchange == "fused":
-            peer_keep = install_peer_exchange(pkg, model, ranks, cfg["dim"])
+            peer_keep = pkg.rendezvous.install_peer_exchange(model, ranks, cfg["dim"])
             if peer_keep is None:
                 args.exchange = "nccl (peer memory could not be mapped)"
     model.load_synthetic(SEED)
@@ -576,11 +449,10 @@ def main():
         "dtype": "q4_0 weights (int8 dot products on 23-bit fixed-point activations), fp32 accumulation, fp16 KV cache",
         "data": "synthetic",
         "config": {"workload": ("Llama-2-7B-shaped model (32 layers, hidden 4096, 32 heads x 128, FFN 11008, vocab 32000), random-init "
-                                "Q4_0 weights, fp16 LM head, 512-token random prompt then greedy decode at batch 1 (BASELINE config 4)"
+                                "Q4_0 weights, fp16 LM head, 512-token random prompt then greedy decode at batch 1"
                                 if args.workload == "c4" else
                                 "Llama-3-70B-shaped model (80 layers, hidden 8192, GQA 64/8 heads x 128, FFN 28672, vocab 128256), random-init "
-                                "Q4_0 weights, fp16 LM head, random prompt then greedy decode at BATCH 1 (the shape of BASELINE config 5, "
-                                "not its batch of 16)"),
+                                "Q4_0 weights, fp16 LM head, random prompt then greedy decode at BATCH 1 (the 70B shape at batch 1)"),
                    "prompt_len": args.prompt_len, "parallelism": (f"tp{tp}, exchange {args.exchange}" if tp > 1 else "single GPU"),
                    "l2_defeat": f"every step streams {model_step_bytes(cfg, pos) / 1e9:.1f} GB of distinct weights (L2 is 126 MB)", "seed": SEED},
         "clocks": clocks, "gpu_launches": int(launches),

@@ -7,5 +7,5 @@ This Python package only loads them through ctypes for the tests and the
 benchmark; it holds no compute of its own and has no CPU fallback: if the CUDA
 library is missing or no device is present, calls raise.
 """
-from . import ffi, model  # noqa: F401
+from . import ffi, model, rendezvous  # noqa: F401
 from .build import build  # noqa: F401

@@ -7,15 +7,19 @@
 // each, 128-bit loads), four keys per warp step, so one warp load instruction
 // covers four whole cache rows.  Each lane group keeps its own running maximum,
 // normaliser and output slice (online softmax); groups, warps and finally splits
-// are merged with the usual (max, sum, vector) rescaling.  Splits meet through a
-// scratch buffer: every CTA publishes its partial result, bumps a per-head
-// counter, and the CTA that sees the last ticket does the merge - no CTA ever
-// waits on another.
+// are merged with the usual (max, sum, vector) rescaling.  The splits of a head
+// meet in one of two ways:
+//   * attn_cluster_kernel (the default): the splits form a thread-block cluster,
+//     every CTA leaves its partial result in its own shared memory and CTA 0 reads
+//     them through distributed shared memory after a cluster barrier - no scratch;
+//   * attn_kernel (tuning switch attn_cluster = 0, the persistent decode step, and
+//     always for greta_cuda_attn_decode_static): through a scratch buffer - every
+//     CTA publishes its partial result, bumps a per-head ticket, and the CTA that
+//     draws the last ticket does the merge; no CTA ever waits on another.
 #include <cooperative_groups.h>
 #include <math.h>
 
 #include <algorithm>
-#include <cstdlib>
 #include <mutex>
 
 #include "attention_device.cuh"
@@ -47,7 +51,7 @@ __global__ void __launch_bounds__(CL_WARPS * 32) attn_cluster_kernel(const AttnP
   pdl_launch_dependents();
   pdl_wait();  // q, the position and the newest cache row come from the previous kernel
   const uint32_t split = cluster.block_rank(), head = blockIdx.y, qi = blockIdx.z;
-  const uint32_t L = (p.d_pos ? __ldcg(p.d_pos) + 1 : p.len0) + qi;
+  const uint32_t L = min((p.d_pos ? __ldcg(p.d_pos) + 1 : p.len0) + qi, p.max_seq);  // never past the cache
   const uint32_t chunk = (L + CL_SPLITS - 1) / CL_SPLITS;
   const uint32_t k0 = split * chunk, k1 = min(L, k0 + chunk);
   const int tid = threadIdx.x;
@@ -157,16 +161,11 @@ int launch_attn_cluster(cudaStream_t stream, AttnParams p, uint32_t Dh) {
   return launched("attn_cluster_kernel");
 }
 
-// GRETA_ATTN_CLUSTER=0 keeps the splits on the scratch-buffer path.
-bool cluster_path_enabled() {
-  const char *e = getenv("GRETA_ATTN_CLUSTER");
-  return !(e && e[0] == '0');
-}
-
+// scratch_merge_only: the splits meet through `scratch` whatever the attn_cluster switch says.
 template <typename KV>
 int attn_decode_impl(greta_stream_t stream, const float *q, const void *kc, const void *vc, float *o,
                      const uint32_t *d_pos, uint32_t seq_len, uint32_t H, uint32_t Hkv, uint32_t Dh, uint32_t max_seq,
-                     float scale, void *scratch, size_t scratch_bytes) {
+                     float scale, void *scratch, size_t scratch_bytes, bool scratch_merge_only = false) {
   GRETA_REQUIRE(H && Hkv && H % Hkv == 0, "attn_decode: num_heads=%u must be a positive multiple of num_heads_kv=%u", H, Hkv);
   GRETA_REQUIRE(q && kc && vc && o, "attn_decode: null pointer");
   GRETA_REQUIRE(aligned16(q) && aligned16(kc) && aligned16(vc), "attn_decode: pointers must be 16-byte aligned");
@@ -183,7 +182,7 @@ int attn_decode_impl(greta_stream_t stream, const float *q, const void *kc, cons
                   "attn_decode: scratch of %zu bytes needed, %zu given", greta_cuda_attn_decode_scratch_bytes(H, Dh), scratch_bytes);
     p.counters = reinterpret_cast<uint32_t *>(scratch);
     p.partial = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(scratch) + counters_bytes(H));
-    if (cluster_path_enabled()) return launch_attn_cluster<KV>((cudaStream_t)stream, p, Dh);
+    if (!scratch_merge_only && tuning().attn_cluster) return launch_attn_cluster<KV>((cudaStream_t)stream, p, Dh);
   }
   return launch_attn<KV>((cudaStream_t)stream, p, 1, Dh);
 }
@@ -247,7 +246,9 @@ int greta_cuda_attn_decode_static(greta_stream_t stream, const float *q, const v
   if (int rc = static_scratch_address(&scratch)) return rc;
   // The array keeps whatever the previous call left; the tickets must start at zero.
   GRETA_CUDA_TRY(cudaMemsetAsync(scratch, 0, counters_bytes(H), (cudaStream_t)stream));
-  return attn_decode_impl<__half>(stream, q, kc, vc, o, d_pos, seq_len, H, Hkv, Dh, max_seq, scale, scratch, STATIC_SCRATCH_BYTES);
+  // Always the scratch-buffer merge (attn_kernel): the partial results and tickets of the splits live in the array.
+  return attn_decode_impl<__half>(stream, q, kc, vc, o, d_pos, seq_len, H, Hkv, Dh, max_seq, scale, scratch, STATIC_SCRATCH_BYTES,
+                                  /*scratch_merge_only=*/true);
 }
 
 int greta_cuda_attn_prefill(greta_stream_t stream, const float *q, const void *kc, const void *vc, float *o, uint32_t S,

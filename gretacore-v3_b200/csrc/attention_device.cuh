@@ -267,7 +267,7 @@ template <typename KV, int DPL, int NW, bool CG>
 __device__ void attn_body(const AttnParams &p, const uint32_t split, const uint32_t head, const uint32_t qi) {
   constexpr int Dh = DPL * 8;
   __shared__ uint32_t sm_last;
-  const uint32_t L = (p.d_pos ? __ldcg(p.d_pos) + 1 : p.len0) + qi;
+  const uint32_t L = min((p.d_pos ? __ldcg(p.d_pos) + 1 : p.len0) + qi, p.max_seq);  // never past the cache
   const uint32_t chunk = (L + p.splits - 1) / p.splits;
   const uint32_t k0 = split * chunk, k1 = min(L, k0 + chunk);
   const int tid = threadIdx.x;

@@ -390,7 +390,7 @@ int greta_cuda_decode_layers(greta_stream_t stream, const greta_decode_desc *d, 
   GRETA_REQUIRE(plan.xs_bytes + part_bytes + 2 * WARPS * stage_bytes <= DYN_SMEM_LIMIT, "decode_layers: shapes do not fit in shared memory");
   GRETA_REQUIRE(d->num_heads <= sms, "decode_layers: more heads than SMs");
   plan.stages = (uint32_t)std::min<size_t>(MAX_STAGES, (DYN_SMEM_LIMIT - plan.xs_bytes - part_bytes) / (WARPS * stage_bytes));
-  if (const char *e = getenv("GRETA_STEP_STAGES")) plan.stages = std::max(2u, std::min<uint32_t>(plan.stages, (uint32_t)atoi(e)));
+  if (tuning().step_stages > 0) plan.stages = std::max(2u, std::min<uint32_t>(plan.stages, (uint32_t)tuning().step_stages));
   const size_t smem = plan.xs_bytes + (size_t)WARPS * plan.stages * stage_bytes + part_bytes;
   auto kern = q4 ? decode_layers_kernel<GRETA_FMT_Q4_0> : decode_layers_kernel<GRETA_FMT_Q8_0>;
   static bool attr_set[2][64] = {};

@@ -532,13 +532,13 @@ int dispatch_tile(cudaStream_t stream, const CUtensorMap &map, int tn, int rt, c
 // With one MMA row tile per CTA the token operand is written to shared memory once and read once per
 // stage, and together with the weight tile that traffic (about 185 KB per 64-K stage at 512 tokens), not
 // the tensor core, sets the pace; the two-row-tile shapes move no less of it and have a shallower
-// weight ring, so they are never picked here.  GRETA_GEMM_TILE=<tokens>x<row tiles> forces one
+// weight ring, so they are never picked here.  The tuning switch gemm_tile (<tokens>x<row tiles>) forces one
 // (512x1, 256x1, 128x1, 256x2, 128x2).
 void pick_tile(uint32_t M, uint32_t N, int *tn, int *rt) {
   *rt = 1;
-  if (const char *e = getenv("GRETA_GEMM_TILE")) {
-    int a = 0, b = 0;
-    if (sscanf(e, "%dx%d", &a, &b) == 2 && (a == 128 || a == 256 || a == 512) && (b == 1 || b == 2) && a * b <= 512) {
+  {
+    const int a = tuning().gemm_tile_tokens, b = tuning().gemm_tile_rows;
+    if ((a == 128 || a == 256 || a == 512) && (b == 1 || b == 2) && a * b <= 512) {
       *tn = a;
       *rt = b;
       return;

@@ -457,7 +457,7 @@ template <int FMT, int EPI, bool PEER = false>
 int launch_quant(cudaStream_t stream, const GemvParams &p, uint64_t total_rows) {
   const uint64_t cells4 = (total_rows / 4) * ((p.K / 32 + 31) / 32);
   if (EPI == EPI_QKV && (p.Dh / 2) % 2 != 0) return launch_any<FMT, EPI, 2, PEER>(stream, p);
-  static const uint64_t r2_cells = getenv("GRETA_GEMV_R2_CELLS") ? (uint64_t)atoll(getenv("GRETA_GEMV_R2_CELLS")) : (uint64_t)sm_count() * WARPS * 10;
+  const uint64_t r2_cells = tuning().gemv_r2_cells >= 0 ? (uint64_t)tuning().gemv_r2_cells : (uint64_t)sm_count() * WARPS * 10;
   if (cells4 < r2_cells) return launch_any<FMT, EPI, 2, PEER>(stream, p);
   return launch_any<FMT, EPI, 4, PEER>(stream, p);
 }
@@ -486,6 +486,7 @@ int fill_exchange(GemvParams &p, const greta_peer_exchange *ex, uint32_t exch_id
   p.rank = ex->rank;
   p.exch_idx = exch_idx;
   p.d_pos = d_pos;
+  p.poll_limit = tuning().peer_poll_limit;
   return GRETA_OK;
 }
 
@@ -644,6 +645,13 @@ size_t greta_cuda_peer_slot_bytes(uint32_t tp, uint32_t dim) { return (size_t)2 
 int greta_cuda_peer_status(int *code) {
   GRETA_REQUIRE(code, "peer_status: null out pointer");
   GRETA_CUDA_TRY(cudaMemcpyFromSymbol(code, g_peer_error, sizeof(int)));
+  return GRETA_OK;
+}
+
+int greta_cuda_peer_reset(greta_stream_t stream) {
+  void *addr = nullptr;
+  GRETA_CUDA_TRY(cudaGetSymbolAddress(&addr, g_peer_error));
+  GRETA_CUDA_TRY(cudaMemsetAsync(addr, 0, sizeof(int), (cudaStream_t)stream));
   return GRETA_OK;
 }
 

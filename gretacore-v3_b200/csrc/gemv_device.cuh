@@ -54,13 +54,17 @@ struct GemvParams {
   const uint2 *peer_in;
   float *x_out;
   uint32_t tp, rank, exch_idx;
+  uint32_t poll_limit;  // polls a consumer spends on one missing partial before it gives up (tuning switch peer_poll_limit)
 };
 
 // Tag of exchange number exch_idx at the current position: strictly increasing within a decode session.
 __device__ __forceinline__ uint32_t peer_tag(const GemvParams &p) { return ((__ldcg(p.d_pos) + 1u) << 8) | p.exch_idx; }
 
-__device__ int g_peer_error = 0;  // set when a wait for a peer's partial gave up
-constexpr uint32_t PEER_POLL_LIMIT = 1u << 22;
+// Set when a wait for a peer's partial gave up.  Once it is set every later wait gives up after a single look, so
+// a step with a missing rank drains in about one poll budget instead of one budget per thread, pass and kernel;
+// greta_cuda_peer_reset() clears it for the next session.
+__device__ int g_peer_error = 0;
+__device__ __forceinline__ bool peer_failed() { return *reinterpret_cast<volatile int *>(&g_peer_error) != 0; }
 
 __device__ __forceinline__ void st_peer(uint2 *dst, uint2 v) {
   asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(v.x), "r"(v.y) : "memory");
@@ -75,6 +79,7 @@ __device__ __forceinline__ uint4 ld_peer16(const void *src) {
 // ranks when the partials are already there, not one per rank.
 __device__ __forceinline__ void add_peer_partials(const GemvParams &p, uint32_t idx, uint32_t tag, float (&v)[4]) {
   constexpr int BATCH = 4;
+  const uint32_t budget = peer_failed() ? 0u : p.poll_limit;
   for (uint32_t r0 = 0; r0 < p.tp; r0 += BATCH) {
     uint4 a[BATCH], b[BATCH];
 #pragma unroll
@@ -90,7 +95,7 @@ __device__ __forceinline__ void add_peer_partials(const GemvParams &p, uint32_t 
       if (r0 + i < p.tp) {
         uint32_t polls = 0;
         while (!(a[i].y == tag && a[i].w == tag && b[i].y == tag && b[i].w == tag)) {
-          if (++polls > PEER_POLL_LIMIT) {
+          if (++polls > budget || ((polls & 255u) == 0 && peer_failed())) {
             g_peer_error = 1;
             break;
           }
@@ -220,7 +225,7 @@ __device__ __forceinline__ void epilogue(const GemvParams &p, uint32_t grp, uint
             p.k_out[head * p.Dh + i] = o0;
             p.k_out[head * p.Dh + i + p.Dh / 2] = o1;
           }
-          if (p.k_cache) {
+          if (p.k_cache && pos < p.max_seq) {  // a position past the cache is never written
             size_t dst = ((size_t)head * p.max_seq + pos) * p.Dh + i;
             p.k_cache[dst] = __float2half_rn(o0);
             p.k_cache[dst + p.Dh / 2] = __float2half_rn(o1);
@@ -234,7 +239,7 @@ __device__ __forceinline__ void epilogue(const GemvParams &p, uint32_t grp, uint
         if (row < p.Hkv * p.Dh) {
           if (p.v_out) p.v_out[row] = v[r];
           uint32_t head = row / p.Dh, dd = row % p.Dh;
-          if (p.v_cache) p.v_cache[((size_t)head * p.max_seq + pos) * p.Dh + dd] = __float2half_rn(v[r]);
+          if (p.v_cache && pos < p.max_seq) p.v_cache[((size_t)head * p.max_seq + pos) * p.Dh + dd] = __float2half_rn(v[r]);
         }
       }
     }
@@ -295,7 +300,7 @@ __device__ __forceinline__ void epilogue_lane(const GemvParams &p, uint32_t grp,
             p.k_out[head * p.Dh + i] = o0;
             p.k_out[head * p.Dh + i + p.Dh / 2] = o1;
           }
-          if (p.k_cache) {
+          if (p.k_cache && pos < p.max_seq) {
             const size_t dst = ((size_t)head * p.max_seq + pos) * p.Dh + i;
             p.k_cache[dst] = __float2half_rn(o0);
             p.k_cache[dst + p.Dh / 2] = __float2half_rn(o1);
@@ -307,7 +312,7 @@ __device__ __forceinline__ void epilogue_lane(const GemvParams &p, uint32_t grp,
       if (lane < R && row < p.Hkv * p.Dh) {
         if (p.v_out) p.v_out[row] = mine;
         const uint32_t head = row / p.Dh, dd = row % p.Dh;
-        if (p.v_cache) p.v_cache[((size_t)head * p.max_seq + pos) * p.Dh + dd] = __float2half_rn(mine);
+        if (p.v_cache && pos < p.max_seq) p.v_cache[((size_t)head * p.max_seq + pos) * p.Dh + dd] = __float2half_rn(mine);
       }
     }
   }

@@ -46,6 +46,19 @@ inline int launched(const char *kernel, unsigned n = 1) {
 // switched with greta_cuda_set_pdl().
 bool pdl_enabled();
 void set_pdl(bool on);
+
+// Tuning switches.  Each one takes its start value from an environment variable that is read ONCE, when the
+// first of them is looked at (never on a call path), and can be changed with greta_cuda_set_tuning().
+struct Tuning {
+  int attn_cluster;          // GRETA_ATTN_CLUSTER: 1 = the splits of a head meet in a thread-block cluster, 0 = through scratch
+  int gemm_tile_tokens;      // GRETA_GEMM_TILE=<tokens>x<row tiles>: forced tile shape of the prefill GEMM, 0 = automatic
+  int gemm_tile_rows;
+  long long gemv_r2_cells;   // GRETA_GEMV_R2_CELLS: below this many 4-row cells a GEMV uses 2-row cells; < 0 = automatic
+  int step_stages;           // GRETA_STEP_STAGES: ring depth cap of the persistent decode-step kernel, 0 = automatic
+  unsigned peer_poll_limit;  // GRETA_PEER_POLL_LIMIT: polls a consumer spends on one missing partial before it gives up
+  int skinny_max_rows;       // GRETA_SKINNY_MAX_ROWS: activation rows up to which the weights-read-once batched GEMV is used
+};
+Tuning &tuning();
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

@@ -311,7 +311,20 @@ bool BlockScheduler::set_peer_exchange(const greta_peer_exchange &ex, std::strin
   if (!all_reduce_) return fail(err, "set_peer_exchange: install the all-reduce hook first (barriers, last layer, logits)");
   if (!x_alt_.allocate((size_t)c.dim * 4, BufferUsage::DeviceOnly, GretaDataType::FP32, err)) return false;
   peer_ = ex;
+  invalidate_graph();  // a captured step holds the old exchange's pointers
   return true;
+}
+
+void BlockScheduler::set_all_reduce(AllReduceFn fn) {
+  all_reduce_ = std::move(fn);
+  invalidate_graph();
+}
+
+void BlockScheduler::invalidate_graph() {
+  if (graph_) greta_cuda_stream_synchronize(H(stream_));
+  delete graph_;
+  graph_ = nullptr;
+  graph_captured_ = false;
 }
 
 // The five decode kernels of every layer, reading the position from d_pos.  With fused_exchange the
@@ -542,7 +555,9 @@ bool BlockScheduler::begin_decode(int32_t first_token, size_t pos, std::string *
   GRETA_TRY(greta_cuda_memcpy_h2d_sync(a.d_pos.data(), init, 16), "begin_decode");
   GRETA_TRY(greta_cuda_memcpy_h2d_sync(a.d_next.data(), tok, 16), "begin_decode");
   decode_steps_ = 0;
+  decode_pos0_ = pos;
   if (peer_.tp > 1) {
+    GRETA_TRY(greta_cuda_peer_reset(s), "exchange status reset");
     // Exchange tags grow with the position: a session that restarts earlier must not meet the tags of the
     // last one.  Every rank clears its slots, then a collective keeps anyone from storing into a buffer
     // that is still being cleared.
@@ -562,7 +577,7 @@ bool BlockScheduler::begin_decode(int32_t first_token, size_t pos, std::string *
     greta_decode_desc desc;
     fill_decode_desc(desc, c, a, token_embd_, max_seq_);
     graph_ = gcore::rt::GretaContext::instance().create_graph();
-    graph_->capture_start(stream_);
+    graph_->capture_start(stream_);  // void, as in the reference: a capture that failed shows at instantiate()
     bool ok;
     const float *x_last = static_cast<const float *>(a.x.data());
     if (persistent_step_) {
@@ -589,8 +604,16 @@ bool BlockScheduler::begin_decode(int32_t first_token, size_t pos, std::string *
   return true;
 }
 
+// The step about to run reads and writes cache row decode_pos0_ + decode_steps_: it must exist.
+bool BlockScheduler::step_fits(std::string *err) const {
+  if (decode_pos0_ + decode_steps_ >= max_seq_)
+    return fail(err, "decode step at position " + std::to_string(decode_pos0_ + decode_steps_) + " exceeds max_seq_len " + std::to_string(max_seq_));
+  return true;
+}
+
 bool BlockScheduler::decode_step(std::string *err) {
   if (!graph_captured_) return fail(err, "decode_step: begin_decode() first");
+  if (!step_fits(err)) return false;
   if (graph_->launch(stream_) != gcore::rt::GretaResult::SUCCESS) return fail(err, gcore::host::cuda_error("decode step launch failed"));
   ++decode_steps_;
   return true;
@@ -598,6 +621,7 @@ bool BlockScheduler::decode_step(std::string *err) {
 
 bool BlockScheduler::decode_step_host(const int32_t *token_in, int32_t *token_out, std::string *err) {
   if (!graph_captured_) return fail(err, "decode_step_host: begin_decode() first");
+  if (!step_fits(err)) return false;
   cudaStream_t s = H(stream_);
   GRETA_TRY(greta_cuda_memcpy_h2d(activations_.d_next.data(), token_in, 4, s), "token upload");
   if (graph_->launch(stream_) != gcore::rt::GretaResult::SUCCESS) return fail(err, gcore::host::cuda_error("decode step launch failed"));
@@ -648,18 +672,48 @@ std::vector<int32_t> Generator::generate_tokens(const std::vector<int32_t> &prom
   out.push_back(first);
   const size_t steps = (size_t)params.max_tokens - 1;
   double decode_ms = 0.0;
-  if (steps > 0) {
+  // The reference stops when the sampled id is the tokenizer's end-of-sequence id (generator.cpp:1128-1129); the
+  // tokenizer is outside this path, so the id comes in through SamplingParams (-1: never stop early).
+  const bool watch_eos = params.eos_token_id >= 0;
+  if (steps > 0 && !(watch_eos && first == params.eos_token_id)) {
+    if (prompt.size() + steps > scheduler_->max_seq_len()) {
+      if (err) *err = "generate_tokens: prompt + max_tokens exceeds max_seq_len";
+      return out;
+    }
     if (!scheduler_->begin_decode(first, prompt.size(), err)) return out;
     std::unique_ptr<gcore::rt::GretaEvent> e0(gcore::rt::GretaContext::instance().create_event()),
         e1(gcore::rt::GretaContext::instance().create_event());
     e0->record(scheduler_->stream());
-    for (size_t i = 0; i < steps; ++i)
-      if (!scheduler_->decode_step(err)) return out;
+    // The steps run on the device without a host round trip.  With an end-of-sequence id to watch for they run in
+    // chunks: after each chunk the ids produced so far come back and the loop ends at the first match.
+    const size_t chunk = watch_eos ? 16 : steps;
+    size_t done = 0;
+    bool stop = false;
+    while (done < steps && !stop) {
+      const size_t n = std::min(chunk, steps - done);
+      for (size_t i = 0; i < n; ++i)
+        if (!scheduler_->decode_step(err)) return out;
+      done += n;
+      if (watch_eos) {
+        out.resize(1 + done);
+        if (!scheduler_->read_generated(out.data() + 1, done, err)) {
+          out.resize(1);
+          return out;
+        }
+        for (size_t i = done - n; i < done && !stop; ++i)
+          if (out[1 + i] == params.eos_token_id) {
+            out.resize(2 + i);  // the end-of-sequence id is the last one returned
+            stop = true;
+          }
+      }
+    }
     e1->record(scheduler_->stream());
-    out.resize(1 + steps);
-    if (!scheduler_->read_generated(out.data() + 1, steps, err)) {
-      out.resize(1);
-      return out;
+    if (!watch_eos) {
+      out.resize(1 + steps);
+      if (!scheduler_->read_generated(out.data() + 1, steps, err)) {
+        out.resize(1);
+        return out;
+      }
     }
     decode_ms = e1->elapsed_time_since(e0.get());
   }

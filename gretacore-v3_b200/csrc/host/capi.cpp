@@ -129,6 +129,19 @@ int greta_model_generate(greta_model_t m, const int32_t *prompt, uint32_t n_prom
   }
   return 0;
 }
+int greta_model_generate_eos(greta_model_t m, const int32_t *prompt, uint32_t n_prompt, uint32_t max_new, int32_t eos_id, int32_t *out,
+                             uint32_t *n_out) {
+  std::string err;
+  SamplingParams sp;
+  sp.greedy = true;
+  sp.max_tokens = (int32_t)max_new;
+  sp.eos_token_id = eos_id;
+  std::vector<int32_t> ids = M(m)->gen.generate_tokens(std::vector<int32_t>(prompt, prompt + n_prompt), sp, nullptr, &err);
+  if (!err.empty() || ids.empty()) return done(false, err.empty() ? "generation produced nothing" : err);
+  std::memcpy(out, ids.data(), ids.size() * 4);
+  *n_out = (uint32_t)ids.size();
+  return 0;
+}
 int greta_model_begin_decode(greta_model_t m, int32_t first_token, uint32_t pos) {
   std::string err;
   return done(M(m)->sched.begin_decode(first_token, pos, &err), err);

@@ -50,6 +50,30 @@ bool pdl_enabled() {
 }
 void set_pdl(bool on) { g_pdl = on ? 1 : 0; }
 
+Tuning &tuning() {
+  static Tuning t = [] {
+    Tuning v{};
+    const char *e = getenv("GRETA_ATTN_CLUSTER");
+    v.attn_cluster = (e && e[0] == '0') ? 0 : 1;
+    int a = 0, b = 0;
+    e = getenv("GRETA_GEMM_TILE");
+    if (e && sscanf(e, "%dx%d", &a, &b) == 2) {
+      v.gemm_tile_tokens = a;
+      v.gemm_tile_rows = b;
+    }
+    e = getenv("GRETA_GEMV_R2_CELLS");
+    v.gemv_r2_cells = e ? atoll(e) : -1;
+    e = getenv("GRETA_STEP_STAGES");
+    v.step_stages = e ? atoi(e) : 0;
+    e = getenv("GRETA_PEER_POLL_LIMIT");
+    v.peer_poll_limit = e ? (unsigned)strtoul(e, nullptr, 10) : (1u << 22);
+    e = getenv("GRETA_SKINNY_MAX_ROWS");
+    v.skinny_max_rows = e ? atoi(e) : 32;
+    return v;
+  }();
+  return t;
+}
+
 int sm_count() {
   static int cached[64];
   int dev = 0;
@@ -73,6 +97,32 @@ const char *greta_cuda_last_error(void) { return g_err; }
 uint64_t greta_cuda_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 int greta_cuda_set_pdl(int on) {
   set_pdl(on != 0);
+  return GRETA_OK;
+}
+int greta_cuda_set_tuning(const char *name, long long value) {
+  GRETA_REQUIRE(name, "set_tuning: null name");
+  Tuning &t = tuning();
+  if (!strcmp(name, "pdl")) {
+    set_pdl(value != 0);
+  } else if (!strcmp(name, "attn_cluster")) {
+    t.attn_cluster = value != 0;
+  } else if (!strcmp(name, "gemm_tile")) {  // tokens * 10 + row tiles, 0 = automatic
+    t.gemm_tile_tokens = (int)(value / 10);
+    t.gemm_tile_rows = (int)(value % 10);
+  } else if (!strcmp(name, "gemv_r2_cells")) {
+    t.gemv_r2_cells = value;
+  } else if (!strcmp(name, "step_stages")) {
+    t.step_stages = (int)value;
+  } else if (!strcmp(name, "peer_poll_limit")) {
+    GRETA_REQUIRE(value >= 1 && value <= (1ll << 30), "set_tuning: peer_poll_limit=%lld outside 1..2^30", value);
+    t.peer_poll_limit = (unsigned)value;
+  } else if (!strcmp(name, "skinny_max_rows")) {
+    GRETA_REQUIRE(value >= 1 && value <= 32, "set_tuning: skinny_max_rows=%lld outside 1..32", value);
+    t.skinny_max_rows = (int)value;
+  } else {
+    set_error("set_tuning: unknown switch '%s'", name);
+    return GRETA_ERR_INVALID_ARGS;
+  }
   return GRETA_OK;
 }
 

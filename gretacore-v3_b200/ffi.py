@@ -19,7 +19,7 @@ PAYLOAD_BYTES = {FMT_Q4_0: 16, FMT_Q8_0: 32}
 GGUF_BLOCK_BYTES = {FMT_Q4_0: 18, FMT_Q8_0: 34}
 
 _SCALARS = {
-    "int": C.c_int, "float": C.c_float, "double": C.c_double, "uint32_t": C.c_uint32, "int32_t": C.c_int32,
+    "int": C.c_int, "long long": C.c_longlong, "float": C.c_float, "double": C.c_double, "uint32_t": C.c_uint32, "int32_t": C.c_int32,
     "uint64_t": C.c_uint64, "int64_t": C.c_int64, "size_t": C.c_size_t, "greta_stream_t": C.c_void_p,
     "greta_model_t": C.c_void_p,
 }

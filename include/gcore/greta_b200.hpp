@@ -416,8 +416,9 @@ public:
   const gcore::rt::cuda::Buffer &get_output_weight() const { return output_weight_; }
   const ModelConfig &config() const { return config_; }
   size_t num_layers() const { return blocks_.size(); }
+  size_t max_seq_len() const { return max_seq_; }
   gcore::rt::GretaStream *stream() { return stream_; }
-  void set_all_reduce(AllReduceFn fn) { all_reduce_ = std::move(fn); }
+  void set_all_reduce(AllReduceFn fn);  // drops a captured decode step: it holds the old hook
   // Tensor-parallel decode with the exchange fused into the operators over peer memory (greta_cuda.h,
   // greta_peer_exchange): used by the captured decode step; forward() keeps the all-reduce hook.
   bool set_peer_exchange(const greta_peer_exchange &ex, std::string *err);
@@ -426,6 +427,8 @@ public:
 
 private:
   bool decode_layers(std::string *err, bool fused_exchange = false, const float **x_final = nullptr);
+  bool step_fits(std::string *err) const;
+  void invalidate_graph();
   bool build_decode_plan(std::string *err);
   bool lm_head(const float *x_row, std::string *err);
   ModelConfig config_;
@@ -437,7 +440,7 @@ private:
   gcore::rt::GretaStream *stream_ = nullptr;
   gcore::rt::GretaGraph *graph_ = nullptr;
   bool graph_captured_ = false, initialized_ = false;
-  size_t decode_steps_ = 0, max_seq_ = 0;
+  size_t decode_steps_ = 0, decode_pos0_ = 0, max_seq_ = 0;
   AllReduceFn all_reduce_;
   greta_peer_exchange peer_{};            // tp == 0: not installed
   gcore::rt::cuda::Buffer x_alt_;         // second copy of the residual stream for the fused exchange
@@ -453,6 +456,8 @@ struct SamplingParams {
   int32_t max_tokens = 128;
   int32_t seed = 42;
   bool greedy = false;
+  // B200 build: id that ends generation (the reference asks its tokenizer, which is outside this path); -1 = none.
+  int32_t eos_token_id = -1;
 };
 
 struct GenerationStats {

@@ -104,6 +104,17 @@ GRETA_API int greta_cuda_graph_exec_destroy(void *exec);
  * kernel's weight prefetch overlaps the previous kernel's tail).  On by default; GRETA_PDL=0 in the
  * environment or greta_cuda_set_pdl(0) turns it off.  Results do not depend on it. */
 GRETA_API int greta_cuda_set_pdl(int on);
+/* Tuning switches, for tests and measurements; results do not depend on them.  Each switch starts from an
+ * environment variable that is read once, at the first use of any of them - never on a call path (the
+ * reference reads its switches from the environment inside GretaCompute::gemm,
+ * src/compute/src/greta_compute_hip.cpp:148-374):
+ *   "pdl" (GRETA_PDL, 0/1), "attn_cluster" (GRETA_ATTN_CLUSTER, 0/1: splits of a head meet in a thread-block
+ *   cluster or through scratch), "gemm_tile" (GRETA_GEMM_TILE=<tokens>x<row tiles>; value = tokens * 10 + row
+ *   tiles, 0 = automatic), "gemv_r2_cells" (GRETA_GEMV_R2_CELLS, < 0 = automatic), "step_stages"
+ *   (GRETA_STEP_STAGES, 0 = automatic), "peer_poll_limit" (GRETA_PEER_POLL_LIMIT: polls a tensor-parallel
+ *   consumer spends on one missing partial before it gives up, default 2^22), "skinny_max_rows"
+ *   (GRETA_SKINNY_MAX_ROWS, 1..32). */
+GRETA_API int greta_cuda_set_tuning(const char *name, long long value);
 /* Number of kernel launches this library has issued on the calling process (all threads). */
 GRETA_API uint64_t greta_cuda_launch_count(void);
 
@@ -257,7 +268,8 @@ GRETA_API int greta_cuda_attn_decode_f32cache(greta_stream_t stream, const float
  * this library raw pointers out of a memory pool it owns in full (a fixed budget, no cudaMalloc allowed
  * after start-up), or code on a latency-critical serving path where cudaMalloc / cudaFree would
  * synchronise the whole device.  Same arguments and results as greta_cuda_attn_decode (fp16 cache), minus
- * the scratch: the partial results go to an array built into the library, about 1 MiB that every GPU
+ * the scratch: this entry always runs the scratch-merge kernel (never the cluster kernel, which needs no
+ * scratch), and the per-split partial results and per-head tickets go to an array built into the library, about 1 MiB that every GPU
  * loading the library holds until the process exits.  Limit: num_heads <= 64 and head_dim <= 128 (larger
  * shapes are rejected with GRETA_ERR_INVALID_ARGS; use greta_cuda_attn_decode).  The call allocates
  * nothing.  Its first call on a device looks up the array's device address; make that call outside any
@@ -349,6 +361,8 @@ typedef struct greta_peer_exchange {
 } greta_peer_exchange;
 GRETA_API size_t greta_cuda_peer_slot_bytes(uint32_t tp, uint32_t dim);
 GRETA_API int greta_cuda_peer_status(int *code);
+/* Clears the status word (on `stream`): after a time-out every later wait gives up at once until this is called. */
+GRETA_API int greta_cuda_peer_reset(greta_stream_t stream);
 GRETA_API int greta_cuda_ipc_export(void *device_ptr, void *handle64);         /* 64-byte handle of a greta_cuda_malloc block */
 GRETA_API int greta_cuda_ipc_open(const void *handle64, void **device_ptr);    /* maps another process's block */
 GRETA_API int greta_cuda_ipc_close(void *device_ptr);

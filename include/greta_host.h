@@ -61,6 +61,11 @@ GRETA_API int greta_model_sample_greedy(greta_model_t m, int32_t *id);          
 /* Generator::generate_tokens (greedy). stats5 = {prompt tokens, generated tokens, total ms, time to first token ms, decode ms}. */
 GRETA_API int greta_model_generate(greta_model_t m, const int32_t *prompt, uint32_t n_prompt, uint32_t n_new, int32_t *out,
                                    double *stats5);
+/* The same with SamplingParams::eos_token_id = eos_id: generation ends with the first eos_id produced (it is the last id
+ * returned), as the reference's loop does with its tokenizer's id (src/inference/src/generator.cpp:1128-1129).  out holds
+ * max_new ids; *n_out receives how many were produced. */
+GRETA_API int greta_model_generate_eos(greta_model_t m, const int32_t *prompt, uint32_t n_prompt, uint32_t max_new, int32_t eos_id,
+                                       int32_t *out, uint32_t *n_out);
 GRETA_API int greta_model_begin_decode(greta_model_t m, int32_t first_token, uint32_t pos); /* begin_decode */
 GRETA_API int greta_model_decode_step(greta_model_t m);                                   /* decode_step (asynchronous) */
 GRETA_API int greta_model_read_generated(greta_model_t m, int32_t *out, uint32_t n);      /* read_generated (synchronises) */

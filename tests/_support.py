@@ -1,29 +1,22 @@
 """Shared helpers of the test-suite: package loading, seeded GGUF block makers, error metric."""
-import importlib.util
 import os
 import sys
 
 import numpy as np
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-PKG_DIR = os.path.join(ROOT, "gretacore-v3_b200")
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
 
 
 def load_package():
-    """Imports the package directory `gretacore-v3_b200` under the importable name gretacore_v3_b200."""
-    name = "gretacore_v3_b200"
-    if name in sys.modules:
-        return sys.modules[name]
-    spec = importlib.util.spec_from_file_location(name, os.path.join(PKG_DIR, "__init__.py"),
-                                                  submodule_search_locations=[PKG_DIR])
-    mod = importlib.util.module_from_spec(spec)
-    sys.modules[name] = mod
-    spec.loader.exec_module(mod)
-    return mod
+    """The package under its importable name (the loader lives beside the build entry point)."""
+    from __graft_entry__ import load_package as _load
+    return _load()
 
 
 def q4_0_blocks(rng, N, K, sigma=0.02):
-    """GGUF Q4_0 blocks of W[N,K]: q uniform in 0..15, d = |N(0,sigma)|/8 as fp16 (BASELINE config 2)."""
+    """GGUF Q4_0 blocks of W[N,K]: q uniform in 0..15, d = |N(0,sigma)|/8 as fp16 (the prefill-GEMM benchmark distribution)."""
     nb = N * (K // 32)
     blk = np.empty((nb, 18), np.uint8)
     blk[:, :2] = (np.abs(rng.normal(0, sigma, nb)) / 8).astype(np.float16).view(np.uint8).reshape(nb, 2)
@@ -32,7 +25,7 @@ def q4_0_blocks(rng, N, K, sigma=0.02):
 
 
 def q8_0_blocks(rng, N, K, sigma=0.02):
-    """GGUF Q8_0 blocks: q uniform in [-127,127], d = |N(0,sigma)|/127 as fp16 (BASELINE config 1)."""
+    """GGUF Q8_0 blocks: q uniform in [-127,127], d = |N(0,sigma)|/127 as fp16 (the Q8_0 GEMV benchmark distribution)."""
     nb = N * (K // 32)
     blk = np.empty((nb, 34), np.uint8)
     blk[:, :2] = (np.abs(rng.normal(0, sigma, nb)) / 127).astype(np.float16).view(np.uint8).reshape(nb, 2)

@@ -13,15 +13,14 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 from _support import load_package  # noqa: E402
-import bench  # noqa: E402
 
 CFG = dict(dim=512, num_heads=8, num_heads_kv=4, num_layers=3, vocab=2048, hidden_dim=1536, head_dim=64, max_seq=96,
            rope_base=10000.0, rms_eps=1e-5)
 
 
 def main():
-    ranks = bench.Ranks()
     pkg = load_package()
+    ranks = pkg.rendezvous.Ranks()
     g = pkg.ffi
     lib = g.cuda()
     g.check(lib.greta_cuda_set_device(ranks.local))
@@ -36,7 +35,7 @@ def main():
     for mode in ("nccl", "fused"):
         m = pkg.model.Model(CFG, tp_rank=ranks.rank, tp_size=ranks.world)
         m.set_comm(comm)
-        keep = bench.install_peer_exchange(pkg, m, ranks, CFG["dim"]) if mode == "fused" else None
+        keep = pkg.rendezvous.install_peer_exchange(m, ranks, CFG["dim"]) if mode == "fused" else None
         m.load_synthetic(seed)
         for plen in (12, 40, 12):               # GEMV-route prefill, tensor-core prefill, and a session that restarts earlier
             prompt = pkg.model.synth_tokens(seed, plen, CFG["vocab"])

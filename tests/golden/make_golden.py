@@ -148,6 +148,36 @@ def main():
                         np.ones(4, np.float32).ctypes.data_as(C.c_void_p), 1, 4, C.c_float(1e-5))
     g["ka_rms_y"] = ky
 
+    # 6. The CPU attention references the reference keeps inside its block scheduler
+    # (compute_attention_ref_fp64 / _fp32, src/inference/src/block_scheduler.cpp:721-864), GQA 8 / 2 heads of 64,
+    # 70 of 80 cache rows.  Cache values are exactly representable in fp16, so the same numbers can be fed to the
+    # oracle both as the reference's fp32 cache and as the fp16 cache of the B200 build.
+    H, Hkv, Dh, L, S = 8, 2, 64, 70, 80
+    aq = rng.normal(0, 1, H * Dh).astype(np.float32)
+    ak = rng.normal(0, 1, (Hkv, S, Dh)).astype(np.float16).astype(np.float32)
+    av = rng.normal(0, 1, (Hkv, S, Dh)).astype(np.float16).astype(np.float32)
+    g["attn_q"], g["attn_k"], g["attn_v"] = aq, ak, av
+    g["attn_shape"] = np.array([H, Hkv, Dh, L, S], np.int32)
+    for mode, tag in ((0, "fp64"), (1, "fp32")):
+        ao = np.empty(H * Dh, np.float32)
+        ref.ref_sched_attention(aq.ctypes.data_as(C.c_void_p), ak.ctypes.data_as(C.c_void_p), av.ctypes.data_as(C.c_void_p), H, Hkv, Dh, L, S,
+                                C.c_float(0.125), mode, ao.ctypes.data_as(C.c_void_p))
+        g["attn_out_" + tag] = ao
+
+    # 7. The reference's host dequantiser read_weight_value (block_scheduler.cpp:639-671) on the INT4 / INT8 planes its
+    # own loader produced above, and on fp16 bits.
+    def read_weights(dtype, raw, scales, elems):
+        raw = np.ascontiguousarray(raw).view(np.uint8)
+        o = np.empty(elems, np.float32)
+        ref.ref_sched_read_weights(dtype, raw.ctypes.data_as(C.c_void_p), C.c_size_t(raw.size),
+                                   scales.ctypes.data_as(C.c_void_p) if scales is not None else None,
+                                   C.c_size_t(0 if scales is None else scales.size), 32, C.c_size_t(elems), o.ctypes.data_as(C.c_void_p))
+        return o
+    g["rwv_int4_down"] = read_weights(4, g["int4_down_packed"], g["int4_down_scales"], g["int4_down_packed"].size * 2)
+    g["rwv_int8_down"] = read_weights(3, g["int8_down_w"], g["int8_down_scales"], g["int8_down_w"].size)
+    g["rwv_f16_bits"] = allh[::97].copy()
+    g["rwv_f16"] = read_weights(1, g["rwv_f16_bits"], None, g["rwv_f16_bits"].size)
+
     out = os.path.join(HERE, "ref_golden.npz")
     np.savez_compressed(out, **g)
     print("wrote", out, os.path.getsize(out), "bytes")

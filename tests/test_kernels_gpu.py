@@ -30,6 +30,20 @@ def g():
 _KEEP = []
 
 
+@pytest.fixture
+def tuning(g):
+    """Sets a tuning switch of the library for the duration of a test."""
+    undo = []
+
+    def set_(name, value, restore):
+        g.check(g.cuda().greta_cuda_set_tuning(name.encode(), value), "set_tuning")
+        undo.append((name, restore))
+
+    yield set_
+    for name, restore in undo:
+        g.cuda().greta_cuda_set_tuning(name.encode(), restore)
+
+
 @pytest.fixture(autouse=True)
 def _release_device_buffers():
     yield
@@ -167,7 +181,7 @@ def test_gemv_f16_weights_lm_head_form(g):
 
 
 def test_gemv_linearity_at_full_size(g):
-    """Size-independent property at a BASELINE shape (11008 x 4096, Q4_0): W(a x1 + b x2) = a W x1 + b W x2,
+    """Size-independent property at the FFN projection shape of the 7B model (11008 x 4096, Q4_0): W(a x1 + b x2) = a W x1 + b W x2,
     and a sampled row check against the oracle."""
     rng = np.random.default_rng(8)
     N, K = 11008, 4096
@@ -353,15 +367,67 @@ def test_fused_exchange_rejects_bad_descriptors(g):
                                                buf.ptr, buf.ptr, buf.ptr, 64, 64) == 4                         # x_out aliases x_in
 
 
+def test_fused_exchange_wait_runs_out_and_recovers(g, tuning):
+    """A consumer whose producers never ran: with a poll limit of a few thousand the wait gives up by itself, the
+    kernel finishes on what it has, greta_cuda_peer_status reports it; after greta_cuda_peer_reset and with the
+    partials in place the same call is clean again.  Nothing faults and nothing waits without a bound."""
+    import time
+    lib = g.cuda()
+    ofmt, gfmt = FMTS["q4_0"]
+    rng = np.random.default_rng(77)
+    tp, D, F, pos = 2, 512, 64, 3
+    tuning("peer_poll_limit", 2000, restore=1 << 22)
+    g.check(lib.greta_cuda_peer_reset(None))
+    slots = [g.DeviceBuffer(lib.greta_cuda_peer_slot_bytes(tp, D), zero=True) for _ in range(tp)]
+    _KEEP.extend(slots)
+    x, gamma = rng.normal(0, 1, D).astype(np.float32), np.ones(D, np.float32)
+    b1, b3 = make_blocks(rng, ofmt, F, D), make_blocks(rng, ofmt, F, D)
+    w1, w3 = g.Weight(b1, gfmt, F, D), g.Weight(b3, gfmt, F, D)
+    dpos, xd, gd = _dev(g, np.array([pos], np.uint32)), _dev(g, x), _dev(g, gamma)
+    x_out, y = _nan_buffer(g, D), _nan_buffer(g, F)
+    _KEEP.extend([x_out, y])
+    ex = _exchange(g, tp, 0, [b.ptr for b in slots])
+
+    def consume():
+        g.check(lib.greta_cuda_fused_ffn_front_peer(None, gfmt, xd.ptr, x_out.ptr, C.byref(ex), 0, dpos.ptr, gd.ptr, 1e-5, w1.qs.ptr, w1.d.ptr,
+                                                    w3.qs.ptr, w3.d.ptr, y.ptr, D, F))
+        g.check(lib.greta_cuda_device_synchronize())
+        code = C.c_int(-1)
+        g.check(lib.greta_cuda_peer_status(C.byref(code)))
+        return code.value
+
+    t0 = time.time()
+    assert consume() != 0                                      # no producer has written: the wait ran out
+    assert time.time() - t0 < 5.0                              # and it ran out promptly
+    t0 = time.time()
+    assert consume() != 0                                      # still flagged: later waits give up at once
+    assert time.time() - t0 < 5.0
+    # recovery: clear the status, let both producers write, consume again
+    g.check(lib.greta_cuda_peer_reset(None))
+    a = rng.normal(0, 1, 64 * tp).astype(np.float32)
+    wo = make_blocks(rng, ofmt, D, 64 * tp)
+    keep = []
+    for r in range(tp):
+        shard = np.ascontiguousarray(wo.reshape(D, 2 * tp, 18)[:, 2 * r:2 * r + 2]).reshape(-1)
+        ws = g.Weight(shard, gfmt, D, 64)
+        keep.append(ws)
+        exr = _exchange(g, tp, r, [b.ptr for b in slots])
+        g.check(lib.greta_cuda_gemv_peer_scatter(None, gfmt, _dev(g, a[r * 64:(r + 1) * 64]).ptr, ws.qs.ptr, ws.d.ptr, C.byref(exr), 0, dpos.ptr,
+                                                 D, 64))
+    assert consume() == 0
+    want_x = x.astype(np.float64) + O.gemv(a, wo, ofmt, D, 64 * tp)[0]
+    assert max_abs_rel(x_out.download(np.float32), want_x) < TIGHT
+
+
 # ----------------------------------------------------------------------------- attention
 @pytest.mark.parametrize("H,Hkv,Dh,L,max_seq", [(4, 4, 128, 1, 8), (4, 4, 128, 63, 64), (8, 2, 64, 200, 256),
                                                 (32, 32, 128, 2049, 2304), (64, 8, 128, 777, 1024)])
 @pytest.mark.parametrize("use_dpos", [False, True])
 @pytest.mark.parametrize("cluster", ["1", "0"])
-def test_attn_decode_matches_oracle(g, monkeypatch, H, Hkv, Dh, L, max_seq, use_dpos, cluster):
+def test_attn_decode_matches_oracle(g, tuning, H, Hkv, Dh, L, max_seq, use_dpos, cluster):
     """Both ways of merging the sequence splits: inside a thread-block cluster through distributed shared memory
-    (the default) and through the scratch buffer with tickets (GRETA_ATTN_CLUSTER=0)."""
-    monkeypatch.setenv("GRETA_ATTN_CLUSTER", cluster)
+    (the default) and through the scratch buffer with tickets (tuning switch attn_cluster = 0)."""
+    tuning("attn_cluster", int(cluster), restore=1)
     rng = np.random.default_rng(40 + L)
     q = rng.normal(0, 1, H * Dh).astype(np.float32)
     kc = rng.normal(0, 1, (Hkv, max_seq, Dh)).astype(np.float16)
@@ -509,10 +575,11 @@ def test_gemm_matches_oracle(g, name, M, N, K, a_f16, c_f16):
 
 @pytest.mark.parametrize("tile", ["128x1", "256x1", "512x1", "128x2", "256x2"])
 @pytest.mark.parametrize("name,M,N,K", [("q4_0", 600, 300, 1376), ("q8_0", 515, 260, 2048), ("q4_0", 100, 128, 4096)])
-def test_gemm_every_tile_shape(g, monkeypatch, name, M, N, K, tile):
+def test_gemm_every_tile_shape(g, tuning, name, M, N, K, tile):
     """Every tile shape (tokens x 128-row tiles per CTA, normally chosen from the problem size) gives the same
     product: ragged last token tile, ragged last row tile, odd number of blocks in K, more K stages than any ring is deep."""
-    monkeypatch.setenv("GRETA_GEMM_TILE", tile)
+    tokens, rows = (int(v) for v in tile.split("x"))
+    tuning("gemm_tile", tokens * 10 + rows, restore=0)
     ofmt, gfmt = FMTS[name]
     rng = np.random.default_rng(900 + M + len(tile))
     blk = make_blocks(rng, ofmt, N, K)

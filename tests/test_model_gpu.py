@@ -93,6 +93,74 @@ def test_long_prompt_takes_the_tensor_core_route_and_matches_oracle(pkg):
     m.close()
 
 
+@pytest.mark.parametrize("chunks", [(40, 40), (40, 10), (12, 45, 3)])
+def test_chunked_prefill_attends_to_the_cache(pkg, chunks):
+    """A prompt fed in several forward() calls: every chunk after the first starts at pos0 > 0, its queries attend to
+    the cache rows of the earlier chunks (tensor-core route for chunks of more than 32 tokens, GEMV route below).
+    Logits after the last chunk and the greedy ids that follow equal the oracle's on the whole prompt."""
+    cfg, seed = SMALL, 21
+    weights = pkg.model.synth_weights(cfg, seed)
+    prompt = pkg.model.synth_tokens(seed, sum(chunks), cfg["vocab"])
+    m = pkg.model.Model(cfg)
+    m.load_synthetic(seed)
+    ref = O.Model(cfg, weights)
+    pos = 0
+    for n in chunks:
+        lg = m.forward(prompt[pos:pos + n], pos)
+        pos += n
+    lo, xo = ref.forward(prompt, 0)
+    assert max_abs_rel(m.hidden(chunks[-1] - 1), xo) < 1e-4
+    assert max_abs_rel(lg, lo) < 1e-4
+    tok = int(np.argmax(lg))
+    assert tok == O.argmax(lo)[0]
+    m.begin_decode(tok, pos)
+    for _ in range(6):
+        m.decode_step()
+    got = m.read_generated(6)
+    want, gaps = ref.generate(prompt, 7)
+    assert min(gaps) > 1e-5
+    assert [tok] + got == want
+    m.close()
+
+
+def test_decode_loop_is_refused_past_the_cache(pkg):
+    """The device-side loop advances the position by itself: the host refuses the step that would read or write a
+    cache row that does not exist, and generation requests that cannot fit are refused up front."""
+    cfg = dict(SMALL, max_seq=24)
+    prompt = pkg.model.synth_tokens(2, 20, cfg["vocab"])
+    m = pkg.model.Model(cfg)
+    m.load_synthetic(2)
+    tok = int(np.argmax(m.forward(prompt, 0)))
+    m.begin_decode(tok, 20)
+    for _ in range(4):                       # positions 20..23 exist
+        m.decode_step()
+    with pytest.raises(pkg.ffi.GretaError, match="exceeds max_seq_len"):
+        m.decode_step()                      # position 24 does not
+    assert len(m.read_generated(4)) == 4
+    with pytest.raises(pkg.ffi.GretaError, match="exceeds max_seq_len"):
+        m.generate(prompt, 6)                # 20 + 5 decode steps do not fit in 24 rows
+    assert len(m.generate(prompt, 5)[0]) == 5
+    with pytest.raises(pkg.ffi.GretaError):
+        m.begin_decode(tok, 24)
+    m.close()
+
+
+def test_generation_stops_at_the_end_of_sequence_id(pkg):
+    """generate_tokens ends with the first end-of-sequence id it samples (the reference's loop breaks on its
+    tokenizer's id); the ids before it are the ones an unbounded run produces."""
+    cfg, seed = SMALL, 5
+    prompt = pkg.model.synth_tokens(seed, 16, cfg["vocab"])
+    m = pkg.model.Model(cfg)
+    m.load_synthetic(seed)
+    full, _ = m.generate(prompt, 40)
+    for stop_at in (0, 7, 17, 33):           # inside the first chunk of the device loop, on a chunk boundary, later
+        eos = full[stop_at]
+        first = full.index(eos)
+        assert m.generate_until(prompt, 40, eos) == full[:first + 1]
+    assert m.generate_until(prompt, 40, cfg["vocab"] + 5) == full      # an id that never comes: runs to max_tokens
+    m.close()
+
+
 def test_persistent_decode_step_gives_the_same_ids(pkg, monkeypatch):
     """GRETA_PERSISTENT_STEP=1: all layers of a decode step in one persistent kernel (grid barriers between the
     phases) - same greedy ids as the oracle and as the operator-by-operator graph."""

@@ -105,7 +105,7 @@ def test_reference_per_head_scales_are_max_abs(golden):
 
 
 def test_q4_0_equals_reference_int4_storage():
-    """BASELINE's Q4_0 value (q-8)*d maps losslessly onto the reference's INT4 (v=q-8, s=fp32(d))."""
+    """The GGUF Q4_0 value (q-8)*d maps losslessly onto the reference's INT4 (v=q-8, s=fp32(d))."""
     rng = np.random.default_rng(1)
     nb = 64
     blk = np.empty((nb, 18), np.uint8)
@@ -139,6 +139,37 @@ def test_rmsnorm_matches_cpu_reference(golden):
     ka = O.rmsnorm(np.array([[1, 2, 3, 4]], np.float32), np.ones(4, np.float32), 1e-5)
     assert np.allclose(ka, golden["ka_rms_y"], rtol=3e-7)
     assert np.allclose(ka[0], np.array([1, 2, 3, 4]) / np.sqrt(7.5), atol=1e-5)  # cpu_ref_test.cpp:36-41
+
+
+@pytest.mark.parametrize("mode,tag", [(0, "fp64"), (1, "fp32")])
+def test_attention_matches_the_reference_cpu_attention(golden, mode, tag):
+    """oracle_attention_decode against compute_attention_ref_fp64 / _fp32, the CPU references inside the reference's
+    block scheduler (src/inference/src/block_scheduler.cpp:721-864): same arithmetic, same order."""
+    H, Hkv, Dh, L, S = (int(v) for v in golden["attn_shape"])
+    q, k, v, want = golden["attn_q"], golden["attn_k"], golden["attn_v"], golden["attn_out_" + tag]
+    got32 = O.attention_decode(q, k, v, H, Hkv, Dh, L, S, 0.125, mode=mode)                     # the reference's fp32 cache
+    got16 = O.attention_decode(q, k.astype(np.float16).view(np.uint16), v.astype(np.float16).view(np.uint16), H, Hkv, Dh, L, S, 0.125,
+                               mode=mode)                                                        # the same values as an fp16 cache
+    assert np.array_equal(got32.view(np.uint32), want.view(np.uint32))
+    assert np.array_equal(got16.view(np.uint32), want.view(np.uint32))
+    # rows past seq_len are not read: 70 of 80 rows were attended
+    k2 = k.copy()
+    k2[:, L:] = 1e9
+    assert np.array_equal(O.attention_decode(q, k2, v, H, Hkv, Dh, L, S, 0.125, mode=mode), got32)
+
+
+def test_host_dequantiser_matches_the_reference_read_weight_value(golden):
+    """oracle_dequant_ref_int4 / _int8 and the fp16 decoder against read_weight_value
+    (src/inference/src/block_scheduler.cpp:639-671) on the planes the reference's own loader produced."""
+    got4 = O.dequant_ref_int4(golden["int4_down_packed"], golden["int4_down_scales"])
+    assert np.array_equal(got4.view(np.uint32), golden["rwv_int4_down"].view(np.uint32))
+    got8 = O.dequant_ref_int8(golden["int8_down_w"], golden["int8_down_scales"])
+    assert np.array_equal(got8.view(np.uint32), golden["rwv_int8_down"].view(np.uint32))
+    bits = golden["rwv_f16_bits"]
+    gotf, want = O.f16_bits_to_f32(bits), golden["rwv_f16"]
+    nan_in = ((bits & 0x7C00) == 0x7C00) & ((bits & 0x03FF) != 0)     # that decoder turns fp16 NaNs into infinities; the
+    assert np.isinf(want[nan_in]).all() and np.isnan(gotf[nan_in]).all()   # oracle (and the device intrinsic) keep them NaN
+    assert np.array_equal(gotf[~nan_in].view(np.uint32), want[~nan_in].view(np.uint32))
 
 
 def test_live_reference_library_when_present(golden):

@@ -1,5 +1,5 @@
-"""Host-side logic of the multi-GPU path, on CPU with two processes: the rendezvous star that
-bench.py uses to hand out the NCCL id and gather timings, and the tensor-parallel algebra (row-split
+"""Host-side logic of the multi-GPU path, on CPU with two processes: the package's rendezvous star
+(hand-out of the NCCL id, gathering of timings), and the tensor-parallel algebra (row-split
 and column-split shards from the host layer's tensor_shard, partial products summed across ranks)
 checked with the CPU oracle standing in for the kernels."""
 import ctypes as C
@@ -28,10 +28,9 @@ def _rank_main(rank, world, port, q):
     import sys
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
-    import bench
     from oracle import oracle as O
     pkg = load_package()
-    ranks = bench.Ranks()
+    ranks = pkg.rendezvous.Ranks()
     # 1. id hand-out: every rank ends up with rank 0's 128 bytes
     uid = bytes(range(128)) if rank == 0 else b"\0" * 128
     got = ranks.bcast(uid, 128)
