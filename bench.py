@@ -13,9 +13,10 @@ arg-max) after a 512-token random prompt.  The headline numbers printed in one J
              SwiGLU), timed live over the 32 layers' distinct weights (3.6 GB touched per pass, far
              beyond the 126 MB L2), against the measured copy bandwidth of this pool's B200s;
   cpu_baseline  the CPU port of the reference's kernel math (oracle/, OpenMP) on a bounded sample.
-With --gpus N > 1 (launched under torchrun, one rank per GPU) the same model runs tensor-parallel
-over NCCL: the weights are sharded Megatron-style and each layer all-reduces twice.  Total work is
-fixed, so scaling is "strong".
+With --gpus N > 1 (launched under torchrun, one rank per GPU) the same model runs tensor-parallel: the
+weights are sharded Megatron-style, and the exchange after each row-parallel projection is fused into
+the GEMV kernels on either side of it over peer memory (--exchange nccl: an all-reduce instead).  Total
+work is fixed, so scaling is "strong".
 
 --impl reference times the CPU port itself (the reference ships no CPU implementation of this
 path and its GPU kernels are HIP/gfx942 only) on the host cores.
@@ -61,7 +62,7 @@ class ClockSampler:
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "20",
                                           "-i", str(self.device)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except Exception:
@@ -89,65 +90,108 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------- CPU baseline (oracle port)
-def cpu_decode_layer_seconds(cfg, n_layers, reps):
-    """Times the CPU port on `n_layers` decoder layers of the 7B shape at batch 1 (fp32 accumulation, OpenMP over
-    output rows) and returns seconds per layer.  Weights are random GGUF Q4_0 blocks (values do not affect time)."""
+class CpuDecodeSample:
+    """The CPU port of the reference's kernel math (oracle/, OpenMP, fp32 accumulation) on a bounded sample of the decode
+    workload: ONE whole decode step - embedding, every operator of the layer (norms, the seven quantised projections, RoPE,
+    cache write, attention over the cache, SwiGLU, residuals), final norm, LM head - of a 1-layer and of a 2-layer model of
+    the workload's shape at the workload's context length.  The difference of the two is the cost of a layer, the rest is
+    the per-step fixed cost; a step of the full model is fixed + layers x layer.  The reference has no batch dimension
+    (one KV cache, one sequence): a batch of B sequences costs it B steps."""
+
+    def __init__(self, pkg, cfg, context, batch=1):
+        from oracle import oracle as O
+        self.O, self.cfg, self.batch = O, cfg, batch
+        if os.environ.get("TORCHELASTIC_RUN_ID"):        # torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU leg runs
+            O.set_num_threads(os.cpu_count() or 1)       # on rank 0 alone and may use the whole host
+        small = dict(cfg, num_layers=2, max_seq=context + 8)
+        weights = pkg.model.synth_weights(small, SEED)
+        self.models = []
+        for n in (1, 2):
+            c = dict(small, num_layers=n)
+            w = dict(weights, layers=weights["layers"][:n])
+            m = O.Model(c, w)
+            m.k_cache[:] = 0x3C00                          # a cache of ones up to the context: the work does not depend on the values
+            m.v_cache[:] = 0x3C00
+            self.models.append(m)
+        self.context = context
+        self.tok = np.array([1], np.int32)
+        self.cores = O.num_threads()
+
+    def one_step_seconds(self):
+        """Seconds the full model's decode step takes on the CPU port, from one timed step of each small model."""
+        O = self.O
+        O.set_model_acc(O.ACC_FAST_F32)
+        try:
+            t = []
+            for m in self.models:
+                t0 = time.perf_counter()
+                m.forward(self.tok, self.context)
+                t.append(time.perf_counter() - t0)
+        finally:
+            O.set_model_acc(O.ACC_F64)
+        layer = max(t[1] - t[0], 1e-9)
+        fixed = max(t[0] - layer, 0.0)
+        return self.batch * (fixed + self.cfg["num_layers"] * layer), layer, fixed
+
+    def describe(self):
+        return (f"one decode step (all operators, context {self.context}) of a 1-layer and a 2-layer model of the workload's shape on the "
+                f"CPU port (oracle/greta_oracle.cpp, fp32 accumulation, OpenMP), step = fixed + {self.cfg['num_layers']} x layer"
+                + (f", x {self.batch} sequences one after another (the reference has no batch dimension)" if self.batch > 1 else ""))
+
+
+def cpu_q8_0_gemv_4096(reps=20):
+    """The reference's CPU-runnable case: one Q8_0 GEMV, x fp32 [1 x 4096], W [4096 x 4096], seed 0, on the CPU port."""
     from oracle import oracle as O
-    if os.environ.get("TORCHELASTIC_RUN_ID"):        # torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU leg runs
-        O.set_num_threads(os.cpu_count() or 1)       # on rank 0 alone and may use the whole host
     rng = np.random.default_rng(0)
-    D, F = cfg["dim"], cfg["hidden_dim"]
-    shapes = [(D, D)] * 4 + [(F, D), (F, D), (D, F)]
-
-    def blocks(n, k):
-        b = rng.integers(0, 256, (n * (k // 32), 18), dtype=np.uint8)
-        b[:, :2] = np.array([0.002], np.float16).view(np.uint8)
-        return b.reshape(-1)
-
-    layers = [[blocks(n, k) for n, k in shapes] for _ in range(n_layers)]
-    x = rng.normal(0, 1, D).astype(np.float32)
-    xf = rng.normal(0, 1, F).astype(np.float32)
-    O.gemv(x, layers[0][0], O.FMT_Q4_0, D, D, O.ACC_FAST_F32)      # warm-up (thread pool, page faults)
+    N = K = 4096
+    nb = N * (K // 32)
+    blk = np.empty((nb, 34), np.uint8)
+    blk[:, :2] = (np.abs(rng.normal(0, 0.02, nb)) / 127).astype(np.float16).view(np.uint8).reshape(nb, 2)
+    blk[:, 2:] = rng.integers(-127, 128, (nb, 32), dtype=np.int8).view(np.uint8)
+    x = rng.normal(0, 1, K).astype(np.float32)
+    blk = blk.reshape(-1)
+    O.gemv(x, blk, O.FMT_Q8_0, N, K, O.ACC_FAST_F32)
     best = 1e30
     for _ in range(reps):
         t0 = time.perf_counter()
-        for lw in layers:
-            for w, (n, k) in zip(lw, shapes):
-                O.gemv(x if k == D else xf, w, O.FMT_Q4_0, n, k, O.ACC_FAST_F32)
-        best = min(best, (time.perf_counter() - t0) / n_layers)
-    return best, O.num_threads()
+        O.gemv(x, blk, O.FMT_Q8_0, N, K, O.ACC_FAST_F32)
+        best = min(best, time.perf_counter() - t0)
+    alg = nb * 34 + K * 4 + N * 4
+    return {"us": best * 1e6, "gb_per_s": alg / best / 1e9, "algorithmic_bytes": alg, "cores": O.num_threads()}
 
 
-def cpu_baseline(cfg, n_layers=2, reps=3):
-    sec_per_layer, cores = cpu_decode_layer_seconds(cfg, n_layers, reps)
-    tok_s = 1.0 / (sec_per_layer * cfg["num_layers"])
-    return {"value": tok_s, "unit": "tok/s", "cores": cores, "kind": "port",
-            "sample": f"{n_layers} decoder layers of the 7B shape (7 Q4_0 GEMVs each, batch 1, fp32 accumulate), best of {reps}, "
-                      f"scaled to {cfg['num_layers']} layers; attention, LM head and element-wise work not included"}
+def cpu_baseline(pkg, cfg, context, batch=1, budget_s=10.0):
+    sample = CpuDecodeSample(pkg, cfg, context, batch)
+    sample.one_step_seconds()                              # warm-up (thread pool, page faults)
+    best, t_end, reps = 1e30, time.perf_counter() + budget_s, 0
+    while reps < 3 or time.perf_counter() < t_end:
+        best = min(best, sample.one_step_seconds()[0])
+        reps += 1
+    return {"value": batch / best, "unit": "tok/s", "cores": sample.cores, "kind": "port",
+            "sample": sample.describe() + f"; best of {reps} in about {budget_s:.0f} s",
+            "q8_0_gemv_4096x4096_cpu": cpu_q8_0_gemv_4096()}
 
 
-def run_reference(args, ranks, cfg):
-    """--impl reference: the CPU port of the reference's kernel math on the host cores."""
+def run_reference(args, ranks, cfg, pkg, batch, context):
+    """--impl reference: the CPU port of the reference's kernel math on the host cores (rank 0 alone)."""
     if ranks.rank != 0:
         return
-    n_layers = 2
-    for _ in range(max(args.warmup, 1) if args.warmup < 2 else 1):
-        cpu_decode_layer_seconds(cfg, 1, 1)
-    times = []
-    for _ in range(args.steps):
-        sec, cores = cpu_decode_layer_seconds(cfg, n_layers, 1)
-        times.append(sec * cfg["num_layers"])
+    sample = CpuDecodeSample(pkg, cfg, context, batch)
+    for _ in range(max(1, min(args.warmup, 3))):
+        sample.one_step_seconds()
+    steps = max(1, min(args.steps, 200))
+    times = [sample.one_step_seconds()[0] for _ in range(steps)]
     ms = 1e3 * float(np.mean(times))
-    val = 1e3 / ms
-    sample = (f"each step = {n_layers} decoder layers of the 7B shape on the CPU port (oracle/greta_oracle.cpp, fp32 accumulate, "
-              f"OpenMP), scaled to {cfg['num_layers']} layers")
+    val = 1e3 * batch / ms
     print(json.dumps({
-        "impl": "reference", "metric": METRIC, "value": val, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
+        "impl": "reference", "metric": metric_name(args), "value": val, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "q4_0 weights, fp32 activations/accumulation", "data": "synthetic",
-        "config": {"workload": "Llama-2-7B-shaped decode, batch 1, Q4_0, CPU port of the reference kernel math",
-                   "note": "the reference has no CPU implementation of this path and its GPU kernels are HIP/gfx942 only"},
-        "cpu_baseline": {"value": val, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+        "config": dict(workload_config(args, cfg, 1, "host cores"),
+                       note="the reference has no CPU implementation of this path and its GPU kernels are HIP/gfx942 only: this arm is "
+                            "the CPU port of its kernel math"),
+        "cpu_baseline": {"value": val, "unit": "tok/s", "cores": sample.cores, "kind": "port",
+                         "sample": sample.describe() + f"; mean of {steps} samples"},
         "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -369,7 +413,7 @@ def main():
     from gretacore_v3_b200.model import LLAMA2_7B, LLAMA3_70B
     cfg = dict(LLAMA2_7B if args.workload == "c4" else LLAMA3_70B)
     if args.impl == "reference":
-        run_reference(args, ranks, cfg)
+        run_reference(args, ranks, cfg, pkg, 1, args.prompt_len + max(args.warmup, 3) + args.steps // 2)
         return
 
     import ctypes as C
@@ -416,7 +460,6 @@ def main():
     t1 = time.time()
     launches = lib.greta_cuda_launch_count() - launches0
     ms = ranks.gather_max(float(ms))
-    clocks = sampler.stop(t0, t1) if ranks.rank == 0 else None
     ids_dev = model.read_generated(max(args.warmup, 3) + args.steps)
 
     # ---- e2e: host-driven loop (token id up, sampled id down, every step), restarted from the same state
@@ -424,7 +467,9 @@ def main():
     ids_e2e, ms_e2e = model.decode_e2e(first, pos, max(args.warmup, 3))      # warm-up of this loop
     ids_e2e, ms_e2e = model.decode_e2e(first, pos, args.steps)
     ms_e2e = ranks.gather_max(float(ms_e2e))
+    clocks = sampler.stop(t0, time.time()) if ranks.rank == 0 else None      # sampled over both timed loops
     same = ids_e2e == ids_dev[:args.steps]
+    oracle_check = check_against_stored_oracle_ids(args, cfg, prompt, [first] + ids_dev, [first] + ids_e2e)
 
     if ranks.rank != 0:
         return
@@ -443,29 +488,57 @@ def main():
     # whole-step view of the same bound: bytes one decode step must read
     step_bytes = model_step_bytes(cfg, pos + args.steps // 2)
     out = {
-        "metric": METRIC if args.workload == "c4" else "decode_tokens_per_s_llama3_70b_shape_q4_0_batch1",
+        "metric": metric_name(args),
         "value": tok_s, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "q4_0 weights (int8 dot products on 23-bit fixed-point activations), fp32 accumulation, fp16 KV cache",
         "data": "synthetic",
-        "config": {"workload": ("Llama-2-7B-shaped model (32 layers, hidden 4096, 32 heads x 128, FFN 11008, vocab 32000), random-init "
-                                "Q4_0 weights, fp16 LM head, 512-token random prompt then greedy decode at batch 1"
-                                if args.workload == "c4" else
-                                "Llama-3-70B-shaped model (80 layers, hidden 8192, GQA 64/8 heads x 128, FFN 28672, vocab 128256), random-init "
-                                "Q4_0 weights, fp16 LM head, random prompt then greedy decode at BATCH 1 (the 70B shape at batch 1)"),
-                   "prompt_len": args.prompt_len, "parallelism": (f"tp{tp}, exchange {args.exchange}" if tp > 1 else "single GPU"),
-                   "l2_defeat": f"every step streams {model_step_bytes(cfg, pos) / 1e9:.1f} GB of distinct weights (L2 is 126 MB)", "seed": SEED},
+        "config": workload_config(args, cfg, tp, f"tp{tp}, exchange {args.exchange}" if tp > 1 else "single GPU"),
         "clocks": clocks, "gpu_launches": int(launches),
         "e2e": {"value": 1e3 * args.steps / ms_e2e, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4,
                 "ids_match_device_loop": bool(same)},
+        "ids_match_oracle": oracle_check["match"], "ids_checked": oracle_check,
         "roofline": roofline,
         "step_hbm": {"bytes_per_step": step_bytes, "achieved_gbs": step_bytes / (ms / args.steps) / 1e6,
                      "frac_of_peak": step_bytes / (ms / args.steps) / 1e6 / (peak * tp),
                      "note": "aggregate over the N GPUs; the fraction is of N x the measured per-GPU peak"},
     }
     if not args.no_cpu_baseline and tp == 1:                 # reported at N=1 only
-        out["cpu_baseline"] = cpu_baseline(cfg)
+        out["cpu_baseline"] = cpu_baseline(pkg, cfg, pos + max(args.warmup, 3) + args.steps // 2)
     print(json.dumps(out))
+
+
+def metric_name(args):
+    return METRIC if args.workload == "c4" else "decode_tokens_per_s_llama3_70b_shape_q4_0_batch1"
+
+
+def workload_config(args, cfg, tp, parallelism):
+    shape = (f"{cfg['num_layers']} layers, hidden {cfg['dim']}, {cfg['num_heads']}/{cfg['num_heads_kv']} heads x {cfg['head_dim']}, "
+             f"FFN {cfg['hidden_dim']}, vocab {cfg['vocab']}")
+    name = "Llama-2-7B-shaped" if args.workload == "c4" else "Llama-3-70B-shaped"
+    return {"workload": f"{name} model ({shape}), random-init Q4_0 weights, fp16 LM head, {args.prompt_len}-token random prompt then greedy "
+                        f"decode at batch 1",
+            "prompt_len": args.prompt_len, "parallelism": parallelism,
+            "l2_defeat": f"every step streams {model_step_bytes(cfg, args.prompt_len) / 1e9:.1f} GB of distinct weights (L2 is 126 MB)",
+            "seed": SEED}
+
+
+def check_against_stored_oracle_ids(args, cfg, prompt, ids_device_loop, ids_host_loop):
+    """Compares the ids of the timed runs with the CPU oracle's ids for the same seeded workload, stored in
+    tests/golden/model_ids.npz (the oracle needs minutes of host time for them; tests/golden/make_model_ids.py wrote
+    them).  Only the default workload (7B shape, seed 3, 512-token prompt) has stored ids; `match` is None otherwise."""
+    path = os.path.join(ROOT, "tests", "golden", "model_ids.npz")
+    name = "llama2_7b_seed3"
+    if args.workload != "c4" or not os.path.exists(path):
+        return {"match": None, "why": "no stored oracle ids for this workload"}
+    gold = np.load(path)
+    want, wprompt = gold[name + ".ids"][0].tolist(), gold[name + ".prompts"][0]
+    if len(prompt) != len(wprompt) or not np.array_equal(prompt, wprompt):
+        return {"match": None, "why": "prompt differs from the stored workload's"}
+    n_dev, n_host = min(len(want), len(ids_device_loop)), min(len(want), len(ids_host_loop))
+    ok = ids_device_loop[:n_dev] == want[:n_dev] and ids_host_loop[:n_host] == want[:n_host]
+    return {"match": bool(ok), "device_loop_ids_compared": n_dev, "host_loop_ids_compared": n_host,
+            "oracle_min_top2_gap": float(gold[name + ".gaps"][0].min())}
 
 
 def model_step_bytes(cfg, pos):

@@ -51,7 +51,7 @@ __global__ void __launch_bounds__(CL_WARPS * 32) attn_cluster_kernel(const AttnP
   pdl_launch_dependents();
   pdl_wait();  // q, the position and the newest cache row come from the previous kernel
   const uint32_t split = cluster.block_rank(), head = blockIdx.y, qi = blockIdx.z;
-  const uint32_t L = min((p.d_pos ? __ldcg(p.d_pos) + 1 : p.len0) + qi, p.max_seq);  // never past the cache
+  const uint32_t L = min((p.d_pos ? __ldcg(p.d_pos) + 1 : p.len0) + qi * p.len_step, p.max_seq);  // never past the cache
   const uint32_t chunk = (L + CL_SPLITS - 1) / CL_SPLITS;
   const uint32_t k0 = split * chunk, k1 = min(L, k0 + chunk);
   const int tid = threadIdx.x;
@@ -176,7 +176,7 @@ int attn_decode_impl(greta_stream_t stream, const float *q, const void *kc, cons
   uint32_t splits = std::max(1u, std::min({want, (uint32_t)MAX_SPLITS, (Lmax + 63) / 64}));
   AttnParams p{};
   p.q = q; p.kc = kc; p.vc = vc; p.o = o; p.d_pos = d_pos; p.len0 = seq_len;
-  p.H = H; p.Hkv = Hkv; p.max_seq = max_seq; p.scale = scale; p.splits = splits;
+  p.H = H; p.Hkv = Hkv; p.max_seq = max_seq; p.scale = scale; p.splits = splits; p.len_step = 1;
   if (splits > 1) {
     GRETA_REQUIRE(scratch && scratch_bytes >= greta_cuda_attn_decode_scratch_bytes(H, Dh),
                   "attn_decode: scratch of %zu bytes needed, %zu given", greta_cuda_attn_decode_scratch_bytes(H, Dh), scratch_bytes);
@@ -260,8 +260,23 @@ int greta_cuda_attn_prefill(greta_stream_t stream, const float *q, const void *k
   GRETA_REQUIRE(S <= 65535, "attn_prefill: S=%u exceeds 65535", S);
   AttnParams p{};
   p.q = q; p.kc = kc; p.vc = vc; p.o = o; p.d_pos = nullptr; p.len0 = pos0 + 1;
-  p.H = H; p.Hkv = Hkv; p.max_seq = max_seq; p.scale = scale; p.splits = 1;
+  p.H = H; p.Hkv = Hkv; p.max_seq = max_seq; p.scale = scale; p.splits = 1; p.len_step = 1;
   return launch_attn<__half>((cudaStream_t)stream, p, S, Dh);
+}
+
+int greta_cuda_attn_prefill_f32(greta_stream_t stream, const float *q, const float *k, const float *v, float *o, uint32_t S, uint32_t H,
+                                uint32_t Hkv, uint32_t Dh, float scale, int causal) {
+  if (S == 0) return GRETA_OK;
+  GRETA_REQUIRE(H && Hkv && H % Hkv == 0, "attn_prefill_f32: num_heads=%u must be a positive multiple of num_heads_kv=%u", H, Hkv);
+  GRETA_REQUIRE(q && k && v && o, "attn_prefill_f32: null pointer");
+  GRETA_REQUIRE(aligned16(q) && aligned16(k) && aligned16(v), "attn_prefill_f32: pointers must be 16-byte aligned");
+  GRETA_REQUIRE(S <= 65535, "attn_prefill_f32: S=%u exceeds 65535", S);
+  AttnParams p{};
+  p.q = q; p.kc = k; p.vc = v; p.o = o; p.d_pos = nullptr;
+  p.len0 = causal ? 1 : S; p.len_step = causal ? 1 : 0;
+  p.H = H; p.Hkv = Hkv; p.max_seq = S; p.scale = scale; p.splits = 1;
+  p.head_stride = Dh; p.row_stride = Hkv * Dh;  // K/V are [S][Hkv][Dh]
+  return launch_attn<float>((cudaStream_t)stream, p, S, Dh);
 }
 
 int greta_cuda_rope(greta_stream_t stream, float *x, uint32_t S, uint32_t H, uint32_t Dh, float base, uint32_t pos_offset,

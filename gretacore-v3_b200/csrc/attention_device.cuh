@@ -47,6 +47,10 @@ struct AttnParams {
   uint32_t H, Hkv, max_seq;
   float scale;
   uint32_t splits;
+  // Element strides of the K/V arrays: the cache [Hkv][max_seq][Dh] has head_stride = max_seq * Dh and row_stride = Dh;
+  // the prompt-major arrays [S][Hkv][Dh] of the reference's prefill entry have head_stride = Dh, row_stride = Hkv * Dh.
+  // 0 = the cache layout.  len_step: keys query z sees beyond query 0's (1 = causal, 0 = every query sees len0 keys).
+  uint32_t head_stride, row_stride, len_step;
   uint32_t *counters;    // [H] zero on entry, left zero
   float *partial;        // [H][splits][Dh + 2]
 };
@@ -114,8 +118,9 @@ __device__ __forceinline__ void attn_partial(const AttnParams &p, const uint32_t
   const int sub = lane & 7, grp = lane >> 3;  // 8 lanes per key, 4 keys per warp step
   const uint32_t kvh = head / (p.H / p.Hkv);
 
-  const KV *kbase = reinterpret_cast<const KV *>(p.kc) + (size_t)kvh * p.max_seq * Dh + sub * DPL;
-  const KV *vbase = reinterpret_cast<const KV *>(p.vc) + (size_t)kvh * p.max_seq * Dh + sub * DPL;
+  const size_t hs = p.head_stride ? p.head_stride : (size_t)p.max_seq * Dh, rs = p.row_stride ? p.row_stride : Dh;
+  const KV *kbase = reinterpret_cast<const KV *>(p.kc) + (size_t)kvh * hs + sub * DPL;
+  const KV *vbase = reinterpret_cast<const KV *>(p.vc) + (size_t)kvh * hs + sub * DPL;
 
   float qv[DPL];
   {
@@ -136,8 +141,8 @@ __device__ __forceinline__ void attn_partial(const AttnParams &p, const uint32_t
     const uint32_t ta = tw + grp, tb = tw + 4 * ATT_WARPS + grp;
     const bool va = ta < k1, vb = tb < k1;
     float ka[DPL], kb[DPL], xa[DPL], xb[DPL];
-    if (va) { load_row<KV, DPL, CG>(kbase + (size_t)ta * Dh, ka); load_row<KV, DPL, CG>(vbase + (size_t)ta * Dh, xa); }
-    if (vb) { load_row<KV, DPL, CG>(kbase + (size_t)tb * Dh, kb); load_row<KV, DPL, CG>(vbase + (size_t)tb * Dh, xb); }
+    if (va) { load_row<KV, DPL, CG>(kbase + (size_t)ta * rs, ka); load_row<KV, DPL, CG>(vbase + (size_t)ta * rs, xa); }
+    if (vb) { load_row<KV, DPL, CG>(kbase + (size_t)tb * rs, kb); load_row<KV, DPL, CG>(vbase + (size_t)tb * rs, xb); }
     float sa = 0.f, sb = 0.f;
     if (va) {
 #pragma unroll
@@ -267,7 +272,7 @@ template <typename KV, int DPL, int NW, bool CG>
 __device__ void attn_body(const AttnParams &p, const uint32_t split, const uint32_t head, const uint32_t qi) {
   constexpr int Dh = DPL * 8;
   __shared__ uint32_t sm_last;
-  const uint32_t L = min((p.d_pos ? __ldcg(p.d_pos) + 1 : p.len0) + qi, p.max_seq);  // never past the cache
+  const uint32_t L = min((p.d_pos ? __ldcg(p.d_pos) + 1 : p.len0) + qi * p.len_step, p.max_seq);  // never past the cache
   const uint32_t chunk = (L + p.splits - 1) / p.splits;
   const uint32_t k0 = split * chunk, k1 = min(L, k0 + chunk);
   const int tid = threadIdx.x;

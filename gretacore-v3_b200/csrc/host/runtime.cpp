@@ -1,5 +1,6 @@
 // L0 (gcore::rt on CUDA), the launch_* kernel entry points and L1
 // (GretaCompute / GretaFused), all written against the C ABI of greta_cuda.h.
+#include <algorithm>
 #include <cstdio>
 #include <cstring>
 
@@ -9,6 +10,8 @@
 namespace gcore::rt {
 
 namespace cuda {
+
+static constexpr size_t kQueryScratchBytes = 256 * 128 * sizeof(float);
 
 // ------------------------------------------------------------------ Buffer
 Buffer::~Buffer() { free(); }
@@ -137,7 +140,7 @@ GretaResult GretaContextCuda::initialize() {
   }
   // scratch for decode attention issued through the reference-signature launchers (<= 256 heads of 128)
   std::string err;
-  if (!attn_scratch_.allocate(greta_cuda_attn_decode_scratch_bytes(256, 128), BufferUsage::DeviceOnly, GretaDataType::FP32, &err))
+  if (!attn_scratch_.allocate(greta_cuda_attn_decode_scratch_bytes(256, 128) + kQueryScratchBytes, BufferUsage::DeviceOnly, GretaDataType::FP32, &err))
     return GretaResult::ERROR_OUT_OF_MEM;
   greta_cuda_memset(attn_scratch_.data(), 0, attn_scratch_.size(), nullptr);
   greta_cuda_device_synchronize();
@@ -151,8 +154,30 @@ GretaMemory *GretaContextCuda::create_memory(size_t size, GretaDataType type, bo
   return new GretaMemoryCuda(size, type, host_visible);
 }
 void *GretaContextCuda::attention_scratch(size_t *bytes) const {
-  if (bytes) *bytes = attn_scratch_.size();
+  if (bytes) *bytes = attn_scratch_.size() - kQueryScratchBytes;
   return const_cast<void *>(attn_scratch_.data());
+}
+float *GretaContextCuda::query_scratch() const {
+  return reinterpret_cast<float *>(static_cast<char *>(const_cast<void *>(attn_scratch_.data())) + attn_scratch_.size() - kQueryScratchBytes);
+}
+
+// ------------------------------------------------------------------ GretaArena
+GretaArena::GretaArena(size_t chunk_size) : chunk_size_(chunk_size) {}
+
+bool GretaArena::allocate(size_t size, void **out_ptr, std::string *err) {
+  if (!out_ptr) return host::fail(err, "GretaArena::allocate: null out pointer");
+  std::lock_guard<std::mutex> lock(mutex_);
+  const size_t need = (size + 255) / 256 * 256;
+  if (chunks_.empty() || current_offset_ + need > chunks_.back()->size()) {
+    auto chunk = std::make_unique<Buffer>();
+    if (!chunk->allocate(std::max(chunk_size_, need), BufferUsage::DeviceOnly, GretaDataType::FP8_E4M3, err)) return false;
+    chunks_.push_back(std::move(chunk));
+    current_offset_ = 0;
+  }
+  *out_ptr = static_cast<char *>(chunks_.back()->data()) + current_offset_;
+  current_offset_ += need;
+  total_allocated_ += need;
+  return true;
 }
 
 // ------------------------------------------------------------------ launch_* entry points
@@ -282,6 +307,26 @@ void launch_flash_attention_decode_f16kv(cudaStream_t stream, const float *Q, co
   void *s = ctx_scratch(&sb);
   note(greta_cuda_attn_decode(stream, Q, K, V, O, d_pos, seq_len, num_heads, num_heads_kv, head_dim, max_seq_len, scale, s, sb));
 }
+void launch_flash_attention_decode_fused_rope(cudaStream_t stream, const float *Q, const float *K, const float *V, float *O, uint32_t num_heads,
+                                              const uint32_t *d_pos, uint32_t max_seq_len, uint32_t head_dim, float scale, float rope_base) {
+  if (head_dim > 128 || num_heads == 0) return;
+  if (num_heads > 256 || !d_pos) {
+    note(GRETA_ERR_INVALID_ARGS);
+    return;
+  }
+  size_t sb = 0;
+  void *s = ctx_scratch(&sb);
+  float *qr = static_cast<GretaContextCuda &>(GretaContext::instance()).query_scratch();
+  int rc = greta_cuda_memcpy_d2d(qr, Q, (size_t)num_heads * head_dim * sizeof(float), stream);
+  if (rc == GRETA_OK) rc = greta_cuda_rope(stream, qr, 1, num_heads, head_dim, rope_base, 0, d_pos);
+  if (rc == GRETA_OK) rc = greta_cuda_attn_decode_f32cache(stream, qr, K, V, O, d_pos, 0, num_heads, num_heads, head_dim, max_seq_len, scale, s, sb);
+  note(rc);
+}
+void launch_flash_attention_prefill(cudaStream_t stream, const float *Q, const float *K, const float *V, float *O, uint32_t seq_len,
+                                    uint32_t num_heads, uint32_t num_heads_kv, uint32_t head_dim, float scale, bool causal) {
+  if (head_dim > 128) return;
+  note(greta_cuda_attn_prefill_f32(stream, Q, K, V, O, seq_len, num_heads, num_heads_kv, head_dim, scale, causal ? 1 : 0));
+}
 void launch_flash_attention_prefill_f16kv(cudaStream_t stream, const float *Q, const uint16_t *K, const uint16_t *V, float *O, uint32_t seq_len,
                                           uint32_t pos0, uint32_t num_heads, uint32_t num_heads_kv, uint32_t head_dim, uint32_t max_seq_len,
                                           float scale) {
@@ -348,8 +393,12 @@ GretaResult GretaCompute::gemm(GretaStream *stream, GretaMemory *A, GretaMemory 
   } else if (fmt == GRETA_FMT_Q4_0 || fmt == GRETA_FMT_Q8_0) {
     void *ws = nullptr;
     if (!a_f16) {
-      size_t need = greta_cuda_gemm_workspace_bytes(M, K);
-      if (g_gemm_ws.size() < need && !g_gemm_ws.allocate(need, gcore::rt::cuda::BufferUsage::DeviceOnly)) return GretaResult::ERROR_OUT_OF_MEM;
+      const size_t need = greta_cuda_gemm_workspace_bytes(M, K);
+      if (g_gemm_ws.size() < need) {  // growing allocates (and frees): never inside a stream capture
+        int capturing = 0;
+        if (greta_cuda_stream_is_capturing(H(stream), &capturing) != GRETA_OK || capturing) return GretaResult::ERROR_GRAPH_CAPTURE;
+        if (!g_gemm_ws.allocate(need, gcore::rt::cuda::BufferUsage::DeviceOnly)) return GretaResult::ERROR_OUT_OF_MEM;
+      }
       ws = g_gemm_ws.data();
     }
     rc = greta_cuda_gemm(H(stream), fmt, A->data(), a_f16, B->data(), qi.scales, C->data(), c_f16, M, N, K, ws);
@@ -386,6 +435,12 @@ GretaResult GretaCompute::rmsnorm(GretaStream *stream, GretaMemory *input, Greta
   return static_cast<GretaResult>(greta_cuda_rmsnorm(H(stream), static_cast<const float *>(input->data()),
                                                      static_cast<const float *>(weight->data()), static_cast<float *>(output->data()), rows,
                                                      dim, eps));
+}
+
+GretaResult GretaCompute::reserve_gemm_workspace(uint32_t max_M, uint32_t max_K) {
+  const size_t need = greta_cuda_gemm_workspace_bytes(max_M, max_K);
+  if (g_gemm_ws.size() < need && !g_gemm_ws.allocate(need, gcore::rt::cuda::BufferUsage::DeviceOnly)) return GretaResult::ERROR_OUT_OF_MEM;
+  return GretaResult::SUCCESS;
 }
 
 void GretaCompute::set_op_label(const char *label) { g_label = label ? label : ""; }

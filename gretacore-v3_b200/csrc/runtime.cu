@@ -300,6 +300,13 @@ int greta_cuda_graph_launch(void *exec, greta_stream_t stream) {
   }
   return GRETA_OK;
 }
+int greta_cuda_stream_is_capturing(greta_stream_t stream, int *capturing) {
+  GRETA_REQUIRE(capturing, "stream_is_capturing: null out pointer");
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  GRETA_CUDA_TRY(cudaStreamIsCapturing(S(stream), &st));
+  *capturing = st != cudaStreamCaptureStatusNone;
+  return GRETA_OK;
+}
 int greta_cuda_graph_destroy(void *graph) {
   if (graph) GRETA_CUDA_TRY(cudaGraphDestroy(reinterpret_cast<cudaGraph_t>(graph)));
   return GRETA_OK;

@@ -18,6 +18,7 @@
 #include <cstdint>
 #include <functional>
 #include <memory>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -25,6 +26,9 @@
 
 struct CUstream_st;
 typedef CUstream_st *cudaStream_t;  // same declaration as the CUDA runtime's
+
+// The host library is compiled with hidden visibility; the classes and functions declared here are its interface.
+#pragma GCC visibility push(default)
 
 namespace gcore::rt {
 
@@ -136,6 +140,24 @@ private:
   BufferUsage usage_ = BufferUsage::DeviceOnly;
 };
 
+// Bump allocator over large device chunks; the reference's gcore::rt::hip::GretaArena (arena.hpp:8-30,
+// arena.cpp:14-53): allocations are rounded up to 256 bytes, a chunk that cannot take the next one is followed by
+// a new chunk (of the request's size if that is larger), nothing is freed before the arena itself.
+class GretaArena {
+public:
+  explicit GretaArena(size_t chunk_size = 256u * 1024 * 1024);
+  GretaArena(const GretaArena &) = delete;
+  GretaArena &operator=(const GretaArena &) = delete;
+  bool allocate(size_t size, void **out_ptr, std::string *err);
+  size_t total_allocated() const { return total_allocated_; }
+  size_t num_chunks() const { return chunks_.size(); }
+
+private:
+  size_t chunk_size_, current_offset_ = 0, total_allocated_ = 0;
+  std::vector<std::unique_ptr<Buffer>> chunks_;
+  std::mutex mutex_;
+};
+
 class GretaEventCuda : public GretaEvent {
 public:
   GretaEventCuda();
@@ -190,6 +212,8 @@ public:
   GretaMemory *create_memory(size_t size, GretaDataType type = GretaDataType::FP32, bool host_visible = false) override;
   // Scratch for split decode attention behind the reference-signature launchers (allocated by initialize()).
   void *attention_scratch(size_t *bytes) const;
+  // [256 * 128] floats behind it: the rotated copy of Q for launch_flash_attention_decode_fused_rope.
+  float *query_scratch() const;
 
 private:
   bool ready_ = false;
@@ -249,6 +273,14 @@ void launch_flash_attention_decode(cudaStream_t stream, const float *Q, const fl
 void launch_flash_attention_decode_f16kv(cudaStream_t stream, const float *Q, const uint16_t *K, const uint16_t *V, float *O,
                                          uint32_t num_heads, uint32_t num_heads_kv, const uint32_t *d_pos, uint32_t seq_len,
                                          uint32_t max_seq_len, uint32_t head_dim, float scale);
+// fused_attention_kernels.hpp:14-20: Q arrives un-rotated, K in the (fp32) cache is already rotated; Q is rotated at
+// *d_pos into scratch of the context and attends over *d_pos + 1 keys.  One KV head per query head, as in the reference.
+void launch_flash_attention_decode_fused_rope(cudaStream_t stream, const float *Q, const float *K, const float *V, float *O,
+                                              uint32_t num_heads, const uint32_t *d_pos, uint32_t max_seq_len, uint32_t head_dim,
+                                              float scale, float rope_base);
+// attention_kernels.hpp:124-128: Q, O [seq_len][num_heads][head_dim], K, V [seq_len][num_heads_kv][head_dim], all fp32.
+void launch_flash_attention_prefill(cudaStream_t stream, const float *Q, const float *K, const float *V, float *O, uint32_t seq_len,
+                                    uint32_t num_heads, uint32_t num_heads_kv, uint32_t head_dim, float scale, bool causal);
 void launch_flash_attention_prefill_f16kv(cudaStream_t stream, const float *Q, const uint16_t *K_cache, const uint16_t *V_cache, float *O,
                                           uint32_t seq_len, uint32_t pos0, uint32_t num_heads, uint32_t num_heads_kv, uint32_t head_dim,
                                           uint32_t max_seq_len, float scale);
@@ -290,7 +322,10 @@ public:
   static GretaResult rmsnorm(GretaStream *stream, GretaMemory *input, GretaMemory *weight, GretaMemory *output, uint32_t dim, float eps);
   static void set_op_label(const char *label);
   static GemmAuditInfo get_last_gemm_audit();
-  // Device scratch the M > 32 route uses when A is FP32 (grown on demand, one per thread).
+  // The M > 32 route converts FP32 activations to FP16 in device scratch owned by the calling thread.  This sizes it
+  // for A of up to max_M x max_K ahead of time.  gemm() grows it on demand otherwise - an allocation, so not while
+  // its stream is capturing a graph: gemm() then returns ERROR_GRAPH_CAPTURE and asks for this call first.
+  static GretaResult reserve_gemm_workspace(uint32_t max_M, uint32_t max_K);
 };
 
 class GretaFused {
@@ -492,3 +527,5 @@ uint64_t tensor_stream(uint32_t layer, int which);  // stream id of a model tens
 }  // namespace synth
 
 }  // namespace gcore::inference
+
+#pragma GCC visibility pop

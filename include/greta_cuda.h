@@ -98,6 +98,8 @@ GRETA_API int greta_cuda_graph_capture_begin(greta_stream_t stream);
 GRETA_API int greta_cuda_graph_capture_end(greta_stream_t stream, void **graph);
 GRETA_API int greta_cuda_graph_instantiate(void *graph, void **exec);
 GRETA_API int greta_cuda_graph_launch(void *exec, greta_stream_t stream);
+/* *capturing = 1 while `stream` is recording a graph (hipStreamIsCapturing in the reference's runtime). */
+GRETA_API int greta_cuda_stream_is_capturing(greta_stream_t stream, int *capturing);
 GRETA_API int greta_cuda_graph_destroy(void *graph);
 GRETA_API int greta_cuda_graph_exec_destroy(void *exec);
 /* Programmatic dependent launch between consecutive kernels of this library on one stream (the next
@@ -287,6 +289,12 @@ GRETA_API int greta_cuda_attn_prefill(greta_stream_t stream, const float *q, con
                                       const void *v_cache_f16, float *o, uint32_t S, uint32_t pos0,
                                       uint32_t num_heads, uint32_t num_heads_kv, uint32_t head_dim,
                                       uint32_t max_seq_len, float scale);
+/* The reference's own prefill entry, launch_flash_attention_prefill (attention_kernels.hpp:124-128, kernel
+ * attention_kernels.hip:543-618): q, o fp32 [S][H][Dh]; k, v fp32 [S][Hkv][Dh] (the prompt's own keys, not a cache);
+ * causal != 0: query s sees keys 0..s, else all S. */
+GRETA_API int greta_cuda_attn_prefill_f32(greta_stream_t stream, const float *q, const float *k, const float *v, float *o,
+                                          uint32_t S, uint32_t num_heads, uint32_t num_heads_kv, uint32_t head_dim,
+                                          float scale, int causal);
 /* RoPE in place on x [S][H][Dh]; position pos_offset + s, or *d_pos + s when
  * d_pos != NULL.  launch_rope, both overloads (attention_kernels.hip:28-84). */
 GRETA_API int greta_cuda_rope(greta_stream_t stream, float *x, uint32_t S, uint32_t num_heads,

@@ -652,14 +652,18 @@ struct OracleModel {
 };
 
 namespace {
+// Accumulation of the model-level functions: ACC_F64 for parity checks (the default); ACC_FAST_F32 when the
+// model is timed as the CPU baseline (fp32 sums as the kernels' arithmetic has them, vectorisable loops).
+int g_model_acc = ACC_F64;
 void proj(const OracleModel *m, const float *x, const uint8_t *w, float *y, uint32_t S, uint32_t N,
           uint32_t K) {
   if (S <= 32)  // the reference's route threshold (greta_compute_hip.cpp:166-167)
-    oracle_gemv(x, 0, w, m->fmt, y, S, N, K, ACC_F64);
+    oracle_gemv(x, 0, w, m->fmt, y, S, N, K, g_model_acc);
   else
-    oracle_gemm(x, 0, w, m->fmt, y, 0, S, N, K, ACC_F64);
+    oracle_gemm(x, 0, w, m->fmt, y, 0, S, N, K, g_model_acc);
 }
 }  // namespace
+OAPI void oracle_set_model_acc(int acc) { g_model_acc = acc; }
 
 // Runs seq_len tokens starting at position seq_start through all layers and
 // writes the logits of the LAST position to logits[vocab].  x_dump (optional,
@@ -695,7 +699,7 @@ OAPI int oracle_model_forward(const OracleModel *m, const int32_t *tokens, uint3
     for (uint32_t s = 0; s < S; ++s)
       oracle_attention_decode(q.data() + (size_t)s * H * Dh, kc, vc, 1,
                               att.data() + (size_t)s * H * Dh, H, Hkv, Dh, seq_start + s + 1,
-                              m->max_seq, scale, 0);
+                              m->max_seq, scale, g_model_acc == ACC_F64 ? 0 : 1);
     proj(m, att.data(), L.wo, tmp.data(), S, D, H * Dh);
     oracle_add(x.data(), tmp.data(), x.data(), (size_t)S * D);
     oracle_rmsnorm(x.data(), L.ffn_norm, nrm.data(), S, D, m->rms_eps, 0);
@@ -708,6 +712,6 @@ OAPI int oracle_model_forward(const OracleModel *m, const int32_t *tokens, uint3
   const float *xl = x.data() + (size_t)(S - 1) * D;
   if (x_dump) std::memcpy(x_dump, xl, (size_t)D * 4);
   oracle_rmsnorm(xl, m->out_norm, nrm.data(), 1, D, m->rms_eps, 0);
-  oracle_gemm_f16w(nrm.data(), m->out_weight, logits, 1, m->vocab, D, ACC_F64);
+  oracle_gemm_f16w(nrm.data(), m->out_weight, logits, 1, m->vocab, D, g_model_acc);
   return 0;
 }

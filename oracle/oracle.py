@@ -70,6 +70,11 @@ def set_num_threads(n):
     lib().oracle_set_num_threads(int(n))
 
 
+def set_model_acc(acc):
+    """Accumulation used by Model.forward: ACC_F64 (parity, the default) or ACC_FAST_F32 (the timed CPU baseline)."""
+    lib().oracle_set_model_acc(C.c_int(acc))
+
+
 # --------------------------------------------------------------------------- formats
 def f16_bits_to_f32(h):
     h = np.ascontiguousarray(h, dtype=np.uint16)
