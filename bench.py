@@ -117,8 +117,8 @@ class CpuDecodeSample:
         self.tok = np.array([1], np.int32)
         self.cores = O.num_threads()
 
-    def one_step_seconds(self):
-        """Seconds the full model's decode step takes on the CPU port, from one timed step of each small model."""
+    def sample(self):
+        """One timed decode step of the 1-layer and of the 2-layer model -> (seconds, seconds)."""
         O = self.O
         O.set_model_acc(O.ACC_FAST_F32)
         try:
@@ -129,9 +129,13 @@ class CpuDecodeSample:
                 t.append(time.perf_counter() - t0)
         finally:
             O.set_model_acc(O.ACC_F64)
-        layer = max(t[1] - t[0], 1e-9)
-        fixed = max(t[0] - layer, 0.0)
-        return self.batch * (fixed + self.cfg["num_layers"] * layer), layer, fixed
+        return t[0], t[1]
+
+    def step_seconds(self, t1, t2):
+        """Seconds the full model's step takes, from the times of the 1-layer and the 2-layer step."""
+        layer = max(t2 - t1, 1e-9)
+        fixed = max(t1 - layer, 0.0)
+        return self.batch * (fixed + self.cfg["num_layers"] * layer)
 
     def describe(self):
         return (f"one decode step (all operators, context {self.context}) of a 1-layer and a 2-layer model of the workload's shape on the "
@@ -162,13 +166,15 @@ def cpu_q8_0_gemv_4096(reps=20):
 
 def cpu_baseline(pkg, cfg, context, batch=1, budget_s=10.0):
     sample = CpuDecodeSample(pkg, cfg, context, batch)
-    sample.one_step_seconds()                              # warm-up (thread pool, page faults)
-    best, t_end, reps = 1e30, time.perf_counter() + budget_s, 0
-    while reps < 3 or time.perf_counter() < t_end:
-        best = min(best, sample.one_step_seconds()[0])
-        reps += 1
+    sample.sample()                                        # warm-up (thread pool, page faults)
+    t1s, t2s, t_end = [], [], time.perf_counter() + budget_s
+    while len(t1s) < 3 or time.perf_counter() < t_end:
+        a, b = sample.sample()
+        t1s.append(a)
+        t2s.append(b)
+    best = sample.step_seconds(float(np.median(t1s)), float(np.median(t2s)))     # medians: a difference of two minima is noise
     return {"value": batch / best, "unit": "tok/s", "cores": sample.cores, "kind": "port",
-            "sample": sample.describe() + f"; best of {reps} in about {budget_s:.0f} s",
+            "sample": sample.describe() + f"; medians of {len(t1s)} samples in about {budget_s:.0f} s",
             "q8_0_gemv_4096x4096_cpu": cpu_q8_0_gemv_4096()}
 
 
@@ -178,10 +184,10 @@ def run_reference(args, ranks, cfg, pkg, batch, context):
         return
     sample = CpuDecodeSample(pkg, cfg, context, batch)
     for _ in range(max(1, min(args.warmup, 3))):
-        sample.one_step_seconds()
+        sample.sample()
     steps = max(1, min(args.steps, 200))
-    times = [sample.one_step_seconds()[0] for _ in range(steps)]
-    ms = 1e3 * float(np.mean(times))
+    pairs = [sample.sample() for _ in range(max(steps, 5))]
+    ms = 1e3 * sample.step_seconds(float(np.median([p[0] for p in pairs])), float(np.median([p[1] for p in pairs])))
     val = 1e3 * batch / ms
     print(json.dumps({
         "impl": "reference", "metric": metric_name(args), "value": val, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
@@ -191,7 +197,7 @@ def run_reference(args, ranks, cfg, pkg, batch, context):
                        note="the reference has no CPU implementation of this path and its GPU kernels are HIP/gfx942 only: this arm is "
                             "the CPU port of its kernel math"),
         "cpu_baseline": {"value": val, "unit": "tok/s", "cores": sample.cores, "kind": "port",
-                         "sample": sample.describe() + f"; mean of {steps} samples"},
+                         "sample": sample.describe() + f"; medians of {len(pairs)} samples"},
         "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 

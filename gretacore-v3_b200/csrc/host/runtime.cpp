@@ -375,7 +375,10 @@ GretaResult GretaCompute::gemm(GretaStream *stream, GretaMemory *A, GretaMemory 
   const bool a_f16 = A->data_type() == GretaDataType::FP16, c_f16 = C->data_type() == GretaDataType::FP16;
   const GretaQuantInfo qi = B->quant_info();
   if (fmt != GRETA_FMT_F16 && (qi.scales == nullptr || qi.group_size != 32)) return GretaResult::ERROR_INVALID_ARGS;
-  const bool gemv = M <= 32 && !c_f16;  // the reference's GEMM_MFMA_THRESHOLD
+  const bool gguf = fmt == GRETA_FMT_Q4_0 || fmt == GRETA_FMT_Q8_0;
+  // M <= 32 takes the GEMV form (the reference's GEMM_MFMA_THRESHOLD); above it the GGUF formats take the tensor-core
+  // GEMM, the reference's own INT4 / INT8 planes and fp16 weights stay on the GEMV kernels for any M.
+  const bool gemv = (M <= 32 && !c_f16) || !gguf;
   g_audit = GemmAuditInfo{};
   g_audit.op_label = g_label;
   g_audit.route = gemv ? "GEMV" : "TCGEN05";
@@ -389,8 +392,9 @@ GretaResult GretaCompute::gemm(GretaStream *stream, GretaMemory *A, GretaMemory 
   g_audit.scales_ptr = (uintptr_t)qi.scales;
   int rc;
   if (gemv) {
+    if (c_f16) return GretaResult::ERROR_NOT_IMPLEMENTED;  // fp16 output exists on the tensor-core route only
     rc = greta_cuda_gemv(H(stream), fmt, A->data(), a_f16, B->data(), qi.scales, static_cast<float *>(C->data()), M, N, K);
-  } else if (fmt == GRETA_FMT_Q4_0 || fmt == GRETA_FMT_Q8_0) {
+  } else {
     void *ws = nullptr;
     if (!a_f16) {
       const size_t need = greta_cuda_gemm_workspace_bytes(M, K);
@@ -402,9 +406,6 @@ GretaResult GretaCompute::gemm(GretaStream *stream, GretaMemory *A, GretaMemory 
       ws = g_gemm_ws.data();
     }
     rc = greta_cuda_gemm(H(stream), fmt, A->data(), a_f16, B->data(), qi.scales, C->data(), c_f16, M, N, K, ws);
-  } else {
-    if (c_f16) return GretaResult::ERROR_NOT_IMPLEMENTED;
-    rc = greta_cuda_gemv(H(stream), fmt, A->data(), a_f16, B->data(), qi.scales, static_cast<float *>(C->data()), M, N, K);
   }
   return static_cast<GretaResult>(rc);
 }
