@@ -51,6 +51,10 @@ struct AttnParams {
   // the prompt-major arrays [S][Hkv][Dh] of the reference's prefill entry have head_stride = Dh, row_stride = Hkv * Dh.
   // 0 = the cache layout.  len_step: keys query z sees beyond query 0's (1 = causal, 0 = every query sees len0 keys).
   uint32_t head_stride, row_stride, len_step;
+  // Batched decode: query z belongs to sequence z, whose cache starts seq_stride elements after sequence z - 1's and
+  // whose position is d_pos[z * pos_stride].  Both 0 for a single sequence.
+  size_t seq_stride;
+  uint32_t pos_stride;
   uint32_t *counters;    // [H] zero on entry, left zero
   float *partial;        // [H][splits][Dh + 2]
 };
@@ -119,8 +123,8 @@ __device__ __forceinline__ void attn_partial(const AttnParams &p, const uint32_t
   const uint32_t kvh = head / (p.H / p.Hkv);
 
   const size_t hs = p.head_stride ? p.head_stride : (size_t)p.max_seq * Dh, rs = p.row_stride ? p.row_stride : Dh;
-  const KV *kbase = reinterpret_cast<const KV *>(p.kc) + (size_t)kvh * hs + sub * DPL;
-  const KV *vbase = reinterpret_cast<const KV *>(p.vc) + (size_t)kvh * hs + sub * DPL;
+  const KV *kbase = reinterpret_cast<const KV *>(p.kc) + (size_t)qi * p.seq_stride + (size_t)kvh * hs + sub * DPL;
+  const KV *vbase = reinterpret_cast<const KV *>(p.vc) + (size_t)qi * p.seq_stride + (size_t)kvh * hs + sub * DPL;
 
   float qv[DPL];
   {
@@ -191,8 +195,8 @@ __device__ __forceinline__ void attn_partial_staged(const AttnParams &p, const u
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int sub = lane & 7, grp = lane >> 3;
   const uint32_t kvh = head / (p.H / p.Hkv);
-  const uint8_t *kg = reinterpret_cast<const uint8_t *>(p.kc) + (size_t)kvh * p.max_seq * ROW;
-  const uint8_t *vg = reinterpret_cast<const uint8_t *>(p.vc) + (size_t)kvh * p.max_seq * ROW;
+  const uint8_t *kg = reinterpret_cast<const uint8_t *>(p.kc) + ((size_t)qi * p.seq_stride + (size_t)kvh * p.max_seq * Dh) * 2;
+  const uint8_t *vg = reinterpret_cast<const uint8_t *>(p.vc) + ((size_t)qi * p.seq_stride + (size_t)kvh * p.max_seq * Dh) * 2;
   const uint32_t n_tiles = k1 > k0 ? (k1 - k0 + TK - 1) / TK : 0;
   auto issue = [&](uint32_t t) {
     if (t < n_tiles) {
@@ -272,7 +276,7 @@ template <typename KV, int DPL, int NW, bool CG>
 __device__ void attn_body(const AttnParams &p, const uint32_t split, const uint32_t head, const uint32_t qi) {
   constexpr int Dh = DPL * 8;
   __shared__ uint32_t sm_last;
-  const uint32_t L = min((p.d_pos ? __ldcg(p.d_pos) + 1 : p.len0) + qi * p.len_step, p.max_seq);  // never past the cache
+  const uint32_t L = min((p.d_pos ? __ldcg(p.d_pos + qi * p.pos_stride) + 1 : p.len0) + qi * p.len_step, p.max_seq);  // never past the cache
   const uint32_t chunk = (L + p.splits - 1) / p.splits;
   const uint32_t k0 = split * chunk, k1 = min(L, k0 + chunk);
   const int tid = threadIdx.x;
@@ -284,17 +288,18 @@ __device__ void attn_body(const AttnParams &p, const uint32_t split, const uint3
     return;
   }
   // publish the partial result, take a ticket; the last CTA of this head merges all splits
-  float *mine = p.partial + ((size_t)head * p.splits + split) * (Dh + 2);
+  const uint32_t slot = qi * p.H + head;  // one ticket and one set of partials per query and head
+  float *mine = p.partial + ((size_t)slot * p.splits + split) * (Dh + 2);
   if (tid < Dh) mine[2 + tid] = fo;
   if (tid == 0) { mine[0] = fm; mine[1] = fl; }
   __threadfence();
   __syncthreads();
-  if (tid == 0) sm_last = (atomicAdd(&p.counters[head], 1u) == p.splits - 1) ? 1u : 0u;
+  if (tid == 0) sm_last = (atomicAdd(&p.counters[slot], 1u) == p.splits - 1) ? 1u : 0u;
   __syncthreads();
   if (!sm_last) return;
   __threadfence();
   if (tid < Dh) {
-    const float *ph = p.partial + (size_t)head * p.splits * (Dh + 2);
+    const float *ph = p.partial + (size_t)slot * p.splits * (Dh + 2);
     float gm = -INFINITY;
     for (uint32_t s = 0; s < p.splits; ++s) gm = fmaxf(gm, __ldcg(ph + (size_t)s * (Dh + 2)));
     float gl = 0.f, go = 0.f;
@@ -307,7 +312,7 @@ __device__ void attn_body(const AttnParams &p, const uint32_t split, const uint3
     }
     out[tid] = go / gl;
   }
-  if (tid == 0) p.counters[head] = 0;  // ready for the next call on this stream
+  if (tid == 0) p.counters[slot] = 0;  // ready for the next call on this stream
 }
 
 }  // namespace

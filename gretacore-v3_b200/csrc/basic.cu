@@ -143,7 +143,7 @@ __global__ void embedding_kernel(const int32_t *__restrict__ tokens, const void 
   out[i] = v;
 }
 
-// Single CTA, 1024 threads: first maximum (lowest index among equal values).
+// One CTA of 1024 threads per row of logits (per sequence of a batch): first maximum (lowest index among equal values).
 __global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ logits, uint32_t n,
                                                       int32_t *__restrict__ out, uint32_t *d_pos, int32_t *out_tokens,
                                                       uint32_t *d_count, uint32_t out_capacity) {
@@ -151,6 +151,12 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ 
   __shared__ uint32_t si[32];
   pdl_launch_dependents();
   pdl_wait();
+  const uint32_t b = blockIdx.x;  // sequence: its own logits row, result, position, counter and output list
+  logits += (size_t)b * n;
+  out += b;
+  if (d_pos) d_pos += b;
+  if (d_count) d_count += b;
+  if (out_tokens) out_tokens += (size_t)b * out_capacity;
   float best = -INFINITY;
   uint32_t bi = 0xffffffffu;
   for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
@@ -302,6 +308,13 @@ int greta_cuda_argmax_advance(greta_stream_t stream, const float *logits, uint32
   GRETA_REQUIRE(n > 0, "argmax_advance: empty input");
   GRETA_REQUIRE(logits && d_next, "argmax_advance: null pointer");
   GRETA_CUDA_TRY(launch_pdl(argmax_kernel, dim3(1), dim3(1024), 0, S(stream), logits, n, d_next, d_pos, d_out_tokens, d_count, out_capacity));
+  return launched("argmax_kernel");
+}
+int greta_cuda_argmax_advance_batch(greta_stream_t stream, const float *logits, uint32_t n, uint32_t batch, int32_t *d_next, uint32_t *d_pos,
+                                    int32_t *d_out_tokens, uint32_t *d_count, uint32_t out_capacity) {
+  GRETA_REQUIRE(n > 0 && batch >= 1 && batch <= 65535, "argmax_advance_batch: n=%u, batch=%u", n, batch);
+  GRETA_REQUIRE(logits && d_next, "argmax_advance_batch: null pointer");
+  GRETA_CUDA_TRY(launch_pdl(argmax_kernel, dim3(batch), dim3(1024), 0, S(stream), logits, n, d_next, d_pos, d_out_tokens, d_count, out_capacity));
   return launched("argmax_kernel");
 }
 int greta_cuda_silu(greta_stream_t stream, const float *x, float *y, size_t n) {

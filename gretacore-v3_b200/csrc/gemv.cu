@@ -47,6 +47,11 @@
 
 #include "gemv_device.cuh"
 
+namespace greta {
+int gemv_batch_plain(cudaStream_t stream, int fmt, const float *x, const void *qs, const void *d, float *y, uint32_t M, uint32_t N, uint32_t K,
+                     uint32_t force_kw);  // gemv_batch.cu
+}
+
 namespace {
 
 // ------------------------------------------------------------------ simple kernel (any K % 32 == 0)
@@ -527,6 +532,18 @@ int greta_cuda_gemv(greta_stream_t stream, int fmt, const void *x, int x_is_f16,
                     fmt == GRETA_FMT_F16,
                 "gemv: unknown weight format %d", fmt);
   if (int rc = check_plane("gemv", qs, d, fmt)) return rc;
+  // Several rows of fp32 activations against a GGUF-format or fp16 weight: the batched kernel reads the weights
+  // once for up to 32 rows (the per-row kernel below would read them M times).
+  if (M > 1 && !x_is_f16 && tuning().skinny_max_rows > 1 && aligned16(x) && (fmt == GRETA_FMT_F16 || aligned16(d)) &&
+      (fmt == GRETA_FMT_Q4_0 || fmt == GRETA_FMT_Q8_0 || fmt == GRETA_FMT_F16)) {
+    const uint32_t step = (uint32_t)tuning().skinny_max_rows;
+    for (uint32_t m0 = 0; m0 < M; m0 += step) {
+      const uint32_t rows = std::min(step, M - m0);
+      if (int rc = gemv_batch_plain((cudaStream_t)stream, fmt, static_cast<const float *>(x) + (size_t)m0 * K, qs, d, y + (size_t)m0 * N, rows, N, K, 0))
+        return rc;
+    }
+    return GRETA_OK;
+  }
   GemvParams p{};
   p.x = x;
   p.x_is_f16 = x_is_f16;

@@ -152,31 +152,45 @@ bool BlockScheduler::allocate_weights(std::string *err) {
 
 bool BlockScheduler::allocate_activations(size_t batch_size, size_t max_seq_len, std::string *err) {
   if (!initialized_) return fail(err, "allocate_activations: init() first");
-  if (batch_size != 1) return fail(err, "allocate_activations: this path runs one sequence (batch 1), like the reference");
+  // The reference runs one sequence (its cache has no batch dimension, block_scheduler.cpp:1490-1494).  Here up to 32
+  // sequences decode in step, each with its own cache and position; prefill still runs one sequence at a time.
+  if (batch_size < 1 || batch_size > 32) return fail(err, "allocate_activations: batch_size must be 1..32");
   const ModelConfig &c = config_;
   max_seq_ = max_seq_len;
-  const size_t S = max_seq_len, D = c.dim;
+  batch_ = (uint32_t)batch_size;
+  cur_seq_ = 0;
+  const size_t S = std::max(max_seq_len, batch_size), D = c.dim, B = batch_size;
   const size_t ql = (size_t)heads_l_ * c.head_dim, kvl = (size_t)kv_heads_l_ * c.head_dim;
   auto dev = [&](Buffer &b, size_t bytes, GretaDataType t = GretaDataType::FP32) { return b.allocate(bytes, BufferUsage::DeviceOnly, t, err); };
   ActivationBuffers &a = activations_;
   if (!dev(a.x, S * D * 4) || !dev(a.norm_out, S * D * 4) || !dev(a.q, S * ql * 4) || !dev(a.k, S * kvl * 4) || !dev(a.v, S * kvl * 4) ||
       !dev(a.attn_out, S * ql * 4) || !dev(a.mlp_gate, S * hidden_l_ * 4) || !dev(a.mlp_up, S * hidden_l_ * 4) || !dev(a.mlp_out, S * D * 4))
     return false;
-  const size_t cache = (size_t)c.num_layers * kv_heads_l_ * S * c.head_dim * 2;
+  const size_t cache = (size_t)c.num_layers * B * kv_heads_l_ * max_seq_len * c.head_dim * 2;  // [L][B][Hkv][S][Dh] fp16
   if (!dev(a.kv_cache_k, cache, GretaDataType::FP16) || !dev(a.kv_cache_v, cache, GretaDataType::FP16)) return false;
-  if (!dev(a.tokens, S * 4) || !dev(a.d_pos, 16) || !dev(a.d_next, 16) || !dev(a.out_tokens, S * 4)) return false;
-  if (!dev(a.attn_scratch, greta_cuda_attn_decode_scratch_bytes(heads_l_, c.head_dim))) return false;
-  if (!dev(a.gemm_ws, greta_cuda_gemm_workspace_bytes((uint32_t)S, std::max(c.dim, c.hidden_dim)))) return false;
-  if (!dev(logits_, (size_t)c.vocab_size * 4)) return false;
+  // d_pos: B positions, then B counts of ids produced; d_next: B token ids; out_tokens: [B][max_seq]
+  if (!dev(a.tokens, S * 4) || !dev(a.d_pos, std::max<size_t>(16, 2 * B * 4)) || !dev(a.d_next, std::max<size_t>(16, B * 4)) ||
+      !dev(a.out_tokens, B * max_seq_len * 4))
+    return false;
+  if (!dev(a.attn_scratch, greta_cuda_attn_decode_scratch_bytes((uint32_t)B * heads_l_, c.head_dim))) return false;
+  if (!dev(a.gemm_ws, greta_cuda_gemm_workspace_bytes((uint32_t)max_seq_len, std::max(c.dim, c.hidden_dim)))) return false;
+  if (!dev(logits_, B * (size_t)c.vocab_size * 4)) return false;
+  if (B > 1 && c.tp_size > 1 && !dev(logits_local_, B * (size_t)vocab_l_ * 4)) return false;
   greta_cuda_memset(a.attn_scratch.data(), 0, a.attn_scratch.size(), nullptr);
   greta_cuda_memset(a.kv_cache_k.data(), 0, cache, nullptr);
   greta_cuda_memset(a.kv_cache_v.data(), 0, cache, nullptr);
-  greta_cuda_memset(a.d_pos.data(), 0, 16, nullptr);
-  greta_cuda_memset(a.d_next.data(), 0, 16, nullptr);
+  greta_cuda_memset(a.d_pos.data(), 0, a.d_pos.size(), nullptr);
+  greta_cuda_memset(a.d_next.data(), 0, a.d_next.size(), nullptr);
   GRETA_TRY(greta_cuda_device_synchronize(), "allocate_activations");
   delete graph_;
   graph_ = nullptr;
   graph_captured_ = false;
+  return true;
+}
+
+bool BlockScheduler::set_sequence(size_t seq, std::string *err) {
+  if (seq >= batch_) return fail(err, "set_sequence: sequence index beyond the batch");
+  cur_seq_ = (uint32_t)seq;
   return true;
 }
 
@@ -424,6 +438,70 @@ bool BlockScheduler::decode_layers(std::string *err, bool fused_exchange, const 
   return true;
 }
 
+// The decode step of a batch: the same five kernels per layer in their batched forms (weights streamed once for all
+// sequences, every sequence at its own position).  Under tensor parallelism the partial products of the row-parallel
+// projections are summed by the all-reduce hook over [batch x dim].
+bool BlockScheduler::decode_layers_batch(std::string *err) {
+  const ModelConfig &c = config_;
+  ActivationBuffers &a = activations_;
+  cudaStream_t s = H(stream_);
+  const int fmt = fmt_of(c.weight_type);
+  const uint32_t D = c.dim, Dh = c.head_dim, ql = heads_l_ * Dh, B = batch_;
+  const float scale = 1.0f / std::sqrt((float)Dh);
+  const size_t cache_l = (size_t)B * kv_heads_l_ * max_seq_ * Dh;  // elements per layer: [B][Hkv][S][Dh]
+  const uint32_t *dpos = static_cast<const uint32_t *>(a.d_pos.data());
+  float *x = static_cast<float *>(a.x.data()), *q = static_cast<float *>(a.q.data()), *att = static_cast<float *>(a.attn_out.data());
+  float *gate = static_cast<float *>(a.mlp_gate.data());
+  const bool tp = c.tp_size > 1, fold = !tp || c.tp_rank == 0;  // one rank folds the residual in, the others contribute bare partials
+  for (uint32_t l = 0; l < c.num_layers; ++l) {
+    BlockBuffers &b = blocks_[l];
+    uint16_t *kc = static_cast<uint16_t *>(a.kv_cache_k.data()) + l * cache_l;
+    uint16_t *vc = static_cast<uint16_t *>(a.kv_cache_v.data()) + l * cache_l;
+    GRETA_TRY(greta_cuda_fused_rmsnorm_qkv_rope_kv_batch(s, fmt, x, static_cast<const float *>(b.attn_norm.data()), c.rms_eps, b.wq.data(),
+                                                         b.s_wq.data(), b.wk.data(), b.s_wk.data(), b.wv.data(), b.s_wv.data(), q, nullptr, nullptr,
+                                                         kc, vc, dpos, B, heads_l_, kv_heads_l_, Dh, (uint32_t)max_seq_, c.rope_base, D),
+              "fused qkv (batch)");
+    GRETA_TRY(greta_cuda_attn_decode_batch(s, q, kc, vc, att, dpos, B, heads_l_, kv_heads_l_, Dh, (uint32_t)max_seq_, scale, a.attn_scratch.data(),
+                                           a.attn_scratch.size()),
+              "attention decode (batch)");
+    GRETA_TRY(greta_cuda_gemv_batch(s, fmt, att, nullptr, 0.f, b.wo.data(), b.s_wo.data(), fold ? x : nullptr, x, B, D, ql, 0), "wo (batch)");
+    if (tp && all_reduce_(x, (size_t)B * D, s) != 0) return fail(err, "all-reduce after the O-projection failed");
+    GRETA_TRY(greta_cuda_fused_ffn_front_batch(s, fmt, x, static_cast<const float *>(b.ffn_norm.data()), c.rms_eps, b.w1.data(), b.s_w1.data(),
+                                               b.w3.data(), b.s_w3.data(), gate, B, D, hidden_l_),
+              "ffn front (batch)");
+    GRETA_TRY(greta_cuda_gemv_batch(s, fmt, gate, nullptr, 0.f, b.w2.data(), b.s_w2.data(), fold ? x : nullptr, x, B, D, hidden_l_, 0), "w2 (batch)");
+    if (tp && all_reduce_(x, (size_t)B * D, s) != 0) return fail(err, "all-reduce after the down-projection failed");
+  }
+  return true;
+}
+
+// Final norm + LM head for every sequence of the batch -> logits_ [B][vocab] (full vocabulary on every rank).
+bool BlockScheduler::lm_head_batch(std::string *err) {
+  const ModelConfig &c = config_;
+  cudaStream_t s = H(stream_);
+  const int lf = fmt_of(c.lm_head_type);
+  const float *x = static_cast<const float *>(activations_.x.data());
+  const void *d = lf == GRETA_FMT_F16 ? nullptr : s_output_weight_.data();
+  float *logits = static_cast<float *>(logits_.data());
+  if (c.tp_size == 1) {
+    GRETA_TRY(greta_cuda_gemv_batch(s, lf, x, static_cast<const float *>(output_norm_.data()), c.rms_eps, output_weight_.data(), d, nullptr, logits,
+                                    batch_, c.vocab_size, c.dim, 0),
+              "lm head (batch)");
+    return true;
+  }
+  // every rank computes its slice of the vocabulary, places it in a zeroed [B][vocab] buffer; the sum over ranks is the gather
+  if (!all_reduce_) return fail(err, "tensor parallel run without an all-reduce hook");
+  float *local = static_cast<float *>(logits_local_.data());
+  GRETA_TRY(greta_cuda_gemv_batch(s, lf, x, static_cast<const float *>(output_norm_.data()), c.rms_eps, output_weight_.data(), d, nullptr, local,
+                                  batch_, vocab_l_, c.dim, 0),
+            "lm head (batch)");
+  GRETA_TRY(greta_cuda_memcpy_2d_d2d(logits + (size_t)c.tp_rank * vocab_l_, (size_t)c.vocab_size * 4, local, (size_t)vocab_l_ * 4,
+                                     (size_t)vocab_l_ * 4, batch_, s),
+            "logits placement");
+  if (all_reduce_(logits, (size_t)batch_ * c.vocab_size, s) != 0) return fail(err, "all-reduce of the logits failed");
+  return true;
+}
+
 bool BlockScheduler::execute_layer(size_t layer_idx, size_t seq_start, size_t seq_len, const int32_t *, std::string *err) {
   // Prefill form of one layer over S = seq_len rows (the reference's operator order,
   // block_scheduler.cpp:1814-3032), projections through GretaCompute-style routing: GEMV for
@@ -436,9 +514,9 @@ bool BlockScheduler::execute_layer(size_t layer_idx, size_t seq_start, size_t se
   const int fmt = fmt_of(c.weight_type);
   const uint32_t S = (uint32_t)seq_len, D = c.dim, Dh = c.head_dim, ql = heads_l_ * Dh, kvl = kv_heads_l_ * Dh;
   const float scale = 1.0f / std::sqrt((float)Dh);
-  const size_t cache_l = (size_t)kv_heads_l_ * max_seq_ * Dh;
-  uint16_t *kc = static_cast<uint16_t *>(a.kv_cache_k.data()) + layer_idx * cache_l;
-  uint16_t *vc = static_cast<uint16_t *>(a.kv_cache_v.data()) + layer_idx * cache_l;
+  const size_t cache_s = (size_t)kv_heads_l_ * max_seq_ * Dh;  // one sequence's cache of one layer
+  uint16_t *kc = static_cast<uint16_t *>(a.kv_cache_k.data()) + (layer_idx * batch_ + cur_seq_) * cache_s;
+  uint16_t *vc = static_cast<uint16_t *>(a.kv_cache_v.data()) + (layer_idx * batch_ + cur_seq_) * cache_s;
   float *x = static_cast<float *>(a.x.data()), *nrm = static_cast<float *>(a.norm_out.data());
   float *q = static_cast<float *>(a.q.data()), *k = static_cast<float *>(a.k.data()), *v = static_cast<float *>(a.v.data());
   float *att = static_cast<float *>(a.attn_out.data()), *gate = static_cast<float *>(a.mlp_gate.data()), *up = static_cast<float *>(a.mlp_up.data());
@@ -481,12 +559,12 @@ bool BlockScheduler::forward(const int32_t *tokens, size_t seq_start, size_t seq
                                  (uint32_t)seq_len, c.dim, c.vocab_size),
             "embedding");
   if (c.tp_size > 1) GRETA_TRY(greta_cuda_memset(logits_.data(), 0, logits_.size(), s), "logits clear");
-  if (seq_len == 1) {
+  if (seq_len == 1 && batch_ == 1) {
     uint32_t pos = (uint32_t)seq_start;
     GRETA_TRY(greta_cuda_memcpy_h2d(a.d_pos.data(), &pos, 4, s), "position upload");
     GRETA_TRY(greta_cuda_stream_synchronize(s), "position upload");  // `pos` lives on this stack frame
     if (!decode_layers(err)) return false;
-  } else {
+  } else {  // prefill form, on the current sequence's cache (also a single token when the scheduler holds a batch)
     for (size_t l = 0; l < blocks_.size(); ++l)
       if (!execute_layer(l, seq_start, seq_len, tokens, err)) return false;
   }
@@ -547,15 +625,29 @@ bool BlockScheduler::decode_trace(long long *out25) {
 
 // ------------------------------------------------------------------ device-side decode loop
 bool BlockScheduler::begin_decode(int32_t first_token, size_t pos, std::string *err) {
-  if (pos >= max_seq_) return fail(err, "begin_decode: position exceeds max_seq_len");
+  if (batch_ != 1) return fail(err, "begin_decode: this scheduler holds a batch; use begin_decode_batch");
+  const uint32_t p32 = (uint32_t)pos;
+  return begin_decode_batch(&first_token, &p32, err);
+}
+
+bool BlockScheduler::begin_decode_batch(const int32_t *first_tokens, const uint32_t *positions, std::string *err) {
+  if (!first_tokens || !positions) return fail(err, "begin_decode_batch: null argument");
   ActivationBuffers &a = activations_;
   cudaStream_t s = H(stream_);
-  uint32_t init[4] = {(uint32_t)pos, 0u, 0u, 0u};  // d_pos[0] = position, d_pos[1] = tokens produced
-  int32_t tok[4] = {first_token, 0, 0, 0};
-  GRETA_TRY(greta_cuda_memcpy_h2d_sync(a.d_pos.data(), init, 16), "begin_decode");
-  GRETA_TRY(greta_cuda_memcpy_h2d_sync(a.d_next.data(), tok, 16), "begin_decode");
+  const uint32_t B = batch_;
+  std::vector<uint32_t> init(std::max<size_t>(4, 2 * B), 0u);  // B positions, then B counts of ids produced
+  std::vector<int32_t> tok(std::max<size_t>(4, B), 0);
+  size_t pos_max = 0;
+  for (uint32_t b = 0; b < B; ++b) {
+    if (positions[b] >= max_seq_) return fail(err, "begin_decode: position exceeds max_seq_len");
+    init[b] = positions[b];
+    tok[b] = first_tokens[b];
+    pos_max = std::max<size_t>(pos_max, positions[b]);
+  }
+  GRETA_TRY(greta_cuda_memcpy_h2d_sync(a.d_pos.data(), init.data(), init.size() * 4), "begin_decode");
+  GRETA_TRY(greta_cuda_memcpy_h2d_sync(a.d_next.data(), tok.data(), tok.size() * 4), "begin_decode");
   decode_steps_ = 0;
-  decode_pos0_ = pos;
+  decode_pos0_ = pos_max;  // the sequence closest to the end of its cache bounds the number of steps
   if (peer_.tp > 1) {
     GRETA_TRY(greta_cuda_peer_reset(s), "exchange status reset");
     // Exchange tags grow with the position: a session that restarts earlier must not meet the tags of the
@@ -572,7 +664,7 @@ bool BlockScheduler::begin_decode(int32_t first_token, size_t pos, std::string *
     // gives identical results and is kept as an option: measured slower so far (the per-phase
     // activation staging and grid barriers cost more than the launches they replace).
     const char *env = std::getenv("GRETA_PERSISTENT_STEP");
-    persistent_step_ = c.tp_size == 1 && env && env[0] == '1';
+    persistent_step_ = c.tp_size == 1 && batch_ == 1 && env && env[0] == '1';
     if (persistent_step_ && !build_decode_plan(err)) return false;
     greta_decode_desc desc;
     fill_decode_desc(desc, c, a, token_embd_, max_seq_);
@@ -580,7 +672,17 @@ bool BlockScheduler::begin_decode(int32_t first_token, size_t pos, std::string *
     graph_->capture_start(stream_);  // void, as in the reference: a capture that failed shows at instantiate()
     bool ok;
     const float *x_last = static_cast<const float *>(a.x.data());
-    if (persistent_step_) {
+    if (batch_ > 1) {
+      if (peer_.tp > 1) return fail(err, "begin_decode: the fused exchange serves one sequence; a batch uses the all-reduce hook");
+      ok = greta_cuda_embedding(s, static_cast<const int32_t *>(a.d_next.data()), token_embd_.data(), 1, static_cast<float *>(a.x.data()), batch_,
+                                c.dim, c.vocab_size) == GRETA_OK;
+      if (ok && c.tp_size > 1) ok = greta_cuda_memset(logits_.data(), 0, logits_.size(), s) == GRETA_OK;
+      ok = ok && decode_layers_batch(err) && lm_head_batch(err);
+      uint32_t *dp = static_cast<uint32_t *>(a.d_pos.data());
+      ok = ok && greta_cuda_argmax_advance_batch(s, static_cast<const float *>(logits_.data()), c.vocab_size, batch_,
+                                                 static_cast<int32_t *>(a.d_next.data()), dp, static_cast<int32_t *>(a.out_tokens.data()), dp + batch_,
+                                                 (uint32_t)max_seq_) == GRETA_OK;
+    } else if (persistent_step_) {
       ok = greta_cuda_decode_layers(s, &desc, decode_plan_.data()) == GRETA_OK;
       if (!ok && err) *err = gcore::host::cuda_error("decode_layers");
     } else {
@@ -589,9 +691,9 @@ bool BlockScheduler::begin_decode(int32_t first_token, size_t pos, std::string *
       if (ok && c.tp_size > 1) ok = greta_cuda_memset(logits_.data(), 0, logits_.size(), s) == GRETA_OK;
       ok = ok && decode_layers(err, peer_.tp > 1, &x_last);
     }
-    ok = ok && lm_head(x_last, err);
+    if (batch_ == 1) ok = ok && lm_head(x_last, err);
     uint32_t *dp = static_cast<uint32_t *>(a.d_pos.data());
-    ok = ok && greta_cuda_argmax_advance(s, static_cast<const float *>(logits_.data()), c.vocab_size, static_cast<int32_t *>(a.d_next.data()), dp,
+    if (batch_ == 1) ok = ok && greta_cuda_argmax_advance(s, static_cast<const float *>(logits_.data()), c.vocab_size, static_cast<int32_t *>(a.d_next.data()), dp,
                                          static_cast<int32_t *>(a.out_tokens.data()), dp + 1, (uint32_t)max_seq_) == GRETA_OK;
     graph_->capture_end(stream_);
     if (!ok || graph_->instantiate() != gcore::rt::GretaResult::SUCCESS) {
@@ -623,9 +725,9 @@ bool BlockScheduler::decode_step_host(const int32_t *token_in, int32_t *token_ou
   if (!graph_captured_) return fail(err, "decode_step_host: begin_decode() first");
   if (!step_fits(err)) return false;
   cudaStream_t s = H(stream_);
-  GRETA_TRY(greta_cuda_memcpy_h2d(activations_.d_next.data(), token_in, 4, s), "token upload");
+  GRETA_TRY(greta_cuda_memcpy_h2d(activations_.d_next.data(), token_in, (size_t)batch_ * 4, s), "token upload");
   if (graph_->launch(stream_) != gcore::rt::GretaResult::SUCCESS) return fail(err, gcore::host::cuda_error("decode step launch failed"));
-  GRETA_TRY(greta_cuda_memcpy_d2h(token_out, activations_.d_next.data(), 4, s), "token download");
+  GRETA_TRY(greta_cuda_memcpy_d2h(token_out, activations_.d_next.data(), (size_t)batch_ * 4, s), "token download");
   GRETA_TRY(greta_cuda_stream_synchronize(s), "decode_step_host");
   ++decode_steps_;
   return true;
@@ -634,7 +736,9 @@ bool BlockScheduler::decode_step_host(const int32_t *token_in, int32_t *token_ou
 bool BlockScheduler::read_generated(int32_t *out, size_t n, std::string *err) {
   GRETA_TRY(greta_cuda_stream_synchronize(H(stream_)), "read_generated");
   if (n > decode_steps_) return fail(err, "read_generated: fewer steps were run");
-  return activations_.out_tokens.copy_to_host(out, n * 4, err);
+  for (uint32_t b = 0; b < batch_; ++b)  // out is [batch][n]; the device list is [batch][max_seq]
+    if (!activations_.out_tokens.copy_to_host_offset(out + (size_t)b * n, (size_t)b * max_seq_ * 4, n * 4, err)) return false;
+  return true;
 }
 
 // ------------------------------------------------------------------ Generator
@@ -654,6 +758,46 @@ int32_t Generator::sample(const float *logits, size_t vocab_size, const Sampling
       id = (int32_t)i;
     }
   return id;
+}
+
+std::vector<std::vector<int32_t>> Generator::generate_batch(const std::vector<std::vector<int32_t>> &prompts, const SamplingParams &params,
+                                                            std::string *err) {
+  std::vector<std::vector<int32_t>> out;
+  if (!scheduler_ || params.max_tokens <= 0) return out;
+  const size_t B = scheduler_->batch_size();
+  if (prompts.size() != B) {
+    if (err) *err = "generate_batch: one prompt per sequence of the batch";
+    return out;
+  }
+  if (!params.greedy) {
+    if (err) *err = "only greedy decoding is on this path";
+    return out;
+  }
+  const size_t steps = (size_t)params.max_tokens - 1;
+  std::vector<int32_t> first(B);
+  std::vector<uint32_t> pos(B);
+  for (size_t b = 0; b < B; ++b) {  // prefill, one sequence at a time, into that sequence's cache
+    if (prompts[b].empty() || prompts[b].size() + steps > scheduler_->max_seq_len()) {
+      if (err) *err = "generate_batch: empty prompt, or prompt + max_tokens exceeds max_seq_len";
+      return out;
+    }
+    if (!scheduler_->set_sequence(b, err) || !scheduler_->forward(prompts[b].data(), 0, prompts[b].size(), err)) return out;
+    first[b] = scheduler_->sample_greedy_gpu(0, err);
+    pos[b] = (uint32_t)prompts[b].size();
+  }
+  std::vector<int32_t> rest(B * steps);
+  if (steps > 0) {
+    if (!scheduler_->begin_decode_batch(first.data(), pos.data(), err)) return out;
+    for (size_t i = 0; i < steps; ++i)
+      if (!scheduler_->decode_step(err)) return out;
+    if (!scheduler_->read_generated(rest.data(), steps, err)) return out;
+  }
+  out.resize(B);
+  for (size_t b = 0; b < B; ++b) {
+    out[b].push_back(first[b]);
+    out[b].insert(out[b].end(), rest.begin() + b * steps, rest.begin() + (b + 1) * steps);
+  }
+  return out;
 }
 
 std::vector<int32_t> Generator::generate_tokens(const std::vector<int32_t> &prompt, const SamplingParams &params, GenerationStats *stats,

@@ -64,7 +64,9 @@ int greta_host_tensor_shard(const greta_model_config *c, int which, uint32_t *ou
   return 0;
 }
 
-int greta_model_create(const greta_model_config *c, greta_model_t *out) {
+int greta_model_create(const greta_model_config *c, greta_model_t *out) { return greta_model_create_batch(c, 1, out); }
+
+int greta_model_create_batch(const greta_model_config *c, uint32_t batch, greta_model_t *out) {
   if (!c || !out) return done(false, "model_create: null argument");
   auto m = std::make_unique<Model>();
   ModelConfig &k = m->cfg;
@@ -74,7 +76,7 @@ int greta_model_create(const greta_model_config *c, greta_model_t *out) {
   k.weight_type = dtype(c->weight_fmt); k.lm_head_type = dtype(c->lm_head_fmt);
   k.tp_rank = c->tp_rank; k.tp_size = c->tp_size ? c->tp_size : 1;
   std::string err;
-  bool ok = m->sched.init(k, &err) && m->sched.allocate_weights(&err) && m->sched.allocate_activations(1, k.max_seq_len, &err) &&
+  bool ok = m->sched.init(k, &err) && m->sched.allocate_weights(&err) && m->sched.allocate_activations(batch, k.max_seq_len, &err) &&
             m->gen.init(k, &m->sched, &err);
   if (!ok) return done(false, err);
   *out = m.release();
@@ -142,6 +144,30 @@ int greta_model_generate_eos(greta_model_t m, const int32_t *prompt, uint32_t n_
   *n_out = (uint32_t)ids.size();
   return 0;
 }
+int greta_model_set_sequence(greta_model_t m, uint32_t seq) {
+  std::string err;
+  return done(M(m)->sched.set_sequence(seq, &err), err);
+}
+int greta_model_begin_decode_batch(greta_model_t m, const int32_t *first_tokens, const uint32_t *positions) {
+  std::string err;
+  return done(M(m)->sched.begin_decode_batch(first_tokens, positions, &err), err);
+}
+int greta_model_generate_batch(greta_model_t m, const int32_t *prompts, uint32_t n_prompt, uint32_t n_new, int32_t *out) {
+  std::string err;
+  SamplingParams sp;
+  sp.greedy = true;
+  sp.max_tokens = (int32_t)n_new;
+  const size_t B = M(m)->sched.batch_size();
+  std::vector<std::vector<int32_t>> in(B);
+  for (size_t b = 0; b < B; ++b) in[b].assign(prompts + b * n_prompt, prompts + (b + 1) * n_prompt);
+  std::vector<std::vector<int32_t>> ids = M(m)->gen.generate_batch(in, sp, &err);
+  if (ids.size() != B) return done(false, err.empty() ? "batched generation failed" : err);
+  for (size_t b = 0; b < B; ++b) {
+    if (ids[b].size() != n_new) return done(false, err.empty() ? "generation stopped early" : err);
+    std::memcpy(out + b * n_new, ids[b].data(), (size_t)n_new * 4);
+  }
+  return 0;
+}
 int greta_model_begin_decode(greta_model_t m, int32_t first_token, uint32_t pos) {
   std::string err;
   return done(M(m)->sched.begin_decode(first_token, pos, &err), err);
@@ -166,19 +192,23 @@ int greta_model_decode_timed(greta_model_t m, uint32_t steps, float *ms) {
   return 0;
 }
 int greta_model_decode_e2e(greta_model_t m, int32_t first_token, uint32_t pos, uint32_t steps, int32_t *out, float *ms) {
+  return greta_model_decode_e2e_batch(m, &first_token, &pos, steps, out, ms);
+}
+int greta_model_decode_e2e_batch(greta_model_t m, const int32_t *first_tokens, const uint32_t *positions, uint32_t steps, int32_t *out, float *ms) {
   std::string err;
-  if (!M(m)->sched.begin_decode(first_token, pos, &err)) return done(false, err);
+  const size_t B = M(m)->sched.batch_size();
+  if (!M(m)->sched.begin_decode_batch(first_tokens, positions, &err)) return done(false, err);
   gcore::rt::cuda::Buffer pin;
-  if (!pin.allocate(64, gcore::rt::cuda::BufferUsage::HostVisible, GretaDataType::FP32, &err)) return done(false, err);
-  int32_t *tok = static_cast<int32_t *>(pin.data());
-  tok[0] = first_token;
+  if (!pin.allocate(2 * B * 4 + 64, gcore::rt::cuda::BufferUsage::HostVisible, GretaDataType::FP32, &err)) return done(false, err);
+  int32_t *tok = static_cast<int32_t *>(pin.data()), *got = tok + B;
+  std::memcpy(tok, first_tokens, B * 4);
   auto &ctx = gcore::rt::GretaContext::instance();
   std::unique_ptr<gcore::rt::GretaEvent> e0(ctx.create_event()), e1(ctx.create_event());
   e0->record(M(m)->sched.stream());
   for (uint32_t i = 0; i < steps; ++i) {
-    if (!M(m)->sched.decode_step_host(tok, tok + 1, &err)) return done(false, err);
-    out[i] = tok[1];
-    tok[0] = tok[1];
+    if (!M(m)->sched.decode_step_host(tok, got, &err)) return done(false, err);
+    for (size_t b = 0; b < B; ++b) out[b * steps + i] = got[b];  // out is [batch][steps]
+    std::memcpy(tok, got, B * 4);
   }
   e1->record(M(m)->sched.stream());
   *ms = e1->elapsed_time_since(e0.get());

@@ -187,6 +187,10 @@ int greta_cuda_memcpy_d2d(void *dst, const void *src, size_t bytes, greta_stream
   GRETA_CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, S(stream)));
   return GRETA_OK;
 }
+int greta_cuda_memcpy_2d_d2d(void *dst, size_t dst_pitch, const void *src, size_t src_pitch, size_t width, size_t height, greta_stream_t stream) {
+  GRETA_CUDA_TRY(cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width, height, cudaMemcpyDeviceToDevice, S(stream)));
+  return GRETA_OK;
+}
 int greta_cuda_memcpy_h2d_sync(void *dst, const void *src, size_t bytes) {
   GRETA_CUDA_TRY(cudaMemcpy(dst, src, bytes, cudaMemcpyHostToDevice));
   return GRETA_OK;

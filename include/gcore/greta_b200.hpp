@@ -440,6 +440,13 @@ public:
   // previous arg-max, all layers, LM head, arg-max, position bump) is captured once into a CUDA
   // graph; decode_step() replays it.  begin_decode() seeds it with the first token and position.
   bool begin_decode(int32_t first_token, size_t pos, std::string *err);
+  // B200 build: a batch of sequences decoding in step (allocate_activations(batch, ...)).  Prefill fills one sequence's
+  // cache at a time: set_sequence(b), then forward() as usual.  begin_decode_batch takes every sequence's first token
+  // and position; decode_step() then advances all of them; read_generated() returns [batch][n] ids;
+  // decode_step_host() moves `batch` ids each way.
+  bool set_sequence(size_t seq, std::string *err);
+  bool begin_decode_batch(const int32_t *first_tokens, const uint32_t *positions, std::string *err);
+  size_t batch_size() const { return batch_; }
   bool decode_step(std::string *err);                 // asynchronous
   bool read_generated(int32_t *out, size_t n, std::string *err);  // synchronises; ids produced since begin_decode()
   // Host-driven step: token id in from pinned host memory, sampled id out to pinned host memory, synchronised.
@@ -462,6 +469,8 @@ public:
 
 private:
   bool decode_layers(std::string *err, bool fused_exchange = false, const float **x_final = nullptr);
+  bool decode_layers_batch(std::string *err);
+  bool lm_head_batch(std::string *err);
   bool step_fits(std::string *err) const;
   void invalidate_graph();
   bool build_decode_plan(std::string *err);
@@ -476,6 +485,8 @@ private:
   gcore::rt::GretaGraph *graph_ = nullptr;
   bool graph_captured_ = false, initialized_ = false;
   size_t decode_steps_ = 0, decode_pos0_ = 0, max_seq_ = 0;
+  uint32_t batch_ = 1, cur_seq_ = 0;      // sequences held; the one forward() / execute_layer() work on
+  gcore::rt::cuda::Buffer logits_local_;  // tensor-parallel batch: this rank's slice of the logits before placement
   AllReduceFn all_reduce_;
   greta_peer_exchange peer_{};            // tp == 0: not installed
   gcore::rt::cuda::Buffer x_alt_;         // second copy of the residual stream for the fused exchange
@@ -507,6 +518,10 @@ public:
   bool init(const ModelConfig &config, BlockScheduler *scheduler, std::string *err);
   std::vector<int32_t> generate_tokens(const std::vector<int32_t> &prompt_tokens, const SamplingParams &params,
                                        GenerationStats *stats = nullptr, std::string *err = nullptr);
+  // B200 build: greedy generation for every sequence of the scheduler's batch (prompts.size() == batch_size()):
+  // the prompts are prefilled one sequence at a time, then all sequences decode in step on the device.
+  std::vector<std::vector<int32_t>> generate_batch(const std::vector<std::vector<int32_t>> &prompts, const SamplingParams &params,
+                                                   std::string *err = nullptr);
   // First maximum wins, as the reference's host sampler does (generator.cpp:735-744).
   int32_t sample(const float *logits, size_t vocab_size, const SamplingParams &params);
 

@@ -79,6 +79,9 @@ GRETA_API int greta_cuda_free_host(void *ptr);
 GRETA_API int greta_cuda_memcpy_h2d(void *dst, const void *src, size_t bytes, greta_stream_t stream);
 GRETA_API int greta_cuda_memcpy_d2h(void *dst, const void *src, size_t bytes, greta_stream_t stream);
 GRETA_API int greta_cuda_memcpy_d2d(void *dst, const void *src, size_t bytes, greta_stream_t stream);
+/* height rows of width bytes between pitched device arrays, asynchronous on `stream` (hipMemcpy2DAsync in the reference's runtime). */
+GRETA_API int greta_cuda_memcpy_2d_d2d(void *dst, size_t dst_pitch, const void *src, size_t src_pitch, size_t width, size_t height,
+                                       greta_stream_t stream);
 GRETA_API int greta_cuda_memcpy_h2d_sync(void *dst, const void *src, size_t bytes);
 GRETA_API int greta_cuda_memcpy_d2h_sync(void *dst, const void *src, size_t bytes);
 GRETA_API int greta_cuda_memset(void *dst, int value, size_t bytes, greta_stream_t stream);
@@ -190,6 +193,32 @@ GRETA_API int greta_cuda_fused_ffn_front(greta_stream_t stream, int fmt, const f
                                          const void *w1_d, const void *w3_qs, const void *w3_d,
                                          float *y, uint32_t D, uint32_t F);
 
+/* ------------------------------------------------------------------ batched decode (M = 1..32 sequences)
+ * The same operators for a batch of M sequences that decode in step, each with its own position: the weights are
+ * streamed once for all M activation rows (tensor-core block products on exact integer weights, fp32 block sums
+ * and scales; the activations keep fp32 precision as a pair of fp16 values).  The reference has no batch
+ * dimension: its GEMV route launches grid.y = M and re-reads the weights per row
+ * (src/rt/backend/hip/kernels/gemm_kernels.hip:742-760, 910-942), and its scheduler holds one sequence
+ * (src/inference/src/block_scheduler.cpp:1490-1494).  Formats: Q4_0, Q8_0, F16.  x is fp32 [M][K], row-major,
+ * 16-byte aligned; outputs are [M][...] row-major.  k_slices forces the number of K slices (1, 2, 4 or 8; 0 =
+ * chosen from the shape).
+ *
+ * y[M][N] = (resid ? resid[M][N] : 0) + rmsnorm?(x)[M][K] * dequant(W)^T; gamma == NULL: no norm. */
+GRETA_API int greta_cuda_gemv_batch(greta_stream_t stream, int fmt, const float *x, const float *gamma, float eps,
+                                    const void *qs, const void *d, const float *resid, float *y, uint32_t M, uint32_t N,
+                                    uint32_t K, uint32_t k_slices);
+/* greta_cuda_fused_rmsnorm_qkv_rope_kv for M sequences: q_out [M][H*Dh]; row m is rotated at d_pos[m] and its K / V
+ * go to row d_pos[m] of sequence m's cache; caches are fp16 [M][Hkv][max_seq][Dh]. */
+GRETA_API int greta_cuda_fused_rmsnorm_qkv_rope_kv_batch(
+    greta_stream_t stream, int fmt, const float *x, const float *gamma, float eps, const void *wq_qs, const void *wq_d,
+    const void *wk_qs, const void *wk_d, const void *wv_qs, const void *wv_d, float *q_out, float *k_out, float *v_out,
+    void *k_cache_f16, void *v_cache_f16, const uint32_t *d_pos, uint32_t M, uint32_t num_heads, uint32_t num_heads_kv,
+    uint32_t head_dim, uint32_t max_seq_len, float rope_base, uint32_t D);
+/* greta_cuda_fused_ffn_front for M rows: y [M][F]. */
+GRETA_API int greta_cuda_fused_ffn_front_batch(greta_stream_t stream, int fmt, const float *x, const float *gamma, float eps,
+                                               const void *w1_qs, const void *w1_d, const void *w3_qs, const void *w3_d,
+                                               float *y, uint32_t M, uint32_t D, uint32_t F);
+
 /* ------------------------------------------------------------------ whole decode step, one launch
  * All decoder layers of one batch-1 decode step as a single persistent kernel: the five operators
  * above, per layer, as phases of one launch separated by grid-wide barriers, with the weight stream
@@ -264,6 +293,17 @@ GRETA_API int greta_cuda_attn_decode_f32cache(greta_stream_t stream, const float
                                               uint32_t num_heads, uint32_t num_heads_kv,
                                               uint32_t head_dim, uint32_t max_seq_len, float scale,
                                               void *scratch, size_t scratch_bytes);
+/* Decode attention for a batch of M sequences that decode in step: q, o fp32 [M][H*Dh]; fp16 caches
+ * [M][Hkv][max_seq][Dh]; sequence m attends to its keys 0..d_pos[m].  With 2..16 query heads per KV head (grouped-query
+ * attention) one CTA serves all query heads of a KV head from one staged copy of its keys, so the cache is read once per
+ * KV head; otherwise the per-head kernels run with one (sequence, head) per CTA group.  scratch: greta_cuda_attn_decode_
+ * scratch_bytes(M * H, Dh) bytes (tickets zero before the first call), used by the per-head scratch-merge route only.
+ * The reference has no batch dimension (one cache per layer, src/inference/src/block_scheduler.cpp:1490-1494); per
+ * sequence this is launch_flash_attention_decode (attention_kernels.hip:167-380). */
+GRETA_API int greta_cuda_attn_decode_batch(greta_stream_t stream, const float *q, const void *k_cache_f16,
+                                           const void *v_cache_f16, float *o, const uint32_t *d_pos, uint32_t M,
+                                           uint32_t num_heads, uint32_t num_heads_kv, uint32_t head_dim, uint32_t max_seq_len,
+                                           float scale, void *scratch, size_t scratch_bytes);
 /* Decode attention for callers that must not allocate and have no scratch to lend.  No counterpart in
  * the reference: its launchers take no scratch argument because its attention kernel needs none, and
  * the split-sequence kernel here does.  Such callers are, for example, a host application that gives
@@ -336,6 +376,12 @@ GRETA_API int greta_cuda_argmax(greta_stream_t stream, const float *logits, uint
 GRETA_API int greta_cuda_argmax_advance(greta_stream_t stream, const float *logits, uint32_t n,
                                         int32_t *d_next, uint32_t *d_pos, int32_t *d_out_tokens,
                                         uint32_t *d_count, uint32_t out_capacity);
+
+/* The same for `batch` sequences: logits [batch][n]; d_next, d_pos, d_count are arrays of `batch`; sequence b's ids go
+ * to d_out_tokens[b * out_capacity + ...]. */
+GRETA_API int greta_cuda_argmax_advance_batch(greta_stream_t stream, const float *logits, uint32_t n, uint32_t batch,
+                                              int32_t *d_next, uint32_t *d_pos, int32_t *d_out_tokens, uint32_t *d_count,
+                                              uint32_t out_capacity);
 
 /* ------------------------------------------------------------------ tensor-parallel exchange
  * The reference is single-GPU (hipSetDevice(0), greta_runtime_hip.cpp:153); these are new.

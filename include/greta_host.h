@@ -49,6 +49,9 @@ GRETA_API int greta_host_tensor_shard(const greta_model_config *cfg, int which, 
 
 /* BlockScheduler::init + allocate_weights + allocate_activations(1, max_seq_len). */
 GRETA_API int greta_model_create(const greta_model_config *cfg, greta_model_t *out);
+/* The same with allocate_activations(batch, max_seq_len): `batch` sequences (1..32) that decode in step, each with its own
+ * KV cache and position.  New with this build: the reference's scheduler holds one sequence. */
+GRETA_API int greta_model_create_batch(const greta_model_config *cfg, uint32_t batch, greta_model_t *out);
 GRETA_API int greta_model_destroy(greta_model_t m);
 GRETA_API int greta_model_load_synthetic(greta_model_t m, uint64_t seed);                 /* load_synthetic_weights */
 /* set_layer_tensor / set_global_tensor: `which` is a LayerTensor / GlobalTensor value; host points at the GLOBAL tensor. */
@@ -67,8 +70,13 @@ GRETA_API int greta_model_generate(greta_model_t m, const int32_t *prompt, uint3
 GRETA_API int greta_model_generate_eos(greta_model_t m, const int32_t *prompt, uint32_t n_prompt, uint32_t max_new, int32_t eos_id,
                                        int32_t *out, uint32_t *n_out);
 GRETA_API int greta_model_begin_decode(greta_model_t m, int32_t first_token, uint32_t pos); /* begin_decode */
+/* Batch: set_sequence (which sequence's cache forward() fills), begin_decode_batch (first token and position of every
+ * sequence), Generator::generate_batch (prompts [batch][n_prompt] of equal length -> out [batch][n_new]). */
+GRETA_API int greta_model_set_sequence(greta_model_t m, uint32_t seq);
+GRETA_API int greta_model_begin_decode_batch(greta_model_t m, const int32_t *first_tokens, const uint32_t *positions);
+GRETA_API int greta_model_generate_batch(greta_model_t m, const int32_t *prompts, uint32_t n_prompt, uint32_t n_new, int32_t *out);
 GRETA_API int greta_model_decode_step(greta_model_t m);                                   /* decode_step (asynchronous) */
-GRETA_API int greta_model_read_generated(greta_model_t m, int32_t *out, uint32_t n);      /* read_generated (synchronises) */
+GRETA_API int greta_model_read_generated(greta_model_t m, int32_t *out, uint32_t n);      /* read_generated (synchronises); out is [batch][n] */
 /* `steps` decode_step() calls bracketed by events on the model's stream; *ms = device time. */
 GRETA_API int greta_model_decode_timed(greta_model_t m, uint32_t steps, float *ms);
 /* The reference's decode loop shape (src/inference/src/generator.cpp:1128-1156): every step uploads the
@@ -76,6 +84,9 @@ GRETA_API int greta_model_decode_timed(greta_model_t m, uint32_t steps, float *m
  * to the host before the next step.  *ms = device time of the whole loop (events), copies included;
  * out receives the `steps` ids.  Bytes per step: 4 up, 4 down. */
 GRETA_API int greta_model_decode_e2e(greta_model_t m, int32_t first_token, uint32_t pos, uint32_t steps, int32_t *out, float *ms);
+/* The same for a batch: every step uploads `batch` ids and reads `batch` ids back; out is [batch][steps]. */
+GRETA_API int greta_model_decode_e2e_batch(greta_model_t m, const int32_t *first_tokens, const uint32_t *positions, uint32_t steps,
+                                           int32_t *out, float *ms);
 /* greta_cuda_decode_trace of the model's persistent decode step (zeros when that path is off). */
 GRETA_API int greta_model_decode_trace(greta_model_t m, long long *out25);
 GRETA_API uint64_t greta_model_weight_bytes(greta_model_t m);

@@ -161,6 +161,59 @@ def test_generation_stops_at_the_end_of_sequence_id(pkg):
     m.close()
 
 
+@pytest.mark.parametrize("cfg,batch", [(SMALL, 5), (SMALL_MHA, 3), (SMALL, 16)])
+def test_batched_decode_matches_the_oracle_sequence_by_sequence(pkg, cfg, batch):
+    """A batch of sequences decoding in step (weights streamed once per step for all of them): every sequence's greedy ids
+    equal the oracle's for that sequence alone.  Prompts of different lengths, so every sequence sits at its own position."""
+    seed, n_new = 31, 10
+    weights = pkg.model.synth_weights(cfg, seed)
+    ref = O.Model(cfg, weights)
+    lens = [8 + 3 * (b % 5) for b in range(batch)]
+    prompts = [pkg.model.synth_tokens(seed, lens[b], cfg["vocab"], stream=(1 << 40) + b) for b in range(batch)]
+    m = pkg.model.Model(cfg, batch=batch)
+    m.load_synthetic(seed)
+    first = []
+    for b in range(batch):                       # prefill, one sequence at a time
+        m.set_sequence(b)
+        first.append(int(np.argmax(m.forward(prompts[b], 0))))
+    m.begin_decode(first, lens)
+    for _ in range(n_new - 1):
+        m.decode_step()
+    got = m.read_generated(n_new - 1)
+    for b in range(batch):
+        want, gaps = ref.generate(prompts[b], n_new)
+        assert min(gaps) > 1e-6
+        assert [first[b]] + got[b].tolist() == want, b
+    # the host-driven loop (ids up and down every step) gives the same ids
+    ids, _ = m.decode_e2e(first, lens, n_new - 1)
+    assert np.array_equal(ids, got)
+    m.close()
+
+
+def test_batched_70b_shape_ids_equal_the_stored_oracle_ids(pkg):
+    """The tensor-parallel scaling workload's shape (hidden 8192, 64 / 8 heads of 128, FFN 28672, vocab 128256, rope base
+    500000) at 2 layers, 16 sequences with their own 48-token prompts, 8 greedy ids each: equal to the oracle's ids stored
+    in tests/golden/model_ids.npz (tests/golden/make_model_ids.py)."""
+    import os
+    from _support import ROOT
+    from gretacore_v3_b200.model import LLAMA3_70B
+    gold = np.load(os.path.join(ROOT, "tests", "golden", "model_ids.npz"))
+    name = "llama3_70b_l2_seed4_b16"
+    want, gaps, prompts, seed = gold[name + ".ids"], gold[name + ".gaps"], gold[name + ".prompts"], int(gold[name + ".seed"])
+    cfg = dict(LLAMA3_70B, num_layers=2, max_seq=64)
+    assert [cfg[k] for k in ("dim", "num_heads", "num_heads_kv", "num_layers", "vocab", "hidden_dim", "head_dim", "max_seq")] == list(gold[name + ".shape"])
+    B = want.shape[0]
+    for b in range(B):
+        assert np.array_equal(prompts[b], pkg.model.synth_tokens(seed, prompts.shape[1], cfg["vocab"], stream=(1 << 40) + b))
+    m = pkg.model.Model(cfg, batch=B)
+    m.load_synthetic(seed)
+    ids = m.generate_batch(prompts, want.shape[1])
+    m.close()
+    bad = [(b, int(np.argmax(ids[b] != want[b]))) for b in range(B) if not np.array_equal(ids[b], want[b])]
+    print(f"70B shape x 2 layers, batch {B}: smallest top-2 logit gap of the oracle {gaps.min():.3e}; sequences that differ: {bad}")
+    assert not bad
+
+
 def test_persistent_decode_step_gives_the_same_ids(pkg, monkeypatch):
     """GRETA_PERSISTENT_STEP=1: all layers of a decode step in one persistent kernel (grid barriers between the
     phases) - same greedy ids as the oracle and as the operator-by-operator graph."""
