@@ -203,8 +203,9 @@ def run_reference(args, ranks, cfg, pkg, batch, context):
 
 
 # ----------------------------------------------------------------------------- roofline of the dominant kernel
-def time_dominant_kernel(pkg, cfg, tp, reps=4):
-    """Fused RMSNorm -> gate/up GEMV -> SwiGLU over 32 distinct weight sets, captured in one graph, CUDA events."""
+def time_dominant_kernel(pkg, cfg, tp, batch=1, reps=4):
+    """Fused RMSNorm -> gate/up GEMV -> SwiGLU (single-row or batched form) over distinct weight sets far larger than L2,
+    captured in one graph, CUDA events on the launching stream."""
     import ctypes as C
     g = pkg.ffi
     lib = g.cuda()
@@ -216,15 +217,18 @@ def time_dominant_kernel(pkg, cfg, tp, reps=4):
     d_h = (np.abs(rng.normal(0, 0.02, nb)) / 8).astype(np.float16).view(np.uint16)
     sets = [(g.DeviceBuffer.from_numpy(qs_h), g.DeviceBuffer.from_numpy(d_h), g.DeviceBuffer.from_numpy(qs_h),
              g.DeviceBuffer.from_numpy(d_h)) for _ in range(max(4, min(L, int(4e9 // (2 * nb * 18)))))]   # >> L2, at most ~4 GB
-    x = g.DeviceBuffer.from_numpy(rng.normal(0, 1, D).astype(np.float32))
+    x = g.DeviceBuffer.from_numpy(rng.normal(0, 1, batch * D).astype(np.float32))
     gam = g.DeviceBuffer.from_numpy(np.ones(D, np.float32))
-    y = g.DeviceBuffer(F * 4)
+    y = g.DeviceBuffer(batch * F * 4)
     stream = C.c_void_p()
     g.check(lib.greta_cuda_stream_create(C.byref(stream)))
 
     def one_pass():
         for a, b, c, d in sets:
-            g.check(lib.greta_cuda_fused_ffn_front(stream, g.FMT_Q4_0, x.ptr, gam.ptr, 1e-5, a.ptr, b.ptr, c.ptr, d.ptr, y.ptr, D, F))
+            if batch == 1:
+                g.check(lib.greta_cuda_fused_ffn_front(stream, g.FMT_Q4_0, x.ptr, gam.ptr, 1e-5, a.ptr, b.ptr, c.ptr, d.ptr, y.ptr, D, F))
+            else:
+                g.check(lib.greta_cuda_fused_ffn_front_batch(stream, g.FMT_Q4_0, x.ptr, gam.ptr, 1e-5, a.ptr, b.ptr, c.ptr, d.ptr, y.ptr, batch, D, F))
 
     one_pass()
     g.check(lib.greta_cuda_stream_synchronize(stream))
@@ -246,11 +250,13 @@ def time_dominant_kernel(pkg, cfg, tp, reps=4):
     ms = C.c_float()
     lib.greta_cuda_event_elapsed_ms(e0, e1, C.byref(ms))
     us = ms.value * 1e3 / (reps * len(sets))
-    alg_bytes = 2 * nb * 18 + 2 * D * 4 + F * 4          # both weight matrices + x + gamma in, y out
+    alg_bytes = 2 * nb * 18 + (batch + 1) * D * 4 + batch * F * 4          # both weight matrices + x + gamma in, y out
     for s in sets:
         for b in s:
             b.free()
-    return us, alg_bytes
+    name = ("gemv_pipe_kernel<Q4_0, SwiGLU> (fused RMSNorm -> gate/up GEMV -> SwiGLU)" if batch == 1 else
+            f"gemv_batch_kernel<Q4_0, SwiGLU> (fused RMSNorm -> gate/up matmul for {batch} rows -> SwiGLU, weights read once)")
+    return us, alg_bytes, name
 
 
 # ----------------------------------------------------------------------------- GEMV bandwidth per projection shape
@@ -318,6 +324,112 @@ def gemv_shapes(pkg):
             d.free()
         x.free()
         y.free()
+
+
+def gemv_batch_shapes(pkg, M=16):
+    """Times the batched operators (M activation rows, weights streamed once) on the projection shapes of the 70B and 7B
+    models and the grouped-query batched attention at 16 x 4096 keys: distinct weight / cache copies rotate so nothing is
+    served from L2, launches are captured in one CUDA graph, CUDA events.  One JSON line per shape."""
+    import ctypes as C
+    g = pkg.ffi
+    lib = g.cuda()
+    peak, peak_src = measured_peak_gbs()
+    stream = C.c_void_p()
+    g.check(lib.greta_cuda_stream_create(C.byref(stream)))
+    e0, e1 = C.c_void_p(), C.c_void_p()
+    lib.greta_cuda_event_create(C.byref(e0))
+    lib.greta_cuda_event_create(C.byref(e1))
+    rng = np.random.default_rng(0)
+
+    def timed(one_pass, per_pass):
+        one_pass()
+        g.check(lib.greta_cuda_stream_synchronize(stream))
+        graph, ex = C.c_void_p(), C.c_void_p()
+        g.check(lib.greta_cuda_graph_capture_begin(stream))
+        for _ in range(3):
+            one_pass()
+        g.check(lib.greta_cuda_graph_capture_end(stream, C.byref(graph)))
+        g.check(lib.greta_cuda_graph_instantiate(graph, C.byref(ex)))
+        lib.greta_cuda_graph_launch(ex, stream)
+        lib.greta_cuda_stream_synchronize(stream)
+        best = 1e30
+        for _ in range(3):
+            lib.greta_cuda_event_record(e0, stream)
+            lib.greta_cuda_graph_launch(ex, stream)
+            lib.greta_cuda_event_record(e1, stream)
+            lib.greta_cuda_event_synchronize(e1)
+            ms = C.c_float()
+            lib.greta_cuda_event_elapsed_ms(e0, e1, C.byref(ms))
+            best = min(best, ms.value)
+        lib.greta_cuda_graph_exec_destroy(ex)
+        lib.greta_cuda_graph_destroy(graph)
+        return best * 1e3 / (3 * per_pass)
+
+    shapes = [("plain", 8192, 8192), ("plain", 8192, 28672), ("swiglu", 28672, 8192), ("qkv", 10240, 8192), ("plain", 4096, 4096),
+              ("swiglu", 11008, 4096), ("plain", 4096, 11008), ("plain", 1024, 8192), ("swiglu", 3584, 8192), ("plain", 8192, 3584)]
+    for kind, N, K in shapes:
+        rows = 2 * N if kind == "swiglu" else N
+        nb = rows * (K // 32)
+        wbytes = nb * 18
+        copies = max(2, int(700e6 // wbytes))
+        qs_h = rng.integers(0, 256, nb * 16, dtype=np.uint8)
+        d_h = (np.abs(rng.normal(0, 0.02, nb)) / 8).astype(np.float16).view(np.uint16)
+        planes = [(g.DeviceBuffer.from_numpy(qs_h), g.DeviceBuffer.from_numpy(d_h)) for _ in range(copies)]
+        x = g.DeviceBuffer.from_numpy(rng.normal(0, 1, M * K).astype(np.float32))
+        gam = g.DeviceBuffer.from_numpy(np.ones(K, np.float32))
+        y = g.DeviceBuffer(M * rows * 4)
+        dpos = g.DeviceBuffer.from_numpy(np.full(M, 7, np.uint32))
+        kc = g.DeviceBuffer(M * 8 * 16 * 128 * 2, zero=True)
+
+        def one_pass():
+            for qs, d in planes:
+                if kind == "plain":
+                    g.check(lib.greta_cuda_gemv_batch(stream, g.FMT_Q4_0, x.ptr, None, 0.0, qs.ptr, d.ptr, None, y.ptr, M, N, K, 0))
+                elif kind == "swiglu":
+                    half = N * (K // 32)
+                    g.check(lib.greta_cuda_fused_ffn_front_batch(stream, g.FMT_Q4_0, x.ptr, gam.ptr, 1e-5, qs.ptr, d.ptr, qs.ptr + half * 16,
+                                                                 d.ptr + half * 2, y.ptr, M, K, N))
+                else:                                      # 64 query heads + 8 + 8 KV heads of 128
+                    oq, ok = 8192 * (K // 32), 9216 * (K // 32)
+                    g.check(lib.greta_cuda_fused_rmsnorm_qkv_rope_kv_batch(stream, g.FMT_Q4_0, x.ptr, gam.ptr, 1e-5, qs.ptr, d.ptr, qs.ptr + oq * 16,
+                                                                           d.ptr + oq * 2, qs.ptr + ok * 16, d.ptr + ok * 2, y.ptr, None, None, kc.ptr,
+                                                                           kc.ptr, dpos.ptr, M, 64, 8, 128, 16, 500000.0, K))
+
+        us = timed(one_pass, copies)
+        alg = wbytes + M * K * 4 + M * (N if kind != "qkv" else rows) * 4
+        print(json.dumps({"case": "gemv_batch_shapes", "op": kind, "rows_of_x": M, "N": N, "K": K, "us_per_launch": round(us, 2),
+                          "algorithmic_bytes": alg, "gb_per_s": round(alg / us / 1e3, 1), "frac_of_peak": round(alg / us / 1e3 / peak, 3),
+                          "peak_source": f"of {peak_src}"}), flush=True)
+        for qs, d in planes:
+            qs.free()
+            d.free()
+        for b in (x, gam, y, dpos, kc):
+            b.free()
+    # grouped-query batched attention: 16 sequences x 4096 keys, 64 / 8 heads of 128 (and one rank's share under 8-way sharding)
+    for H, Hkv in ((64, 8), (8, 1)):
+        S, L, Dh = 4160, 4096, 128
+        n = M * Hkv * S * Dh
+        kv = rng.normal(0, 1, n).astype(np.float16).view(np.uint16)
+        copies = max(2, int(600e6 // (2 * n * 2)))
+        caches = [(g.DeviceBuffer.from_numpy(kv), g.DeviceBuffer.from_numpy(kv)) for _ in range(copies)]
+        q = g.DeviceBuffer.from_numpy(rng.normal(0, 1, M * H * Dh).astype(np.float32))
+        o = g.DeviceBuffer(M * H * Dh * 4)
+        dpos = g.DeviceBuffer.from_numpy(np.full(M, L - 1, np.uint32))
+        nbytes = lib.greta_cuda_attn_decode_scratch_bytes(M * H, Dh)
+        scratch = g.DeviceBuffer(nbytes, zero=True)
+
+        def attn_pass():
+            for k, v in caches:
+                g.check(lib.greta_cuda_attn_decode_batch(stream, q.ptr, k.ptr, v.ptr, o.ptr, dpos.ptr, M, H, Hkv, Dh, S, 0.0884, scratch.ptr, nbytes))
+
+        us = timed(attn_pass, copies)
+        alg = 2 * M * Hkv * L * Dh * 2 + 2 * M * H * Dh * 4
+        print(json.dumps({"case": "gemv_batch_shapes", "op": "attn_decode_batch", "sequences": M, "heads": H, "kv_heads": Hkv, "keys": L,
+                          "us_per_launch": round(us, 2), "algorithmic_bytes": alg, "gb_per_s": round(alg / us / 1e3, 1),
+                          "frac_of_peak": round(alg / us / 1e3 / peak, 3), "peak_source": f"of {peak_src}"}), flush=True)
+        for k, v in caches:
+            k.free()
+            v.free()
 
 
 # ----------------------------------------------------------------------------- small single-kernel cases (for ncu)
@@ -394,11 +506,13 @@ def main():
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
+    ap.add_argument("--prompt-len", type=int, default=0, help="prompt tokens per sequence (default 512)")
+    ap.add_argument("--batch", type=int, default=0, help="sequences decoding in step (default: 1, or 16 for --workload c5)")
     ap.add_argument("--prefill-chunk", type=int, default=0, help="tokens per prefill call (0 = the whole prompt at once)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", choices=["c4", "c5-batch1"], default="c4",
-                    help="c4: the 7B shape at batch 1 (the metric's workload); c5-batch1: the 70B shape at batch 1")
+    ap.add_argument("--workload", choices=["c4", "c5", "c5-batch1"], default="c4",
+                    help="c4: the 7B shape at batch 1 (the metric's workload); c5: the 70B shape at batch 16 (the tensor-parallel scaling "
+                         "workload; --prompt-len 4096 --steps 256 for its full size); c5-batch1: the 70B shape at batch 1")
     ap.add_argument("--exchange", choices=["fused", "nccl"], default="fused",
                     help="tensor-parallel exchange of the decode step: fused into the GEMV kernels over peer memory, or NCCL all-reduce")
     ap.add_argument("--case", default=None, help="run a small single-kernel case (gemv_swiglu, gemv_plain, gemm_c2, attn_decode, decode_step) and exit; "
@@ -413,13 +527,26 @@ def main():
         pkg.ffi.require_device()
         gemv_shapes(pkg)
         return
+    if args.case == "gemv_batch_shapes":
+        pkg.ffi.require_device()
+        gemv_batch_shapes(pkg, args.batch or 16)
+        return
     if args.case:
         run_case(pkg, args.case)
         return
     from gretacore_v3_b200.model import LLAMA2_7B, LLAMA3_70B
     cfg = dict(LLAMA2_7B if args.workload == "c4" else LLAMA3_70B)
+    B = args.batch if args.batch else (16 if args.workload == "c5" else 1)
+    if args.prompt_len == 0:
+        args.prompt_len = PROMPT_LEN
+    n_warm = max(args.warmup, 3)
+    if args.workload != "c4":                                 # the cache is sized for this run (the 70B shape's full context would be 43 GB at batch 16)
+        cfg["max_seq"] = (args.prompt_len + n_warm + args.steps + 8 + 63) // 64 * 64
+    if args.prompt_len + n_warm + args.steps > cfg["max_seq"]:
+        raise SystemExit(f"prompt {args.prompt_len} + warm-up {n_warm} + steps {args.steps} exceed the cache of {cfg['max_seq']} positions")
+    context = args.prompt_len + n_warm + args.steps // 2
     if args.impl == "reference":
-        run_reference(args, ranks, cfg, pkg, 1, args.prompt_len + max(args.warmup, 3) + args.steps // 2)
+        run_reference(args, ranks, cfg, pkg, B, context)
         return
 
     import ctypes as C
@@ -428,7 +555,7 @@ def main():
     lib = g.cuda()
     g.check(lib.greta_cuda_set_device(ranks.local))
     tp = ranks.world
-    model = pkg.model.Model(cfg, tp_rank=ranks.rank, tp_size=tp)
+    model = pkg.model.Model(cfg, tp_rank=ranks.rank, tp_size=tp, batch=B)
     if tp > 1:
         uid = (C.c_char * 128)()
         if ranks.rank == 0:
@@ -438,21 +565,29 @@ def main():
         idbuf = C.create_string_buffer(raw, 128)
         g.check(lib.greta_cuda_comm_init(C.byref(comm), idbuf, tp, ranks.rank), "comm_init")
         model.set_comm(comm)
-        if args.exchange == "fused":
+        if B > 1:
+            args.exchange = "nccl (a batch uses the all-reduce)"
+        elif args.exchange == "fused":
             peer_keep = pkg.rendezvous.install_peer_exchange(model, ranks, cfg["dim"])
             if peer_keep is None:
                 args.exchange = "nccl (peer memory could not be mapped)"
-    model.load_synthetic(SEED)
-    prompt = pkg.model.synth_tokens(SEED, args.prompt_len, cfg["vocab"])
-    chunk = args.prefill_chunk or args.prompt_len           # prefill (not timed): one tensor-core pass by default
-    for c0 in range(0, args.prompt_len, chunk):
-        logits = model.forward(prompt[c0:c0 + chunk], c0)
-    first = int(np.argmax(logits))
+    model.load_synthetic(SEED if args.workload == "c4" else 4)
+    seed = SEED if args.workload == "c4" else 4
+    prompts = [pkg.model.synth_tokens(seed, args.prompt_len, cfg["vocab"], stream=(1 << 40) + b) for b in range(B)]
+    chunk = args.prefill_chunk or args.prompt_len           # prefill (not timed): one tensor-core pass per sequence by default
+    first = []
+    for b in range(B):
+        if B > 1:
+            model.set_sequence(b)
+        for c0 in range(0, args.prompt_len, chunk):
+            logits = model.forward(prompts[b][c0:c0 + chunk], c0)
+        first.append(int(np.argmax(logits)))
     pos = args.prompt_len
+    first_arg = first[0] if B == 1 else first
 
     # ---- value: device-resident decode loop, CUDA events, max over ranks
-    model.begin_decode(first, pos)
-    model.decode_timed(max(args.warmup, 3))
+    model.begin_decode(first_arg, pos)
+    model.decode_timed(n_warm)
     sampler = ClockSampler(ranks.local)
     if ranks.rank == 0:
         sampler.start()
@@ -463,46 +598,47 @@ def main():
     t0 = time.time()
     ms = model.decode_timed(args.steps)
     g.check(lib.greta_cuda_device_synchronize())
-    t1 = time.time()
     launches = lib.greta_cuda_launch_count() - launches0
     ms = ranks.gather_max(float(ms))
-    ids_dev = model.read_generated(max(args.warmup, 3) + args.steps)
+    ids_dev = np.asarray(model.read_generated(n_warm + args.steps)).reshape(B, -1)
 
-    # ---- e2e: host-driven loop (token id up, sampled id down, every step), restarted from the same state
+    # ---- e2e: host-driven loop (token ids up, sampled ids down, every step), restarted from the same state
     ranks.barrier()
-    ids_e2e, ms_e2e = model.decode_e2e(first, pos, max(args.warmup, 3))      # warm-up of this loop
-    ids_e2e, ms_e2e = model.decode_e2e(first, pos, args.steps)
+    model.decode_e2e(first_arg, pos, n_warm)                                 # warm-up of this loop
+    ids_e2e, ms_e2e = model.decode_e2e(first_arg, pos, args.steps)
+    ids_e2e = np.asarray(ids_e2e).reshape(B, -1)
     ms_e2e = ranks.gather_max(float(ms_e2e))
     clocks = sampler.stop(t0, time.time()) if ranks.rank == 0 else None      # sampled over both timed loops
-    same = ids_e2e == ids_dev[:args.steps]
-    oracle_check = check_against_stored_oracle_ids(args, cfg, prompt, [first] + ids_dev, [first] + ids_e2e)
+    same = bool(np.array_equal(ids_e2e, ids_dev[:, :args.steps]))
+    oracle_check = check_against_stored_oracle_ids(args, cfg, prompts[0], [first[0]] + ids_dev[0].tolist(), [first[0]] + ids_e2e[0].tolist())
 
     if ranks.rank != 0:
         return
     # ---- roofline of the dominant kernel and the CPU baseline (rank 0)
     model.close()
-    us, alg = time_dominant_kernel(pkg, cfg, tp)
+    us, alg, kernel_name = time_dominant_kernel(pkg, cfg, tp, B)
     peak, peak_src = measured_peak_gbs()
     achieved = alg / us / 1e3
-    roofline = {"bound": "hbm", "kernel": "gemv_pipe_kernel<Q4_0, SwiGLU> (fused RMSNorm -> gate/up GEMV -> SwiGLU)",
+    roofline = {"bound": "hbm", "kernel": kernel_name,
                 "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": f"of {peak_src}",
                 "us_per_launch": us, "algorithmic_bytes_per_launch": alg,
-                # dram__bytes_read + write of one launch from the ncu capture of the 7B-sized kernel (50.83 MB for 50.80 MB
-                # algorithmic; the summary is under profiles/); a tensor-parallel shard moves proportionally less
+                # dram__bytes_read + write per launch, from the ncu capture of the 7B-sized single-row kernel (50.83 MB for
+                # 50.80 MB algorithmic; summary under profiles/), scaled by the bytes this launch moves
                 "traffic": int(alg * 50830848 / 50801664)}
-    tok_s = 1e3 * args.steps / ms
+    tok_s = 1e3 * B * args.steps / ms
     # whole-step view of the same bound: bytes one decode step must read
-    step_bytes = model_step_bytes(cfg, pos + args.steps // 2)
+    step_bytes = model_step_bytes(cfg, pos + n_warm + args.steps // 2, B)
     out = {
         "metric": metric_name(args),
         "value": tok_s, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "q4_0 weights (int8 dot products on 23-bit fixed-point activations), fp32 accumulation, fp16 KV cache",
+        "dtype": ("q4_0 weights (int8 dot products on 23-bit fixed-point activations), fp32 accumulation, fp16 KV cache" if B == 1 else
+                  "q4_0 weights (exact integer weights x activations as fp16 pairs on the tensor cores), fp32 accumulation, fp16 KV cache"),
         "data": "synthetic",
-        "config": workload_config(args, cfg, tp, f"tp{tp}, exchange {args.exchange}" if tp > 1 else "single GPU"),
+        "config": workload_config(args, cfg, tp, f"tp{tp}, exchange {args.exchange}" if tp > 1 else "single GPU", B),
         "clocks": clocks, "gpu_launches": int(launches),
-        "e2e": {"value": 1e3 * args.steps / ms_e2e, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 4,
-                "ids_match_device_loop": bool(same)},
+        "e2e": {"value": 1e3 * B * args.steps / ms_e2e, "unit": "tok/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B,
+                "ids_match_device_loop": same},
         "ids_match_oracle": oracle_check["match"], "ids_checked": oracle_check,
         "roofline": roofline,
         "step_hbm": {"bytes_per_step": step_bytes, "achieved_gbs": step_bytes / (ms / args.steps) / 1e6,
@@ -510,22 +646,25 @@ def main():
                      "note": "aggregate over the N GPUs; the fraction is of N x the measured per-GPU peak"},
     }
     if not args.no_cpu_baseline and tp == 1:                 # reported at N=1 only
-        out["cpu_baseline"] = cpu_baseline(pkg, cfg, pos + max(args.warmup, 3) + args.steps // 2)
+        out["cpu_baseline"] = cpu_baseline(pkg, cfg, context, B)
     print(json.dumps(out))
 
 
 def metric_name(args):
-    return METRIC if args.workload == "c4" else "decode_tokens_per_s_llama3_70b_shape_q4_0_batch1"
+    if args.workload == "c4":
+        return METRIC if (args.batch or 1) == 1 else f"decode_tokens_per_s_llama2_7b_shape_q4_0_batch{args.batch}"
+    return f"decode_tokens_per_s_llama3_70b_shape_q4_0_batch{args.batch or (16 if args.workload == 'c5' else 1)}"
 
 
-def workload_config(args, cfg, tp, parallelism):
+def workload_config(args, cfg, tp, parallelism, batch=1):
     shape = (f"{cfg['num_layers']} layers, hidden {cfg['dim']}, {cfg['num_heads']}/{cfg['num_heads_kv']} heads x {cfg['head_dim']}, "
              f"FFN {cfg['hidden_dim']}, vocab {cfg['vocab']}")
     name = "Llama-2-7B-shaped" if args.workload == "c4" else "Llama-3-70B-shaped"
     return {"workload": f"{name} model ({shape}), random-init Q4_0 weights, fp16 LM head, {args.prompt_len}-token random prompt then greedy "
-                        f"decode at batch 1",
+                        f"decode at batch {batch}" + (" (every sequence its own prompt, cache and position)" if batch > 1 else ""),
             "prompt_len": args.prompt_len, "parallelism": parallelism,
-            "l2_defeat": f"every step streams {model_step_bytes(cfg, args.prompt_len) / 1e9:.1f} GB of distinct weights (L2 is 126 MB)",
+            "batch": batch,
+            "l2_defeat": f"every step streams {model_step_bytes(cfg, args.prompt_len, batch) / 1e9:.1f} GB of distinct weights and cache (L2 is 126 MB)",
             "seed": SEED}
 
 
@@ -547,11 +686,12 @@ def check_against_stored_oracle_ids(args, cfg, prompt, ids_device_loop, ids_host
             "oracle_min_top2_gap": float(gold[name + ".gaps"][0].min())}
 
 
-def model_step_bytes(cfg, pos):
+def model_step_bytes(cfg, pos, batch=1):
+    """Bytes one decode step must read: the weights once, and every sequence's keys and values."""
     D, F, L, V = cfg["dim"], cfg["hidden_dim"], cfg["num_layers"], cfg["vocab"]
     kv = cfg["num_heads_kv"] * cfg["head_dim"]
     w = L * ((2 * D * D + 2 * D * kv + 3 * D * F) * 18 // 32)
-    return w + V * D * 2 + L * 2 * kv * 2 * (pos + 1)
+    return w + V * D * 2 + batch * L * 2 * kv * 2 * (pos + 1)
 
 
 if __name__ == "__main__":
