@@ -482,6 +482,25 @@ def run_case(pkg, name):
         for i in range(12):
             k, v = caches[i % 6]
             g.check(lib.greta_cuda_attn_decode(None, q.ptr, k.ptr, v.ptr, o.ptr, None, L, H, H, Dh, S, 0.0884, scratch.ptr, nbytes))
+    elif name == "gemv_batch":       # batched plain matmul, 16 rows x (8192 x 8192 Q4_0): 37.7 MB per launch, 5 distinct copies (189 MB)
+        M, N, K = 16, 8192, 8192
+        w = planes(N, K, 5)
+        x = g.DeviceBuffer.from_numpy(rng.normal(0, 1, M * K).astype(np.float32))
+        y = g.DeviceBuffer(M * N * 4)
+        for i in range(10):
+            g.check(lib.greta_cuda_gemv_batch(None, g.FMT_Q4_0, x.ptr, None, 0.0, w[i % 5][0].ptr, w[i % 5][1].ptr, None, y.ptr, M, N, K, 0))
+    elif name == "attn_batch":       # grouped-query batched attention: 16 sequences x 2048 keys, 64 / 8 heads of 128 (134 MB per launch), 2 caches
+        M, H, Hkv, Dh, L, S = 16, 64, 8, 128, 2048, 2112
+        kv = rng.normal(0, 1, M * Hkv * S * Dh).astype(np.float16).view(np.uint16)
+        caches = [(g.DeviceBuffer.from_numpy(kv), g.DeviceBuffer.from_numpy(kv)) for _ in range(2)]
+        q = g.DeviceBuffer.from_numpy(rng.normal(0, 1, M * H * Dh).astype(np.float32))
+        o = g.DeviceBuffer(M * H * Dh * 4)
+        dpos = g.DeviceBuffer.from_numpy(np.full(M, L - 1, np.uint32))
+        nbytes = lib.greta_cuda_attn_decode_scratch_bytes(M * H, Dh)
+        scratch = g.DeviceBuffer(nbytes, zero=True)
+        for i in range(6):
+            k, v = caches[i % 2]
+            g.check(lib.greta_cuda_attn_decode_batch(None, q.ptr, k.ptr, v.ptr, o.ptr, dpos.ptr, M, H, Hkv, Dh, S, 0.0884, scratch.ptr, nbytes))
     elif name == "decode_step":      # persistent decode-step kernel on a 4-layer model of the 7B shape (0.46 GB of weights)
         from gretacore_v3_b200.model import LLAMA2_7B
         cfg = dict(LLAMA2_7B)

@@ -481,12 +481,17 @@ int fill_exchange(GemvParams &p, const greta_peer_exchange *ex, uint32_t exch_id
   GRETA_REQUIRE(ex->tp >= 1 && ex->tp <= (uint32_t)MAX_TP && ex->rank < ex->tp, "tensor-parallel exchange: rank %u of %u", ex->rank, ex->tp);
   GRETA_REQUIRE(exch_idx < 256, "tensor-parallel exchange: index %u out of range (256 per step)", exch_idx);
   GRETA_REQUIRE(dim % 32 == 0 && dim <= 8192, "tensor-parallel exchange: dim=%u must be a multiple of 32, at most 8192", dim);
-  const size_t parity_words = (size_t)ex->tp * dim;  // {value, tag} words per parity
+  const size_t parity_words = (size_t)(ex->tp + 1) * dim;  // {value, tag} words per parity: tp partial vectors, then the sum vector
   for (uint32_t j = 0; j < ex->tp; ++j) {
     GRETA_REQUIRE(ex->slots[j] && aligned16(ex->slots[j]), "tensor-parallel exchange: slot buffer %u is null or misaligned", j);
     p.peer_out[j] = as_producer ? static_cast<uint2 *>(ex->slots[j]) + (exch_idx & 1) * parity_words : nullptr;
   }
   p.peer_in = as_producer ? nullptr : static_cast<const uint2 *>(ex->slots[ex->rank]) + (exch_idx & 1) * parity_words;
+  if (!as_producer) {
+    p.sum_out = static_cast<uint2 *>(ex->slots[ex->rank]) + (exch_idx & 1) * parity_words + (size_t)ex->tp * dim;
+    p.sum_in = p.sum_out;
+    p.two_level = ex->tp >= (uint32_t)tuning().peer_two_level_min_tp ? 1u : 0u;
+  }
   p.tp = ex->tp;
   p.rank = ex->rank;
   p.exch_idx = exch_idx;
@@ -657,7 +662,7 @@ int greta_cuda_fused_ffn_front(greta_stream_t stream, int fmt, const float *x, c
 }
 
 // ---- tensor-parallel exchange over peer memory ---------------------------------------------------
-size_t greta_cuda_peer_slot_bytes(uint32_t tp, uint32_t dim) { return (size_t)2 * tp * dim * sizeof(uint2); }
+size_t greta_cuda_peer_slot_bytes(uint32_t tp, uint32_t dim) { return (size_t)2 * (tp + 1) * dim * sizeof(uint2); }
 
 int greta_cuda_peer_status(int *code) {
   GRETA_REQUIRE(code, "peer_status: null out pointer");

@@ -55,6 +55,12 @@ struct GemvParams {
   float *x_out;
   uint32_t tp, rank, exch_idx;
   uint32_t poll_limit;  // polls a consumer spends on one missing partial before it gives up (tuning switch peer_poll_limit)
+  // Two-level gather (tp >= tuning switch peer_two_level_min_tp): the CTAs of a consumer split the vector into blocks of 32,
+  // each sums the tp partials of its blocks into the residual stream once and publishes {sum, tag} words in the local
+  // sum buffer; then every CTA reads the dim summed words instead of tp x dim partial words.
+  const uint2 *sum_in;
+  uint2 *sum_out;
+  uint32_t two_level;
 };
 
 // Tag of exchange number exch_idx at the current position: strictly increasing within a decode session.
@@ -74,32 +80,37 @@ __device__ __forceinline__ uint4 ld_peer16(const void *src) {
   asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src) : "memory");
   return v;
 }
-// Adds the tp partials of elements idx .. idx+3 to v, in rank order, waiting (bounded) for their tags.  The
-// loads of four sources at a time are issued before any tag is looked at: one round trip to L2 per four
-// ranks when the partials are already there, not one per rank.
-__device__ __forceinline__ void add_peer_partials(const GemvParams &p, uint32_t idx, uint32_t tag, float (&v)[4]) {
+__device__ __forceinline__ uint2 ld_peer8(const void *src) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(src) : "memory");
+  return v;
+}
+// Adds the `nsrc` tagged vectors at `base` ([nsrc][K] words) for elements idx .. idx+3 to v, in order, waiting (bounded) for
+// their tags.  The loads of four sources at a time are issued before any tag is looked at: one round trip to L2 per
+// four sources when the words are already there, not one per source.
+__device__ __forceinline__ void add_tagged_words(const GemvParams &p, const uint2 *base, uint32_t nsrc, uint32_t idx, uint32_t tag, float (&v)[4]) {
   constexpr int BATCH = 4;
   const uint32_t budget = peer_failed() ? 0u : p.poll_limit;
-  for (uint32_t r0 = 0; r0 < p.tp; r0 += BATCH) {
+  for (uint32_t r0 = 0; r0 < nsrc; r0 += BATCH) {
     uint4 a[BATCH], b[BATCH];
 #pragma unroll
     for (int i = 0; i < BATCH; ++i) {
-      if (r0 + i < p.tp) {
-        const uint2 *src = p.peer_in + (size_t)(r0 + i) * p.K + idx;
+      if (r0 + i < nsrc) {
+        const uint2 *src = base + (size_t)(r0 + i) * p.K + idx;
         a[i] = ld_peer16(src);
         b[i] = ld_peer16(src + 2);
       }
     }
 #pragma unroll
     for (int i = 0; i < BATCH; ++i) {
-      if (r0 + i < p.tp) {
+      if (r0 + i < nsrc) {
         uint32_t polls = 0;
         while (!(a[i].y == tag && a[i].w == tag && b[i].y == tag && b[i].w == tag)) {
           if (++polls > budget || ((polls & 255u) == 0 && peer_failed())) {
             g_peer_error = 1;
             break;
           }
-          const uint2 *src = p.peer_in + (size_t)(r0 + i) * p.K + idx;
+          const uint2 *src = base + (size_t)(r0 + i) * p.K + idx;
           a[i] = ld_peer16(src);
           b[i] = ld_peer16(src + 2);
         }
@@ -109,6 +120,39 @@ __device__ __forceinline__ void add_peer_partials(const GemvParams &p, uint32_t 
         v[3] += __uint_as_float(b[i].z);
       }
     }
+  }
+}
+
+// First level of the two-level gather: this CTA's blocks of 32 elements (block b belongs to CTA b % gridDim.x, one warp per
+// block, one element per lane): residual stream + the tp partials in rank order -> the local sum buffer, tagged, and x_out.
+__device__ __forceinline__ void peer_sum_slice(const GemvParams &p, uint32_t tag) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t nbk = p.K / 32;
+  const uint32_t budget = peer_failed() ? 0u : p.poll_limit;
+  const float *xin = reinterpret_cast<const float *>(p.x);
+  for (uint32_t b = blockIdx.x + gridDim.x * warp; b < nbk; b += gridDim.x * (blockDim.x >> 5)) {
+    const uint32_t e = b * 32 + lane;
+    float v = __ldcg(xin + e);
+    uint2 w[MAX_TP];
+#pragma unroll
+    for (int r = 0; r < MAX_TP; ++r)
+      if ((uint32_t)r < p.tp) w[r] = ld_peer8(p.peer_in + (size_t)r * p.K + e);  // all sources in flight before any tag is looked at
+#pragma unroll
+    for (int r = 0; r < MAX_TP; ++r) {
+      if ((uint32_t)r < p.tp) {
+        uint32_t polls = 0;
+        while (w[r].y != tag) {
+          if (++polls > budget || ((polls & 255u) == 0 && peer_failed())) {
+            g_peer_error = 1;
+            break;
+          }
+          w[r] = ld_peer8(p.peer_in + (size_t)r * p.K + e);
+        }
+        v += __uint_as_float(w[r].x);
+      }
+    }
+    st_peer(p.sum_out + e, make_uint2(__float_as_uint(v), tag));
+    p.x_out[e] = v;
   }
 }
 
@@ -627,6 +671,7 @@ __device__ void stage_fixed_point(const GemvParams &p, uint32_t m, uint32_t *xq,
   const uint32_t b0 = threadIdx.x >> 3;
   constexpr int NPR = PEER ? 4 : 2;  // passes kept in registers (the peer form has no other path: K <= 8192)
   if ((p.gamma && nb <= 64 * NPR) || PEER) {
+    if (PEER && p.two_level) peer_sum_slice(p, peer_tag(p));
     float v[NPR][4], gm[NPR][4];
 #pragma unroll
     for (int i = 0; i < NPR; ++i) {
@@ -639,8 +684,14 @@ __device__ void stage_fixed_point(const GemvParams &p, uint32_t m, uint32_t *xq,
         load_slot_values<FMT>(xf, xh, p.gamma, b0 + 64 * i, j, v[i], gm[i]);
         if (PEER) {
           const uint32_t idx = (b0 + 64 * i) * 32 + slot_element<FMT>(4 * j);
-          add_peer_partials(p, idx, peer_tag(p), v[i]);
-          if (blockIdx.x == 0) *reinterpret_cast<float4 *>(p.x_out + idx) = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+          if (p.two_level) {  // the summed stream, published by the CTA that owns the block
+#pragma unroll
+            for (int k = 0; k < 4; ++k) v[i][k] = 0.f;
+            add_tagged_words(p, p.sum_in, 1, idx, peer_tag(p), v[i]);
+          } else {
+            add_tagged_words(p, p.peer_in, p.tp, idx, peer_tag(p), v[i]);
+            if (blockIdx.x == 0) *reinterpret_cast<float4 *>(p.x_out + idx) = make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+          }
         }
       }
     }

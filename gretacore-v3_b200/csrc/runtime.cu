@@ -67,6 +67,8 @@ Tuning &tuning() {
     v.step_stages = e ? atoi(e) : 0;
     e = getenv("GRETA_PEER_POLL_LIMIT");
     v.peer_poll_limit = e ? (unsigned)strtoul(e, nullptr, 10) : (1u << 22);
+    e = getenv("GRETA_PEER_TWO_LEVEL_MIN_TP");
+    v.peer_two_level_min_tp = e ? atoi(e) : 4;
     e = getenv("GRETA_SKINNY_MAX_ROWS");
     v.skinny_max_rows = e ? atoi(e) : 32;
     return v;
@@ -116,6 +118,8 @@ int greta_cuda_set_tuning(const char *name, long long value) {
   } else if (!strcmp(name, "peer_poll_limit")) {
     GRETA_REQUIRE(value >= 1 && value <= (1ll << 30), "set_tuning: peer_poll_limit=%lld outside 1..2^30", value);
     t.peer_poll_limit = (unsigned)value;
+  } else if (!strcmp(name, "peer_two_level_min_tp")) {
+    t.peer_two_level_min_tp = (int)value;
   } else if (!strcmp(name, "skinny_max_rows")) {
     GRETA_REQUIRE(value >= 1 && value <= 32, "set_tuning: skinny_max_rows=%lld outside 1..32", value);
     t.skinny_max_rows = (int)value;

@@ -117,7 +117,8 @@ GRETA_API int greta_cuda_set_pdl(int on);
  *   cluster or through scratch), "gemm_tile" (GRETA_GEMM_TILE=<tokens>x<row tiles>; value = tokens * 10 + row
  *   tiles, 0 = automatic), "gemv_r2_cells" (GRETA_GEMV_R2_CELLS, < 0 = automatic), "step_stages"
  *   (GRETA_STEP_STAGES, 0 = automatic), "peer_poll_limit" (GRETA_PEER_POLL_LIMIT: polls a tensor-parallel
- *   consumer spends on one missing partial before it gives up, default 2^22), "skinny_max_rows"
+ *   consumer spends on one missing partial before it gives up, default 2^22), "peer_two_level_min_tp"
+ *   (GRETA_PEER_TWO_LEVEL_MIN_TP: ranks from which an exchange consumer gathers in two levels, default 4), "skinny_max_rows"
  *   (GRETA_SKINNY_MAX_ROWS, 1..32). */
 GRETA_API int greta_cuda_set_tuning(const char *name, long long value);
 /* Number of kernel launches this library has issued on the calling process (all threads). */
@@ -402,8 +403,10 @@ GRETA_API int greta_cuda_comm_allreduce_f32(void *comm, float *buf, size_t count
  *             travels with the value);
  *   consumer  ..._peer forms of the fused QKV and FFN-front operators: the activation staging waits (bounded)
  *             for the tp tagged partials in the local slot buffer, adds them to the residual stream x_in in
- *             rank order (bit-identical on every rank), normalises and goes on; CTA 0 writes the new stream
- *             to x_out (a different buffer from x_in).
+ *             rank order (bit-identical on every rank), normalises and goes on; the new stream is written
+ *             to x_out (a different buffer from x_in).  From 4 ranks on the gather has two levels: the CTAs
+ *             split the vector, each sums its blocks of 32 once and publishes the tagged sums in the local
+ *             buffer, and every CTA then reads dim summed words instead of tp x dim partial words.
  * Tags are ((*d_pos + 1) << 8) | exch_idx: they grow with the position, so a slot buffer must be zeroed,
  * on every rank and with a barrier after it, whenever a decode session restarts at an earlier position.
  * Consecutive exchanges must alternate exch_idx parity (two halves of the slot buffer), or be separated by
