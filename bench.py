@@ -220,6 +220,7 @@ def time_dominant_kernel(pkg, cfg, tp, batch=1, reps=4):
     x = g.DeviceBuffer.from_numpy(rng.normal(0, 1, batch * D).astype(np.float32))
     gam = g.DeviceBuffer.from_numpy(np.ones(D, np.float32))
     y = g.DeviceBuffer(batch * F * 4)
+    ws = g.DeviceBuffer(lib.greta_cuda_gemv_batch_workspace_bytes(batch, D))
     stream = C.c_void_p()
     g.check(lib.greta_cuda_stream_create(C.byref(stream)))
 
@@ -228,7 +229,7 @@ def time_dominant_kernel(pkg, cfg, tp, batch=1, reps=4):
             if batch == 1:
                 g.check(lib.greta_cuda_fused_ffn_front(stream, g.FMT_Q4_0, x.ptr, gam.ptr, 1e-5, a.ptr, b.ptr, c.ptr, d.ptr, y.ptr, D, F))
             else:
-                g.check(lib.greta_cuda_fused_ffn_front_batch(stream, g.FMT_Q4_0, x.ptr, gam.ptr, 1e-5, a.ptr, b.ptr, c.ptr, d.ptr, y.ptr, batch, D, F))
+                g.check(lib.greta_cuda_fused_ffn_front_batch(stream, g.FMT_Q4_0, x.ptr, gam.ptr, 1e-5, a.ptr, b.ptr, c.ptr, d.ptr, y.ptr, batch, D, F, ws.ptr))
 
     one_pass()
     g.check(lib.greta_cuda_stream_synchronize(stream))
@@ -326,7 +327,7 @@ def gemv_shapes(pkg):
         y.free()
 
 
-def gemv_batch_shapes(pkg, M=16):
+def gemv_batch_shapes(pkg, M=16, prepared=True):
     """Times the batched operators (M activation rows, weights streamed once) on the projection shapes of the 70B and 7B
     models and the grouped-query batched attention at 16 x 4096 keys: distinct weight / cache copies rotate so nothing is
     served from L2, launches are captured in one CUDA graph, CUDA events.  One JSON line per shape."""
@@ -380,24 +381,26 @@ def gemv_batch_shapes(pkg, M=16):
         y = g.DeviceBuffer(M * rows * 4)
         dpos = g.DeviceBuffer.from_numpy(np.full(M, 7, np.uint32))
         kc = g.DeviceBuffer(M * 8 * 16 * 128 * 2, zero=True)
+        ws = g.DeviceBuffer(lib.greta_cuda_gemv_batch_workspace_bytes(M, K)) if prepared else None
+        wsp = ws.ptr if ws else None
 
         def one_pass():
             for qs, d in planes:
                 if kind == "plain":
-                    g.check(lib.greta_cuda_gemv_batch(stream, g.FMT_Q4_0, x.ptr, None, 0.0, qs.ptr, d.ptr, None, y.ptr, M, N, K, 0))
+                    g.check(lib.greta_cuda_gemv_batch(stream, g.FMT_Q4_0, x.ptr, None, 0.0, qs.ptr, d.ptr, None, y.ptr, M, N, K, 0, wsp))
                 elif kind == "swiglu":
                     half = N * (K // 32)
                     g.check(lib.greta_cuda_fused_ffn_front_batch(stream, g.FMT_Q4_0, x.ptr, gam.ptr, 1e-5, qs.ptr, d.ptr, qs.ptr + half * 16,
-                                                                 d.ptr + half * 2, y.ptr, M, K, N))
+                                                                 d.ptr + half * 2, y.ptr, M, K, N, wsp))
                 else:                                      # 64 query heads + 8 + 8 KV heads of 128
                     oq, ok = 8192 * (K // 32), 9216 * (K // 32)
                     g.check(lib.greta_cuda_fused_rmsnorm_qkv_rope_kv_batch(stream, g.FMT_Q4_0, x.ptr, gam.ptr, 1e-5, qs.ptr, d.ptr, qs.ptr + oq * 16,
                                                                            d.ptr + oq * 2, qs.ptr + ok * 16, d.ptr + ok * 2, y.ptr, None, None, kc.ptr,
-                                                                           kc.ptr, dpos.ptr, M, 64, 8, 128, 16, 500000.0, K))
+                                                                           kc.ptr, dpos.ptr, M, 64, 8, 128, 16, 500000.0, K, wsp))
 
         us = timed(one_pass, copies)
         alg = wbytes + M * K * 4 + M * (N if kind != "qkv" else rows) * 4
-        print(json.dumps({"case": "gemv_batch_shapes", "op": kind, "rows_of_x": M, "N": N, "K": K, "us_per_launch": round(us, 2),
+        print(json.dumps({"case": "gemv_batch_shapes", "op": kind, "prepared_activations": bool(prepared), "rows_of_x": M, "N": N, "K": K, "us_per_launch": round(us, 2),
                           "algorithmic_bytes": alg, "gb_per_s": round(alg / us / 1e3, 1), "frac_of_peak": round(alg / us / 1e3 / peak, 3),
                           "peak_source": f"of {peak_src}"}), flush=True)
         for qs, d in planes:
@@ -487,8 +490,9 @@ def run_case(pkg, name):
         w = planes(N, K, 5)
         x = g.DeviceBuffer.from_numpy(rng.normal(0, 1, M * K).astype(np.float32))
         y = g.DeviceBuffer(M * N * 4)
+        ws = g.DeviceBuffer(lib.greta_cuda_gemv_batch_workspace_bytes(M, K))
         for i in range(10):
-            g.check(lib.greta_cuda_gemv_batch(None, g.FMT_Q4_0, x.ptr, None, 0.0, w[i % 5][0].ptr, w[i % 5][1].ptr, None, y.ptr, M, N, K, 0))
+            g.check(lib.greta_cuda_gemv_batch(None, g.FMT_Q4_0, x.ptr, None, 0.0, w[i % 5][0].ptr, w[i % 5][1].ptr, None, y.ptr, M, N, K, 0, ws.ptr))
     elif name == "attn_batch":       # grouped-query batched attention: 16 sequences x 2048 keys, 64 / 8 heads of 128 (134 MB per launch), 2 caches
         M, H, Hkv, Dh, L, S = 16, 64, 8, 128, 2048, 2112
         kv = rng.normal(0, 1, M * Hkv * S * Dh).astype(np.float16).view(np.uint16)

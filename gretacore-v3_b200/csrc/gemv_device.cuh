@@ -61,6 +61,10 @@ struct GemvParams {
   const uint2 *sum_in;
   uint2 *sum_out;
   uint32_t two_level;
+  // Batched form with prepared activations (gemv_batch.cu): x already split into fp16 pairs in matrix-instruction
+  // fragment order, and the factor that finishes each activation row (1 / power-of-two scale, times 1 / rms).
+  const uint8_t *xprep;
+  const float *rowmul;
 };
 
 // Tag of exchange number exch_idx at the current position: strictly increasing within a decode session.

@@ -176,6 +176,7 @@ bool BlockScheduler::allocate_activations(size_t batch_size, size_t max_seq_len,
   if (!dev(a.gemm_ws, greta_cuda_gemm_workspace_bytes((uint32_t)max_seq_len, std::max(c.dim, c.hidden_dim)))) return false;
   if (!dev(logits_, B * (size_t)c.vocab_size * 4)) return false;
   if (B > 1 && c.tp_size > 1 && !dev(logits_local_, B * (size_t)vocab_l_ * 4)) return false;
+  if (B > 1 && !dev(batch_ws_, greta_cuda_gemv_batch_workspace_bytes((uint32_t)B, std::max({c.dim, (uint32_t)ql, hidden_l_})))) return false;
   greta_cuda_memset(a.attn_scratch.data(), 0, a.attn_scratch.size(), nullptr);
   greta_cuda_memset(a.kv_cache_k.data(), 0, cache, nullptr);
   greta_cuda_memset(a.kv_cache_v.data(), 0, cache, nullptr);
@@ -453,23 +454,24 @@ bool BlockScheduler::decode_layers_batch(std::string *err) {
   float *x = static_cast<float *>(a.x.data()), *q = static_cast<float *>(a.q.data()), *att = static_cast<float *>(a.attn_out.data());
   float *gate = static_cast<float *>(a.mlp_gate.data());
   const bool tp = c.tp_size > 1, fold = !tp || c.tp_rank == 0;  // one rank folds the residual in, the others contribute bare partials
+  void *ws = batch_ws_.data();  // prepared activations of the operator in flight (one buffer serves them all: stream order)
   for (uint32_t l = 0; l < c.num_layers; ++l) {
     BlockBuffers &b = blocks_[l];
     uint16_t *kc = static_cast<uint16_t *>(a.kv_cache_k.data()) + l * cache_l;
     uint16_t *vc = static_cast<uint16_t *>(a.kv_cache_v.data()) + l * cache_l;
     GRETA_TRY(greta_cuda_fused_rmsnorm_qkv_rope_kv_batch(s, fmt, x, static_cast<const float *>(b.attn_norm.data()), c.rms_eps, b.wq.data(),
                                                          b.s_wq.data(), b.wk.data(), b.s_wk.data(), b.wv.data(), b.s_wv.data(), q, nullptr, nullptr,
-                                                         kc, vc, dpos, B, heads_l_, kv_heads_l_, Dh, (uint32_t)max_seq_, c.rope_base, D),
+                                                         kc, vc, dpos, B, heads_l_, kv_heads_l_, Dh, (uint32_t)max_seq_, c.rope_base, D, ws),
               "fused qkv (batch)");
     GRETA_TRY(greta_cuda_attn_decode_batch(s, q, kc, vc, att, dpos, B, heads_l_, kv_heads_l_, Dh, (uint32_t)max_seq_, scale, a.attn_scratch.data(),
                                            a.attn_scratch.size()),
               "attention decode (batch)");
-    GRETA_TRY(greta_cuda_gemv_batch(s, fmt, att, nullptr, 0.f, b.wo.data(), b.s_wo.data(), fold ? x : nullptr, x, B, D, ql, 0), "wo (batch)");
+    GRETA_TRY(greta_cuda_gemv_batch(s, fmt, att, nullptr, 0.f, b.wo.data(), b.s_wo.data(), fold ? x : nullptr, x, B, D, ql, 0, ws), "wo (batch)");
     if (tp && all_reduce_(x, (size_t)B * D, s) != 0) return fail(err, "all-reduce after the O-projection failed");
     GRETA_TRY(greta_cuda_fused_ffn_front_batch(s, fmt, x, static_cast<const float *>(b.ffn_norm.data()), c.rms_eps, b.w1.data(), b.s_w1.data(),
-                                               b.w3.data(), b.s_w3.data(), gate, B, D, hidden_l_),
+                                               b.w3.data(), b.s_w3.data(), gate, B, D, hidden_l_, ws),
               "ffn front (batch)");
-    GRETA_TRY(greta_cuda_gemv_batch(s, fmt, gate, nullptr, 0.f, b.w2.data(), b.s_w2.data(), fold ? x : nullptr, x, B, D, hidden_l_, 0), "w2 (batch)");
+    GRETA_TRY(greta_cuda_gemv_batch(s, fmt, gate, nullptr, 0.f, b.w2.data(), b.s_w2.data(), fold ? x : nullptr, x, B, D, hidden_l_, 0, ws), "w2 (batch)");
     if (tp && all_reduce_(x, (size_t)B * D, s) != 0) return fail(err, "all-reduce after the down-projection failed");
   }
   return true;
@@ -485,7 +487,7 @@ bool BlockScheduler::lm_head_batch(std::string *err) {
   float *logits = static_cast<float *>(logits_.data());
   if (c.tp_size == 1) {
     GRETA_TRY(greta_cuda_gemv_batch(s, lf, x, static_cast<const float *>(output_norm_.data()), c.rms_eps, output_weight_.data(), d, nullptr, logits,
-                                    batch_, c.vocab_size, c.dim, 0),
+                                    batch_, c.vocab_size, c.dim, 0, batch_ws_.data()),
               "lm head (batch)");
     return true;
   }
@@ -493,7 +495,7 @@ bool BlockScheduler::lm_head_batch(std::string *err) {
   if (!all_reduce_) return fail(err, "tensor parallel run without an all-reduce hook");
   float *local = static_cast<float *>(logits_local_.data());
   GRETA_TRY(greta_cuda_gemv_batch(s, lf, x, static_cast<const float *>(output_norm_.data()), c.rms_eps, output_weight_.data(), d, nullptr, local,
-                                  batch_, vocab_l_, c.dim, 0),
+                                  batch_, vocab_l_, c.dim, 0, batch_ws_.data()),
             "lm head (batch)");
   GRETA_TRY(greta_cuda_memcpy_2d_d2d(logits + (size_t)c.tp_rank * vocab_l_, (size_t)c.vocab_size * 4, local, (size_t)vocab_l_ * 4,
                                      (size_t)vocab_l_ * 4, batch_, s),

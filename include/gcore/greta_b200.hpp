@@ -486,6 +486,7 @@ private:
   bool graph_captured_ = false, initialized_ = false;
   size_t decode_steps_ = 0, decode_pos0_ = 0, max_seq_ = 0;
   uint32_t batch_ = 1, cur_seq_ = 0;      // sequences held; the one forward() / execute_layer() work on
+  gcore::rt::cuda::Buffer batch_ws_;      // batched decode: activations prepared for the tensor-core matmul kernels
   gcore::rt::cuda::Buffer logits_local_;  // tensor-parallel batch: this rank's slice of the logits before placement
   AllReduceFn all_reduce_;
   greta_peer_exchange peer_{};            // tp == 0: not installed

@@ -203,22 +203,27 @@ GRETA_API int greta_cuda_fused_ffn_front(greta_stream_t stream, int fmt, const f
  * (src/inference/src/block_scheduler.cpp:1490-1494).  Formats: Q4_0, Q8_0, F16.  x is fp32 [M][K], row-major,
  * 16-byte aligned; outputs are [M][...] row-major.  k_slices forces the number of K slices (1, 2, 4 or 8; 0 =
  * chosen from the shape).
+ * workspace: greta_cuda_gemv_batch_workspace_bytes(M, K) bytes of device memory, 16-byte aligned, or NULL.  With it the
+ * activations are converted once, by a small kernel in front, into the layout the tensor-core kernel consumes; without
+ * it every CTA of the matmul kernel repeats that conversion for itself (about 2.5 times slower, same results to the
+ * last bit of the fp16 pairs).  One workspace can serve every call on a stream.
  *
  * y[M][N] = (resid ? resid[M][N] : 0) + rmsnorm?(x)[M][K] * dequant(W)^T; gamma == NULL: no norm. */
+GRETA_API size_t greta_cuda_gemv_batch_workspace_bytes(uint32_t M, uint32_t K);
 GRETA_API int greta_cuda_gemv_batch(greta_stream_t stream, int fmt, const float *x, const float *gamma, float eps,
                                     const void *qs, const void *d, const float *resid, float *y, uint32_t M, uint32_t N,
-                                    uint32_t K, uint32_t k_slices);
+                                    uint32_t K, uint32_t k_slices, void *workspace);
 /* greta_cuda_fused_rmsnorm_qkv_rope_kv for M sequences: q_out [M][H*Dh]; row m is rotated at d_pos[m] and its K / V
  * go to row d_pos[m] of sequence m's cache; caches are fp16 [M][Hkv][max_seq][Dh]. */
 GRETA_API int greta_cuda_fused_rmsnorm_qkv_rope_kv_batch(
     greta_stream_t stream, int fmt, const float *x, const float *gamma, float eps, const void *wq_qs, const void *wq_d,
     const void *wk_qs, const void *wk_d, const void *wv_qs, const void *wv_d, float *q_out, float *k_out, float *v_out,
     void *k_cache_f16, void *v_cache_f16, const uint32_t *d_pos, uint32_t M, uint32_t num_heads, uint32_t num_heads_kv,
-    uint32_t head_dim, uint32_t max_seq_len, float rope_base, uint32_t D);
+    uint32_t head_dim, uint32_t max_seq_len, float rope_base, uint32_t D, void *workspace);
 /* greta_cuda_fused_ffn_front for M rows: y [M][F]. */
 GRETA_API int greta_cuda_fused_ffn_front_batch(greta_stream_t stream, int fmt, const float *x, const float *gamma, float eps,
                                                const void *w1_qs, const void *w1_d, const void *w3_qs, const void *w3_d,
-                                               float *y, uint32_t M, uint32_t D, uint32_t F);
+                                               float *y, uint32_t M, uint32_t D, uint32_t F, void *workspace);
 
 /* ------------------------------------------------------------------ whole decode step, one launch
  * All decoder layers of one batch-1 decode step as a single persistent kernel: the five operators

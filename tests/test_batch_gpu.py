@@ -40,6 +40,16 @@ def _dev(g, arr):
     return b
 
 
+def _ws(g, use, M, K):
+    """Workspace for the prepared-activation route, or None for the route that converts inside the matmul kernel."""
+    if not use:
+        return None
+    b = g.DeviceBuffer(g.cuda().greta_cuda_gemv_batch_workspace_bytes(M, K))
+    b.fill(0xFF)
+    _KEEP.append(b)
+    return b.ptr
+
+
 def _nan(g, n_floats):
     b = g.DeviceBuffer(max(n_floats, 1) * 4)
     b.fill(0xFF)
@@ -47,10 +57,11 @@ def _nan(g, n_floats):
     return b
 
 
+@pytest.mark.parametrize("prepared", [True, False])
 @pytest.mark.parametrize("name", ["q4_0", "q8_0"])
 @pytest.mark.parametrize("M,N,K,slices", [(2, 128, 256, 0), (5, 200, 1376, 1), (16, 384, 2048, 2), (16, 130, 4096, 8), (32, 256, 1024, 4),
-                                          (9, 48, 11008, 0), (16, 4096, 4096, 0)])
-def test_gemv_batch_matches_oracle(g, name, M, N, K, slices):
+                                          (9, 48, 11008, 0), (16, 4096, 4096, 0), (16, 300, 2304, 4), (27, 520, 3584, 2)])
+def test_gemv_batch_matches_oracle(g, name, M, N, K, slices, prepared):
     """Plain, with residual, and with the RMSNorm in front; ragged row tiles, K that is not a multiple of the 256-value
     cell, every number of K slices."""
     ofmt, gfmt = FMTS[name]
@@ -65,15 +76,16 @@ def test_gemv_batch_matches_oracle(g, name, M, N, K, slices):
     xd, gd, rd = _dev(g, x), _dev(g, gamma), _dev(g, resid)
     want = O.gemv(x, blk, ofmt, N, K)
     y = _nan(g, M * N)
-    g.check(lib.greta_cuda_gemv_batch(None, gfmt, xd.ptr, None, 0.0, w.qs.ptr, w.d.ptr, None, y.ptr, M, N, K, slices), "gemv_batch")
+    ws = _ws(g, prepared, M, K)
+    g.check(lib.greta_cuda_gemv_batch(None, gfmt, xd.ptr, None, 0.0, w.qs.ptr, w.d.ptr, None, y.ptr, M, N, K, slices, ws), "gemv_batch")
     got = y.download(np.float32).reshape(M, N)
     for m in range(M):                                    # per row: a small row must not hide behind a large one
         assert max_abs_rel(got[m], want[m]) < TIGHT, m
     y.fill(0xFF)
-    g.check(lib.greta_cuda_gemv_batch(None, gfmt, xd.ptr, None, 0.0, w.qs.ptr, w.d.ptr, rd.ptr, y.ptr, M, N, K, slices), "gemv_batch+resid")
+    g.check(lib.greta_cuda_gemv_batch(None, gfmt, xd.ptr, None, 0.0, w.qs.ptr, w.d.ptr, rd.ptr, y.ptr, M, N, K, slices, ws), "gemv_batch+resid")
     assert max_abs_rel(y.download(np.float32).reshape(M, N), want.astype(np.float64) + resid) < TIGHT
     y.fill(0xFF)
-    g.check(lib.greta_cuda_gemv_batch(None, gfmt, xd.ptr, gd.ptr, 1e-5, w.qs.ptr, w.d.ptr, None, y.ptr, M, N, K, slices), "rmsnorm+gemv_batch")
+    g.check(lib.greta_cuda_gemv_batch(None, gfmt, xd.ptr, gd.ptr, 1e-5, w.qs.ptr, w.d.ptr, None, y.ptr, M, N, K, slices, ws), "rmsnorm+gemv_batch")
     wantn = O.gemv(O.rmsnorm(x, gamma, 1e-5), blk, ofmt, N, K)
     got = y.download(np.float32).reshape(M, N)
     for m in range(M):
@@ -84,7 +96,8 @@ def test_gemv_batch_matches_oracle(g, name, M, N, K, slices):
     assert max_abs_rel(y.download(np.float32).reshape(M, N), want) < TIGHT
 
 
-def test_gemv_batch_fp16_weights_lm_head_form(g):
+@pytest.mark.parametrize("prepared", [True, False])
+def test_gemv_batch_fp16_weights_lm_head_form(g, prepared):
     lib = g.cuda()
     rng = np.random.default_rng(3)
     M, N, K = 16, 1000, 512
@@ -92,7 +105,8 @@ def test_gemv_batch_fp16_weights_lm_head_form(g):
     x = rng.normal(0, 1, (M, K)).astype(np.float32)
     gamma = rng.normal(1, 0.1, K).astype(np.float32)
     y = _nan(g, M * N)
-    g.check(lib.greta_cuda_gemv_batch(None, g.FMT_F16, _dev(g, x).ptr, _dev(g, gamma).ptr, 1e-5, _dev(g, wbits).ptr, None, None, y.ptr, M, N, K, 0))
+    g.check(lib.greta_cuda_gemv_batch(None, g.FMT_F16, _dev(g, x).ptr, _dev(g, gamma).ptr, 1e-5, _dev(g, wbits).ptr, None, None, y.ptr, M, N, K, 0,
+                                      _ws(g, prepared, M, K)))
     want = O.gemm_f16w(O.rmsnorm(x, gamma, 1e-5), wbits, N, K)
     assert max_abs_rel(y.download(np.float32).reshape(M, N), want) < TIGHT
 
@@ -109,9 +123,10 @@ def test_gemv_more_than_32_rows_loops_the_batched_kernel(g):
     assert max_abs_rel(y.download(np.float32).reshape(M, N), O.gemv(x, blk, O.FMT_Q4_0, N, K)) < TIGHT
 
 
+@pytest.mark.parametrize("prepared", [True, False])
 @pytest.mark.parametrize("name", ["q4_0", "q8_0"])
 @pytest.mark.parametrize("M,H,Hkv,Dh,D", [(3, 4, 4, 128, 512), (16, 8, 2, 64, 256), (16, 64, 8, 128, 1024)])
-def test_fused_qkv_batch(g, name, M, H, Hkv, Dh, D):
+def test_fused_qkv_batch(g, name, M, H, Hkv, Dh, D, prepared):
     """Every sequence at its own position: its q is rotated there, its K / V land in that row of its own cache."""
     ofmt, gfmt = FMTS[name]
     lib = g.cuda()
@@ -129,7 +144,7 @@ def test_fused_qkv_batch(g, name, M, H, Hkv, Dh, D):
     _KEEP.extend([kc, vc])
     g.check(lib.greta_cuda_fused_rmsnorm_qkv_rope_kv_batch(None, gfmt, _dev(g, x).ptr, _dev(g, gamma).ptr, 1e-5, wq.qs.ptr, wq.d.ptr, wk.qs.ptr,
                                                            wk.d.ptr, wv.qs.ptr, wv.d.ptr, q_out.ptr, None, None, kc.ptr, vc.ptr, _dev(g, pos).ptr, M,
-                                                           H, Hkv, Dh, max_seq, 10000.0, D), "fused_qkv_batch")
+                                                           H, Hkv, Dh, max_seq, 10000.0, D, _ws(g, prepared, M, D)), "fused_qkv_batch")
     got_q = q_out.download(np.float32).reshape(M, H * Dh)
     got_k = O.f16_bits_to_f32(kc.download(np.uint16)).reshape(M, Hkv, max_seq, Dh)
     got_v = O.f16_bits_to_f32(vc.download(np.uint16)).reshape(M, Hkv, max_seq, Dh)
@@ -147,15 +162,16 @@ def test_fused_qkv_batch(g, name, M, H, Hkv, Dh, D):
     k_out, v_out = _nan(g, M * Hkv * Dh), _nan(g, M * Hkv * Dh)
     g.check(lib.greta_cuda_fused_rmsnorm_qkv_rope_kv_batch(None, gfmt, _dev(g, x).ptr, None, 0.0, wq.qs.ptr, wq.d.ptr, wk.qs.ptr, wk.d.ptr, wv.qs.ptr,
                                                            wv.d.ptr, q_out.ptr, k_out.ptr, v_out.ptr, None, None, None, M, H, Hkv, Dh, max_seq, 10000.0,
-                                                           D), "fused_qkv_batch (plain)")
+                                                           D, _ws(g, prepared, M, D)), "fused_qkv_batch (plain)")
     assert max_abs_rel(q_out.download(np.float32).reshape(M, -1), O.gemv(x, bq, ofmt, H * Dh, D)) < TIGHT
     assert max_abs_rel(k_out.download(np.float32).reshape(M, -1), O.gemv(x, bk, ofmt, Hkv * Dh, D)) < TIGHT
     assert max_abs_rel(v_out.download(np.float32).reshape(M, -1), O.gemv(x, bv, ofmt, Hkv * Dh, D)) < TIGHT
 
 
+@pytest.mark.parametrize("prepared", [True, False])
 @pytest.mark.parametrize("name", ["q4_0", "q8_0"])
 @pytest.mark.parametrize("M,D,F", [(2, 256, 34), (16, 512, 1377), (16, 4096, 11008)])
-def test_fused_ffn_front_batch(g, name, M, D, F):
+def test_fused_ffn_front_batch(g, name, M, D, F, prepared):
     ofmt, gfmt = FMTS[name]
     lib = g.cuda()
     rng = np.random.default_rng(60 + M + F)
@@ -165,7 +181,7 @@ def test_fused_ffn_front_batch(g, name, M, D, F):
     w1, w3 = g.Weight(b1, gfmt, F, D), g.Weight(b3, gfmt, F, D)
     y = _nan(g, M * F)
     g.check(lib.greta_cuda_fused_ffn_front_batch(None, gfmt, _dev(g, x).ptr, _dev(g, gamma).ptr, 1e-5, w1.qs.ptr, w1.d.ptr, w3.qs.ptr, w3.d.ptr, y.ptr,
-                                                 M, D, F), "ffn_front_batch")
+                                                 M, D, F, _ws(g, prepared, M, D)), "ffn_front_batch")
     xn = O.rmsnorm(x, gamma, 1e-5)
     want = O.silu_mul(O.gemv(xn, b1, ofmt, F, D), O.gemv(xn, b3, ofmt, F, D))
     got = y.download(np.float32).reshape(M, F)
@@ -223,9 +239,9 @@ def test_batch_entries_reject_bad_arguments(g):
     lib = g.cuda()
     buf = g.DeviceBuffer(1 << 16)
     _KEEP.append(buf)
-    assert lib.greta_cuda_gemv_batch(None, g.FMT_Q4_0, buf.ptr, None, 0.0, buf.ptr, buf.ptr, None, buf.ptr, 33, 64, 64, 0) == 4      # M > 32
-    assert lib.greta_cuda_gemv_batch(None, g.FMT_Q4_0, buf.ptr, None, 0.0, buf.ptr, buf.ptr, None, buf.ptr, 4, 64, 48, 0) == 4       # K % 32
-    assert lib.greta_cuda_gemv_batch(None, g.FMT_REF_INT4, buf.ptr, None, 0.0, buf.ptr, buf.ptr, None, buf.ptr, 4, 64, 64, 0) == 4   # format
+    assert lib.greta_cuda_gemv_batch(None, g.FMT_Q4_0, buf.ptr, None, 0.0, buf.ptr, buf.ptr, None, buf.ptr, 33, 64, 64, 0, None) == 4      # M > 32
+    assert lib.greta_cuda_gemv_batch(None, g.FMT_Q4_0, buf.ptr, None, 0.0, buf.ptr, buf.ptr, None, buf.ptr, 4, 64, 48, 0, None) == 4       # K % 32
+    assert lib.greta_cuda_gemv_batch(None, g.FMT_REF_INT4, buf.ptr, None, 0.0, buf.ptr, buf.ptr, None, buf.ptr, 4, 64, 64, 0, None) == 4   # format
     assert lib.greta_cuda_attn_decode_batch(None, buf.ptr, buf.ptr, buf.ptr, buf.ptr, None, 4, 8, 2, 64, 16, 1.0, None, 0) == 4      # no positions
     assert lib.greta_cuda_fused_rmsnorm_qkv_rope_kv_batch(None, g.FMT_Q4_0, buf.ptr, None, 0.0, buf.ptr, buf.ptr, buf.ptr, buf.ptr, buf.ptr, buf.ptr,
-                                                          buf.ptr, None, None, None, None, buf.ptr, 4, 8, 2, 64, 16, 1e4, 64) == 4  # positions, no cache
+                                                          buf.ptr, None, None, None, None, buf.ptr, 4, 8, 2, 64, 16, 1e4, 64, None) == 4  # positions, no cache
