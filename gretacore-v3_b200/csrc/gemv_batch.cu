@@ -584,18 +584,18 @@ __global__ void __launch_bounds__(PREP_THREADS) prep_rows_kernel(const float *__
 }
 
 template <int FMT>
-struct PFmt;  // warps per CTA, activation cells per shared-memory buffer
+struct PFmt;  // warps per CTA, CTAs per SM the shared-memory plan aims at
 template <>
 struct PFmt<GRETA_FMT_Q4_0> {
-  static constexpr int NW = 16;
+  static constexpr int NW = 8, CTAS_PER_SM = 2;
 };
 template <>
 struct PFmt<GRETA_FMT_Q8_0> {
-  static constexpr int NW = 16;
+  static constexpr int NW = 8, CTAS_PER_SM = 2;
 };
 template <>
 struct PFmt<GRETA_FMT_F16> {
-  static constexpr int NW = 8;
+  static constexpr int NW = 8, CTAS_PER_SM = 1;
 };
 
 template <int FMT, int MT>
@@ -603,11 +603,13 @@ struct PPlan {
   static constexpr int NW = PFmt<FMT>::NW, PB = BFmt<FMT>::PB;
   static constexpr int ROWB = CELL * PB + 16, STAGE = 16 * ROWB;
   static constexpr int ROWTAB = NW * 16 * (int)sizeof(RowSrc);
+  static constexpr int room_in(int limit, int xcells) { return (limit - 2 * xcells * CELL * MT * 1024 - ROWTAB) / (NW * STAGE); }
+  static constexpr int CTAS = (PFmt<FMT>::CTAS_PER_SM == 2 && room_in(112 * 1024, 1) >= 2) ? 2 : 1;  // CTAs per SM this plan fits
+  static constexpr int LIMIT = CTAS == 2 ? 112 * 1024 : (int)BSMEM_LIMIT;
   // Two activation buffers of XCELLS cells each; a buffer is refilled XCELLS cells ahead, which the weight ring must
-  // cover: XCELLS <= DEPTH - 1.
-  static constexpr int XCELLS_WANT = MT == 4 ? 1 : 2;
-  static constexpr int room(int xcells) { return (int)((BSMEM_LIMIT - 2 * xcells * CELL * MT * 1024 - ROWTAB) / (NW * STAGE)); }
-  static constexpr int XCELLS = room(XCELLS_WANT) >= XCELLS_WANT + 1 ? XCELLS_WANT : 1;
+  // cover: XCELLS <= DEPTH - 1.  Two CTAs of 8 warps per SM (128 rows each) balance the SMs better than one of 16.
+  static constexpr int room(int xcells) { return room_in(LIMIT, xcells); }
+  static constexpr int XCELLS = (MT < 4 && room(2) >= 3) ? 2 : 1;
   static constexpr int DEPTH = room(XCELLS) > 4 ? 4 : room(XCELLS);
   static constexpr int XBUF = XCELLS * CELL * MT * 1024;
   static constexpr size_t SMEM = (size_t)2 * XBUF + ROWTAB + (size_t)NW * DEPTH * STAGE;
@@ -624,7 +626,7 @@ __device__ __forceinline__ void mma_f16_first(float (&d)[4], uint32_t a0, uint32
 // walk the cells of the slice in step; the prepared activations of the next cells arrive by cp.async in the same commit
 // groups as the weight cells, one CTA-wide barrier per activation buffer.
 template <int FMT, int EPI, int MT>
-__global__ void __launch_bounds__(PFmt<FMT>::NW * 32, 1) gemv_batchp_kernel(const GemvParams p) {
+__global__ void __launch_bounds__(PFmt<FMT>::NW * 32, PPlan<FMT, MT>::CTAS) gemv_batchp_kernel(const GemvParams p) {
   using F = BFmt<FMT>;
   using P = PPlan<FMT, MT>;
   constexpr int NW = P::NW, PB = F::PB, ROWB = P::ROWB, STAGE = P::STAGE, DEPTH = P::DEPTH, XCELLS = P::XCELLS, XBUF = P::XBUF;
@@ -788,7 +790,7 @@ uint32_t count_tiles(const GemvParams &p) {
   return (p.H + p.Hkv) * ((p.Dh / 2) / 8) + (p.Hkv * p.Dh + 15) / 16;
 }
 
-uint32_t pick_k_slices(uint32_t row_groups, uint32_t K, uint32_t forced);
+uint32_t pick_k_slices(uint32_t row_groups, uint32_t K, uint32_t forced, uint32_t ctas_per_sm);
 
 template <int FMT, int EPI, int MT, int TPW>
 int launch_batch_cfg(cudaStream_t stream, GemvParams p) {
@@ -807,7 +809,7 @@ int launch_batch_cfg(cudaStream_t stream, GemvParams p) {
     attr_set[dev] = true;
   }
   const uint32_t row_groups = (p.groups + BW * TPW - 1) / (BW * TPW);
-  const uint32_t best_kw = pick_k_slices(row_groups, p.K, p.kw);
+  const uint32_t best_kw = pick_k_slices(row_groups, p.K, p.kw, 1);
   GRETA_REQUIRE(row_groups <= 65535, "batched gemv: %u row groups exceed the grid", row_groups);
   dim3 grid(best_kw, row_groups);
   GRETA_CUDA_TRY(launch_pdl_cluster(kern, grid, dim3(BTHREADS), best_kw, SMEM, stream, p));
@@ -824,9 +826,9 @@ int launch_batch_mt(cudaStream_t stream, GemvParams p) {
   return launch_batch_cfg<FMT, EPI, MT, 1>(stream, p);
 }
 
-uint32_t pick_k_slices(uint32_t row_groups, uint32_t K, uint32_t forced) {
-  // K slices: the split that fills the SMs best in whole waves, each slice at least 4 cells (1024 values) long.
-  const uint32_t ncell = (K / 32 + CELL - 1) / CELL, sms = (uint32_t)sm_count();
+uint32_t pick_k_slices(uint32_t row_groups, uint32_t K, uint32_t forced, uint32_t ctas_per_sm) {
+  // K slices: the split that fills the CTA slots of the GPU best in whole waves, each slice at least 4 cells (1024 values) long.
+  const uint32_t ncell = (K / 32 + CELL - 1) / CELL, sms = (uint32_t)sm_count() * ctas_per_sm;
   if (forced >= 1 && forced <= 8 && (forced & (forced - 1)) == 0 && forced <= ncell) return forced;
   uint32_t best_kw = 1;
   double best = -1.0;
@@ -862,7 +864,7 @@ int launch_batch_prepared(cudaStream_t stream, GemvParams p, void *workspace) {
   if (int rc = launched("prep_rows_kernel")) return rc;
   const uint32_t row_groups = (p.groups + P::NW - 1) / P::NW;
   GRETA_REQUIRE(row_groups <= 65535, "batched gemv: %u row groups exceed the grid", row_groups);
-  const uint32_t kw = pick_k_slices(row_groups, p.K, p.kw);
+  const uint32_t kw = pick_k_slices(row_groups, p.K, p.kw, P::CTAS);
   GRETA_CUDA_TRY(launch_pdl_cluster(kern, dim3(kw, row_groups), dim3(P::NW * 32), kw, P::SMEM, stream, p));
   return launched("gemv_batchp_kernel");
 }

@@ -1,7 +1,7 @@
 """One rank of the tensor-parallel check (launched by test_tp_gpu.py under torch.distributed.run).
 Each rank holds its shard of a small Llama-shaped model and runs prefill + greedy decode twice: with the NCCL
-all-reduce, and with the exchange fused into the GEMV kernels over peer memory; rank 0 compares the ids of both
-with the CPU oracle's and reads the exchange's time-out status."""
+all-reduce, and with the exchange fused into the GEMV kernels over peer memory; then a batch of five sequences
+decoding in step; rank 0 compares all ids with the CPU oracle's and reads the exchange's time-out status."""
 import ctypes as C
 import json
 import os
@@ -54,6 +54,15 @@ def main():
                 g.check(lib.greta_cuda_ipc_close(ptr))
             ranks.barrier()
             keep[0].free()
+    # a batch of sequences under tensor parallelism (batched kernels, all-reduce over [batch x dim], logits gathered per rank slice)
+    B, blen = 5, 14
+    bprompts = np.stack([pkg.model.synth_tokens(seed, blen, CFG["vocab"], stream=(1 << 40) + b) for b in range(B)])
+    m = pkg.model.Model(CFG, tp_rank=ranks.rank, tp_size=ranks.world, batch=B)
+    m.set_comm(comm)
+    m.load_synthetic(seed)
+    out["batch"] = m.generate_batch(bprompts, n_new).tolist()
+    ranks.barrier()
+    m.close()
     if ranks.rank == 0:
         from oracle import oracle as O
         weights = pkg.model.synth_weights(CFG, seed)
@@ -63,6 +72,9 @@ def main():
             want, gaps = O.Model(CFG, weights).generate(prompt, n_new)
             ok = ok and out["nccl" + str(plen)] == want and out["fused" + str(plen)] == want and min(gaps) > 1e-6
             out["want" + str(plen)] = want
+        for b in range(B):
+            want, gaps = O.Model(CFG, weights).generate(bprompts[b], n_new)
+            ok = ok and out["batch"][b] == want and min(gaps) > 1e-6
         out["ok"] = bool(ok) and out.get("peer_status") == 0 and not out.get("repeat_mismatch")
         print("TP_RESULT " + json.dumps(out), flush=True)
     g.check(lib.greta_cuda_comm_destroy(comm))
