@@ -260,6 +260,62 @@ def time_dominant_kernel(pkg, cfg, tp, batch=1, reps=4):
     return us, alg_bytes, name
 
 
+def time_prefill_gemm(pkg, reps=5):
+    """The prefill GEMM benchmark shape: fp16 activations [512 x 4096] x Q4_0 weights [11008 x 4096] -> fp16 [512 x 11008] on
+    the tcgen05 kernel, 6 distinct weight copies (152 MB, beyond L2) captured in one graph, CUDA events; fraction of the
+    measured dense bf16 tensor peak (fp16 runs at the same rate)."""
+    import ctypes as C
+    g = pkg.ffi
+    lib = g.cuda()
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peak, src = float(json.load(f)["bf16_tflops"]), "measured"
+    except Exception:
+        peak, src = 1590.0, "fallback"
+    M, N, K = 512, 11008, 4096
+    rng = np.random.default_rng(1)
+    nb = N * (K // 32)
+    qs_h = rng.integers(0, 256, nb * 16, dtype=np.uint8)
+    d_h = (np.abs(rng.normal(0, 0.02, nb)) / 8).astype(np.float16).view(np.uint16)
+    w = [(g.DeviceBuffer.from_numpy(qs_h), g.DeviceBuffer.from_numpy(d_h)) for _ in range(6)]
+    a = g.DeviceBuffer.from_numpy(rng.normal(0, 1, (M, K)).astype(np.float16).view(np.uint16))
+    c = g.DeviceBuffer(M * N * 2)
+    stream, graph, ex, e0, e1 = C.c_void_p(), C.c_void_p(), C.c_void_p(), C.c_void_p(), C.c_void_p()
+    g.check(lib.greta_cuda_stream_create(C.byref(stream)))
+
+    def one_pass():
+        for qs, d in w:
+            g.check(lib.greta_cuda_gemm(stream, g.FMT_Q4_0, a.ptr, 1, qs.ptr, d.ptr, c.ptr, 1, M, N, K, None))
+
+    one_pass()
+    g.check(lib.greta_cuda_stream_synchronize(stream))
+    g.check(lib.greta_cuda_graph_capture_begin(stream))
+    one_pass()
+    g.check(lib.greta_cuda_graph_capture_end(stream, C.byref(graph)))
+    g.check(lib.greta_cuda_graph_instantiate(graph, C.byref(ex)))
+    lib.greta_cuda_event_create(C.byref(e0))
+    lib.greta_cuda_event_create(C.byref(e1))
+    for _ in range(3):
+        lib.greta_cuda_graph_launch(ex, stream)
+    lib.greta_cuda_stream_synchronize(stream)
+    lib.greta_cuda_event_record(e0, stream)
+    for _ in range(reps):
+        lib.greta_cuda_graph_launch(ex, stream)
+    lib.greta_cuda_event_record(e1, stream)
+    lib.greta_cuda_event_synchronize(e1)
+    ms = C.c_float()
+    lib.greta_cuda_event_elapsed_ms(e0, e1, C.byref(ms))
+    us = ms.value * 1e3 / (reps * len(w))
+    for qs, d in w:
+        qs.free()
+        d.free()
+    a.free()
+    c.free()
+    tflops = 2.0 * M * N * K / us / 1e6
+    return {"shape": "fp16 [512 x 4096] x Q4_0 [11008 x 4096] -> fp16 [512 x 11008]", "us_per_launch": us, "tflops": tflops, "peak_tflops": peak,
+            "frac": tflops / peak, "peak_source": f"of {src}", "bound": "tensor"}
+
+
 # ----------------------------------------------------------------------------- GEMV bandwidth per projection shape
 def gemv_shapes(pkg):
     """Times the plain Q4_0 / Q8_0 GEMV on every projection shape of the 7B and 70B models (batch 1): distinct weight
@@ -668,7 +724,9 @@ def main():
                      "frac_of_peak": step_bytes / (ms / args.steps) / 1e6 / (peak * tp),
                      "note": "aggregate over the N GPUs; the fraction is of N x the measured per-GPU peak"},
     }
-    if not args.no_cpu_baseline and tp == 1:                 # reported at N=1 only
+    if tp == 1:                                              # reported at N=1 only
+        out["prefill_gemm"] = time_prefill_gemm(pkg)         # the tensor-bound half of the path: the prefill dequant-GEMM
+    if not args.no_cpu_baseline and tp == 1:
         out["cpu_baseline"] = cpu_baseline(pkg, cfg, context, B)
     print(json.dumps(out))
 

@@ -24,6 +24,11 @@
 
 #include "attention_device.cuh"
 
+namespace greta {
+int attn_mma_decode(cudaStream_t stream, const AttnParams &p, uint32_t batch, uint32_t nsplit, uint32_t ng, uint32_t Dh);  // attention_mma.cu
+int attn_mma_prefill(cudaStream_t stream, const AttnParams &p, uint32_t S, uint32_t pos0, uint32_t Dh);
+}  // namespace greta
+
 namespace {
 
 constexpr int ATT_WARPS = 4;
@@ -396,6 +401,7 @@ int greta_cuda_attn_decode_batch(greta_stream_t stream, const float *q, const vo
     p.q = q; p.kc = kc; p.vc = vc; p.o = o; p.d_pos = d_pos; p.H = H; p.Hkv = Hkv; p.max_seq = max_seq; p.scale = scale;
     p.seq_stride = (size_t)Hkv * max_seq * Dh;
     p.pos_stride = 1;
+    if (tuning().attn_mma) return attn_mma_decode((cudaStream_t)stream, p, M, nsplit, ng, Dh);  // tensor cores: the group's heads are the rows
     return Dh == 128 ? launch_attn_gqa<16>((cudaStream_t)stream, p, M, nsplit, ng) : launch_attn_gqa<8>((cudaStream_t)stream, p, M, nsplit, ng);
   }
   return attn_decode_impl<__half>(stream, q, kc, vc, o, d_pos, 0, H, Hkv, Dh, max_seq, scale, scratch, scratch_bytes, false, M);
@@ -453,6 +459,10 @@ int greta_cuda_attn_prefill(greta_stream_t stream, const float *q, const void *k
   AttnParams p{};
   p.q = q; p.kc = kc; p.vc = vc; p.o = o; p.d_pos = nullptr; p.len0 = pos0 + 1;
   p.H = H; p.Hkv = Hkv; p.max_seq = max_seq; p.scale = scale; p.splits = 1; p.len_step = 1;
+  // Prompts run on the tensor cores (16 positions of a head per warp, K / V tiles staged once per 64 positions); a few
+  // positions, or the switch off, take one CTA per (position, head) on the decode inner loop.
+  if (tuning().attn_mma && S >= 8 && (Dh == 64 || Dh == 128) && aligned16(q) && aligned16(kc) && aligned16(vc) && aligned16(o))
+    return attn_mma_prefill((cudaStream_t)stream, p, S, pos0, Dh);
   return launch_attn<__half>((cudaStream_t)stream, p, S, Dh);
 }
 

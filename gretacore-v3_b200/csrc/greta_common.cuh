@@ -56,6 +56,7 @@ struct Tuning {
   long long gemv_r2_cells;   // GRETA_GEMV_R2_CELLS: below this many 4-row cells a GEMV uses 2-row cells; < 0 = automatic
   int step_stages;           // GRETA_STEP_STAGES: ring depth cap of the persistent decode-step kernel, 0 = automatic
   unsigned peer_poll_limit;  // GRETA_PEER_POLL_LIMIT: polls a consumer spends on one missing partial before it gives up
+  int attn_mma;              // GRETA_ATTN_MMA: 1 = prefill and grouped-query batched decode attention on the tensor cores
   int peer_two_level_min_tp; // GRETA_PEER_TWO_LEVEL_MIN_TP: ranks from which an exchange consumer gathers in two levels (see gemv_device.cuh)
   int skinny_max_rows;       // GRETA_SKINNY_MAX_ROWS: activation rows up to which the weights-read-once batched GEMV is used
 };

@@ -67,6 +67,8 @@ Tuning &tuning() {
     v.step_stages = e ? atoi(e) : 0;
     e = getenv("GRETA_PEER_POLL_LIMIT");
     v.peer_poll_limit = e ? (unsigned)strtoul(e, nullptr, 10) : (1u << 22);
+    e = getenv("GRETA_ATTN_MMA");
+    v.attn_mma = (e && e[0] == '0') ? 0 : 1;
     e = getenv("GRETA_PEER_TWO_LEVEL_MIN_TP");
     v.peer_two_level_min_tp = e ? atoi(e) : 4;
     e = getenv("GRETA_SKINNY_MAX_ROWS");
@@ -118,6 +120,8 @@ int greta_cuda_set_tuning(const char *name, long long value) {
   } else if (!strcmp(name, "peer_poll_limit")) {
     GRETA_REQUIRE(value >= 1 && value <= (1ll << 30), "set_tuning: peer_poll_limit=%lld outside 1..2^30", value);
     t.peer_poll_limit = (unsigned)value;
+  } else if (!strcmp(name, "attn_mma")) {
+    t.attn_mma = value != 0;
   } else if (!strcmp(name, "peer_two_level_min_tp")) {
     t.peer_two_level_min_tp = (int)value;
   } else if (!strcmp(name, "skinny_max_rows")) {

@@ -117,7 +117,8 @@ GRETA_API int greta_cuda_set_pdl(int on);
  *   cluster or through scratch), "gemm_tile" (GRETA_GEMM_TILE=<tokens>x<row tiles>; value = tokens * 10 + row
  *   tiles, 0 = automatic), "gemv_r2_cells" (GRETA_GEMV_R2_CELLS, < 0 = automatic), "step_stages"
  *   (GRETA_STEP_STAGES, 0 = automatic), "peer_poll_limit" (GRETA_PEER_POLL_LIMIT: polls a tensor-parallel
- *   consumer spends on one missing partial before it gives up, default 2^22), "peer_two_level_min_tp"
+ *   consumer spends on one missing partial before it gives up, default 2^22), "attn_mma" (GRETA_ATTN_MMA, 0/1: prefill and grouped-query batched decode
+ *   attention on the tensor cores), "peer_two_level_min_tp"
  *   (GRETA_PEER_TWO_LEVEL_MIN_TP: ranks from which an exchange consumer gathers in two levels, default 4), "skinny_max_rows"
  *   (GRETA_SKINNY_MAX_ROWS, 1..32). */
 GRETA_API int greta_cuda_set_tuning(const char *name, long long value);

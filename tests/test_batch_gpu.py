@@ -189,11 +189,13 @@ def test_fused_ffn_front_batch(g, name, M, D, F, prepared):
         assert max_abs_rel(got[m], want[m]) < TIGHT, m
 
 
-@pytest.mark.parametrize("M,H,Hkv,Dh,max_seq", [(3, 4, 4, 128, 80), (16, 8, 2, 64, 300), (5, 64, 8, 128, 1100), (16, 8, 1, 128, 700)])
-def test_attn_decode_batch(g, M, H, Hkv, Dh, max_seq):
+@pytest.mark.parametrize("mma", [1, 0])
+@pytest.mark.parametrize("M,H,Hkv,Dh,max_seq", [(3, 4, 4, 128, 80), (16, 8, 2, 64, 300), (5, 64, 8, 128, 1100), (16, 8, 1, 128, 700), (4, 32, 2, 128, 200)])
+def test_attn_decode_batch(g, M, H, Hkv, Dh, max_seq, mma):
     """Sequences of different lengths (one key up to the whole cache) in one launch; grouped-query shapes take the kernel
     that stages each KV head once for its query heads, the 4/4 shape the per-head kernels."""
     lib = g.cuda()
+    g.check(lib.greta_cuda_set_tuning(b"attn_mma", mma))     # grouped-query shapes: tensor-core kernel, or the CUDA-core one
     rng = np.random.default_rng(70 + M + H)
     q = rng.normal(0, 1, (M, H * Dh)).astype(np.float32)
     kc = rng.normal(0, 1, (M, Hkv, max_seq, Dh)).astype(np.float16).view(np.uint16)
@@ -214,6 +216,7 @@ def test_attn_decode_batch(g, M, H, Hkv, Dh, max_seq):
         for m in range(M):
             want = O.attention_decode(q[m], kc[m], vc[m], H, Hkv, Dh, int(pos[m]) + 1, max_seq, scale)
             assert max_abs_rel(got[m], want) < 1e-5, m
+    g.check(lib.greta_cuda_set_tuning(b"attn_mma", 1))
 
 
 def test_argmax_advance_batch(g):

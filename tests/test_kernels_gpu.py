@@ -483,6 +483,32 @@ def test_attn_prefill_causal(g):
     assert max_abs_rel(o.download(np.float32).reshape(S, H * Dh), want) < 1e-5
 
 
+@pytest.mark.parametrize("mma", [1, 0])
+@pytest.mark.parametrize("S,pos0,H,Hkv,Dh", [(512, 0, 8, 8, 128), (200, 313, 8, 2, 128), (65, 1, 4, 1, 64), (9, 0, 2, 2, 64)])
+def test_attn_prefill_on_tensor_cores_and_on_the_scalar_loop(g, tuning, mma, S, pos0, H, Hkv, Dh):
+    """Causal prefill attention of a chunk that starts at pos0 (its queries also see the cache rows of earlier chunks), on
+    the tensor-core kernel and on the per-(position, head) loop: every query against the oracle's decode attention over the
+    keys 0 .. pos0 + s."""
+    tuning("attn_mma", mma, restore=1)
+    rng = np.random.default_rng(43 + S)
+    max_seq = pos0 + S + 7
+    q = rng.normal(0, 1, (S, H * Dh)).astype(np.float32)
+    kc = np.zeros((Hkv, max_seq, Dh), np.float16)
+    vc = np.zeros((Hkv, max_seq, Dh), np.float16)
+    kc[:, :pos0 + S] = rng.normal(0, 1, (Hkv, pos0 + S, Dh)).astype(np.float16)
+    vc[:, :pos0 + S] = rng.normal(0, 1, (Hkv, pos0 + S, Dh)).astype(np.float16)
+    kc[:, pos0 + S:] = np.float16(100.0)      # rows past the chunk must never be read
+    scale = float(1.0 / np.sqrt(Dh))
+    o = _nan_buffer(g, S * H * Dh)
+    g.check(g.cuda().greta_cuda_attn_prefill(None, _dev(g, q).ptr, _dev(g, kc.view(np.uint16)).ptr, _dev(g, vc.view(np.uint16)).ptr, o.ptr, S, pos0, H,
+                                             Hkv, Dh, max_seq, scale))
+    got = o.download(np.float32).reshape(S, H * Dh)
+    assert np.isfinite(got).all()
+    for s_i in sorted({0, 1, 7, 8, 15, 16, 63, 64, S // 2, S - 2, S - 1} & set(range(S))):
+        want = O.attention_decode(q[s_i], kc.view(np.uint16), vc.view(np.uint16), H, Hkv, Dh, pos0 + s_i + 1, max_seq, scale)
+        assert max_abs_rel(got[s_i], want) < 1e-5, s_i
+
+
 @pytest.mark.parametrize("use_dpos", [False, True])
 def test_rope_matches_oracle(g, use_dpos):
     rng = np.random.default_rng(43)
