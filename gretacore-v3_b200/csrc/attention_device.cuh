@@ -38,6 +38,10 @@ __device__ __forceinline__ void load_row(const KV *p, float (&f)[DPL]) {
   }
 }
 
+}  // namespace
+
+namespace greta {
+// Shared by every attention kernel of the library (one definition across the translation units).
 struct AttnParams {
   const float *q;        // [nq][H][Dh]
   const void *kc, *vc;   // [Hkv][max_seq][Dh]
@@ -58,6 +62,10 @@ struct AttnParams {
   uint32_t *counters;    // [H] zero on entry, left zero
   float *partial;        // [H][splits][Dh + 2]
 };
+}  // namespace greta
+
+namespace {
+
 
 // Merge (m2, l2, o2) into (m, l, o).
 template <int DPL>
