@@ -169,6 +169,14 @@ __device__ __forceinline__ void issue_tile(uint8_t *stage, const uint8_t *kg, co
       const uint32_t dst = (uint32_t)__cvta_generic_to_shared(slot + is_v * (MMA_TK * ROWP) + row * ROWP + cc * 16);
       asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
     }
+    // A last group of 16 keys that is only partly there is still multiplied as a whole (its surplus scores are masked):
+    // its surplus rows must hold numbers, not whatever the memory held (0 x NaN is NaN).  The stores become visible with
+    // the barrier that also publishes the copies.
+    const uint32_t pad_rows = ((nk + 15) & ~15u) - nk;
+    for (uint32_t piece = tid; piece < pad_rows * 2 * PPK; piece += nthreads) {
+      const uint32_t row = nk + piece / (2 * PPK), c = piece % (2 * PPK), is_v = c / PPK, cc = c % PPK;
+      *reinterpret_cast<uint4 *>(slot + is_v * (MMA_TK * ROWP) + row * ROWP + cc * 16) = make_uint4(0, 0, 0, 0);
+    }
   }
   asm volatile("cp.async.commit_group;" ::: "memory");
 }

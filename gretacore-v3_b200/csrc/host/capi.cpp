@@ -26,6 +26,8 @@ inline GretaDataType dtype(int fmt) {
 }
 }  // namespace
 
+#define M(m) static_cast<Model *>(m)
+
 extern "C" {
 
 const char *greta_host_last_error(void) { return g_err.c_str(); }
@@ -64,6 +66,42 @@ int greta_host_tensor_shard(const greta_model_config *c, int which, uint32_t *ou
   return 0;
 }
 
+// GGUFLoader::open + get_config + list_tensors, without a device: the parsed shape (and how many tensors the file holds).
+int greta_host_gguf_info(const char *path, greta_model_config *cfg, uint32_t *n_tensors) {
+  std::string err;
+  GGUFLoader ld;
+  if (!path || !ld.open(path, &err)) return done(false, err.empty() ? "gguf_info: null path" : err);
+  const ModelConfig k = ld.get_config();
+  if (cfg) {
+    cfg->dim = k.dim; cfg->num_heads = k.num_heads; cfg->num_heads_kv = k.num_heads_kv; cfg->num_layers = k.num_layers;
+    cfg->vocab_size = k.vocab_size; cfg->hidden_dim = k.hidden_dim; cfg->head_dim = k.head_dim; cfg->max_seq_len = k.max_seq_len;
+    cfg->rope_base = k.rope_base; cfg->rms_eps = k.rms_eps;
+    cfg->weight_fmt = k.weight_type == GretaDataType::Q8_0 ? GRETA_FMT_Q8_0 : GRETA_FMT_Q4_0;
+    cfg->lm_head_fmt = k.lm_head_type == GretaDataType::Q4_0 ? GRETA_FMT_Q4_0 : k.lm_head_type == GretaDataType::Q8_0 ? GRETA_FMT_Q8_0 : GRETA_FMT_F16;
+    cfg->tp_rank = 0; cfg->tp_size = 1;
+  }
+  if (n_tensors) *n_tensors = (uint32_t)ld.list_tensors().size();
+  return 0;
+}
+// GGUFLoader::read_as_fp16: a tensor of the file decoded to fp16 bits in host memory (no device).
+int greta_host_gguf_read_fp16(const char *path, const char *name, void *out_f16, size_t capacity_elems, size_t *elems) {
+  std::string err;
+  GGUFLoader ld;
+  if (!path || !name || !ld.open(path, &err)) return done(false, err.empty() ? "gguf_read_fp16: null argument" : err);
+  std::vector<uint16_t> v;
+  if (!ld.read_as_fp16(name, &v, &err)) return done(false, err);
+  if (elems) *elems = v.size();
+  if (out_f16 && v.size() <= capacity_elems) std::memcpy(out_f16, v.data(), v.size() * 2);
+  return 0;
+}
+// BlockScheduler::load_weights(GGUFLoader): the model must have been created with the file's shape and storage types.
+int greta_model_load_gguf(greta_model_t m, const char *path) {
+  std::string err;
+  GGUFLoader ld;
+  if (!path || !ld.open(path, &err)) return done(false, err.empty() ? "load_gguf: null path" : err);
+  return done(M(m)->sched.load_weights(ld, &err), err);
+}
+
 int greta_model_create(const greta_model_config *c, greta_model_t *out) { return greta_model_create_batch(c, 1, out); }
 
 int greta_model_create_batch(const greta_model_config *c, uint32_t batch, greta_model_t *out) {
@@ -86,7 +124,6 @@ int greta_model_destroy(greta_model_t m) {
   delete static_cast<Model *>(m);
   return 0;
 }
-#define M(m) static_cast<Model *>(m)
 int greta_model_load_synthetic(greta_model_t m, uint64_t seed) {
   std::string err;
   return done(M(m)->sched.load_synthetic_weights(seed, &err), err);

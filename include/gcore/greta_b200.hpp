@@ -401,6 +401,53 @@ struct TensorShard {
 };
 TensorShard tensor_shard(const ModelConfig &config, LayerTensor which);
 
+// Weight files.  The reference's interface (weight_loader.hpp:14-92); GGUF is the format read here.
+struct TensorInfo {
+  std::string name;
+  std::vector<size_t> shape;  // outermost first
+  size_t offset = 0;          // inside the file's data section
+  size_t size_bytes = 0;      // 0 for storage types this path does not read
+  std::string dtype;          // "F32", "F16", "Q4_0", "Q8_0", ...
+};
+
+class WeightLoader {
+public:
+  virtual ~WeightLoader() = default;
+  virtual bool open(const std::string &path, std::string *err) = 0;
+  virtual std::vector<TensorInfo> list_tensors() const = 0;
+  virtual bool load_tensor(const std::string &name, gcore::rt::cuda::Buffer &buffer, std::string *err) = 0;        // F32 / F16 -> fp32
+  virtual bool load_tensor_fp16(const std::string &name, gcore::rt::cuda::Buffer &buffer, std::string *err) = 0;   // any readable type -> fp16
+  // The reference's host-side re-quantisers; not carried over (GGUF blocks are stored as they are): they fail with a message.
+  virtual bool load_tensor_int8(const std::string &name, gcore::rt::cuda::Buffer &buffer, gcore::rt::cuda::Buffer &scales, std::string *err) = 0;
+  virtual bool load_tensor_int4(const std::string &name, gcore::rt::cuda::Buffer &buffer, gcore::rt::cuda::Buffer &scales,
+                                gcore::rt::cuda::Buffer &head_scales, std::string *err) = 0;
+  virtual ModelConfig get_config() const = 0;
+};
+
+class GGUFLoader : public WeightLoader {
+public:
+  GGUFLoader();
+  ~GGUFLoader() override;
+  bool open(const std::string &path, std::string *err) override;
+  std::vector<TensorInfo> list_tensors() const override;
+  bool load_tensor(const std::string &name, gcore::rt::cuda::Buffer &buffer, std::string *err) override;
+  bool load_tensor_fp16(const std::string &name, gcore::rt::cuda::Buffer &buffer, std::string *err) override;
+  bool load_tensor_int8(const std::string &name, gcore::rt::cuda::Buffer &buffer, gcore::rt::cuda::Buffer &scales, std::string *err) override;
+  bool load_tensor_int4(const std::string &name, gcore::rt::cuda::Buffer &buffer, gcore::rt::cuda::Buffer &scales,
+                        gcore::rt::cuda::Buffer &head_scales, std::string *err) override;
+  // Shape from the file's metadata; weight_type / lm_head_type from the storage types of blk.0.attn_q.weight and output.weight.
+  ModelConfig get_config() const override;
+  // B200 build: the tensor's bytes as they lie in the (memory-mapped) file, and a tensor decoded to fp16 on the host.
+  bool tensor_data(const std::string &name, const void **data, size_t *bytes, std::string *dtype, std::string *err) const;
+  bool read_as_fp16(const std::string &name, std::vector<uint16_t> *out, std::string *err) const;
+
+private:
+  struct Impl;
+  std::unique_ptr<Impl> impl_;
+};
+
+std::unique_ptr<WeightLoader> create_weight_loader(const std::string &path, std::string *err);
+
 struct BlockBuffers {
   gcore::rt::cuda::Buffer wq, wk, wv, wo, w1, w2, w3;            // qs planes (w1 gate, w2 down, w3 up)
   gcore::rt::cuda::Buffer s_wq, s_wk, s_wv, s_wo, s_w1, s_w2, s_w3;  // d planes
@@ -427,6 +474,9 @@ public:
   bool allocate_activations(size_t batch_size, size_t max_seq_len, std::string *err);
   // Seeded random weights of the configured shape (GGUF blocks generated on the host, uploaded, repacked on the device).
   bool load_synthetic_weights(uint64_t seed, std::string *err);
+  // From a GGUF file whose projections are stored as Q4_0 or Q8_0 (block_scheduler.hpp:83 in the reference): the blocks go
+  // to the device as they lie in the file; under tensor parallelism every rank keeps its shard.
+  bool load_weights(WeightLoader &loader, std::string *err);
   // One tensor from host memory: GGUF blocks for the projections, fp32 for the norms, fp16 for embedding / LM head.
   bool set_layer_tensor(size_t layer, LayerTensor which, const void *host, size_t bytes, std::string *err);
   bool set_global_tensor(GlobalTensor which, const void *host, size_t bytes, std::string *err);

@@ -47,6 +47,13 @@ GRETA_API uint64_t greta_host_tensor_stream(uint32_t layer, int which);
  * projection `which` (LayerTensor 0..6) that rank cfg->tp_rank holds.  Needs no device. */
 GRETA_API int greta_host_tensor_shard(const greta_model_config *cfg, int which, uint32_t *out6);
 
+/* GGUF files (gcore::inference::GGUFLoader; the reference's parser is src/inference/src/weight_loader.cpp:210-505).
+ * greta_host_gguf_info: open + get_config + list_tensors - the model shape and storage types the file declares, no device
+ * needed.  greta_host_gguf_read_fp16: one tensor (F16, F32, Q4_0 or Q8_0) decoded to fp16 bits on the host; *elems receives
+ * its element count (out_f16 may be NULL to ask for the size). */
+GRETA_API int greta_host_gguf_info(const char *path, greta_model_config *cfg, uint32_t *n_tensors);
+GRETA_API int greta_host_gguf_read_fp16(const char *path, const char *name, void *out_f16, size_t capacity_elems, size_t *elems);
+
 /* BlockScheduler::init + allocate_weights + allocate_activations(1, max_seq_len). */
 GRETA_API int greta_model_create(const greta_model_config *cfg, greta_model_t *out);
 /* The same with allocate_activations(batch, max_seq_len): `batch` sequences (1..32) that decode in step, each with its own
@@ -54,6 +61,9 @@ GRETA_API int greta_model_create(const greta_model_config *cfg, greta_model_t *o
 GRETA_API int greta_model_create_batch(const greta_model_config *cfg, uint32_t batch, greta_model_t *out);
 GRETA_API int greta_model_destroy(greta_model_t m);
 GRETA_API int greta_model_load_synthetic(greta_model_t m, uint64_t seed);                 /* load_synthetic_weights */
+/* BlockScheduler::load_weights from a GGUF file whose projections are stored as Q4_0 / Q8_0: blocks go to the device as
+ * they lie in the file (the model must have been created with the shape and formats greta_host_gguf_info reports). */
+GRETA_API int greta_model_load_gguf(greta_model_t m, const char *path);
 /* set_layer_tensor / set_global_tensor: `which` is a LayerTensor / GlobalTensor value; host points at the GLOBAL tensor. */
 GRETA_API int greta_model_set_layer_tensor(greta_model_t m, uint32_t layer, int which, const void *host, size_t bytes);
 GRETA_API int greta_model_set_global_tensor(greta_model_t m, int which, const void *host, size_t bytes);

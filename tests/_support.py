@@ -1,5 +1,6 @@
 """Shared helpers of the test-suite: package loading, seeded GGUF block makers, error metric."""
 import os
+import struct
 import sys
 
 import numpy as np
@@ -44,3 +45,29 @@ def max_abs_rel(got, want):
     want = np.asarray(want, np.float64)
     denom = np.abs(want).max()
     return float(np.abs(got - want).max() / (denom if denom > 0 else 1.0))
+
+
+def _s(b):
+    return struct.pack("<Q", len(b)) + b
+
+
+def write_gguf(path, kv_u32, kv_f32, tensors):
+    """Minimal GGUF v3 writer: u32 / f32 metadata and raw tensors (name, dims, ggml type, bytes).
+    dims are given outermost-first and stored innermost-first as GGUF does."""
+    out = bytearray(b"GGUF" + struct.pack("<IQQ", 3, len(tensors), len(kv_u32) + len(kv_f32)))
+    for k, v in kv_u32:
+        out += _s(k.encode()) + struct.pack("<II", 4, v)
+    for k, v in kv_f32:
+        out += _s(k.encode()) + struct.pack("<If", 6, v)
+    off = 0
+    for name, dims, gtype, data in tensors:
+        out += _s(name.encode()) + struct.pack("<I", len(dims))
+        for d in reversed(dims):
+            out += struct.pack("<Q", d)
+        out += struct.pack("<IQ", gtype, off)
+        off += (len(data) + 31) // 32 * 32
+    out += b"\0" * ((-len(out)) % 32)
+    for _, _, _, data in tensors:
+        out += data + b"\0" * ((-len(data)) % 32)
+    with open(path, "wb") as f:
+        f.write(out)

@@ -18,35 +18,11 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
 from oracle import oracle  # noqa: E402
+from _support import write_gguf  # noqa: E402
 
 GGML_F32, GGML_Q8_0 = 0, 8
-
-
-def _s(b):
-    return struct.pack("<Q", len(b)) + b
-
-
-def write_gguf(path, kv_u32, kv_f32, tensors):
-    """Minimal GGUF v3 writer: u32 / f32 metadata and raw tensors (name, dims, ggml type, bytes).
-    dims are given outermost-first and stored innermost-first as GGUF does."""
-    out = bytearray(b"GGUF" + struct.pack("<IQQ", 3, len(tensors), len(kv_u32) + len(kv_f32)))
-    for k, v in kv_u32:
-        out += _s(k.encode()) + struct.pack("<II", 4, v)
-    for k, v in kv_f32:
-        out += _s(k.encode()) + struct.pack("<If", 6, v)
-    off = 0
-    for name, dims, gtype, data in tensors:
-        out += _s(name.encode()) + struct.pack("<I", len(dims))
-        for d in reversed(dims):
-            out += struct.pack("<Q", d)
-        out += struct.pack("<IQ", gtype, off)
-        off += (len(data) + 31) // 32 * 32
-    out += b"\0" * ((-len(out)) % 32)
-    for _, _, _, data in tensors:
-        out += data + b"\0" * ((-len(data)) % 32)
-    with open(path, "wb") as f:
-        f.write(out)
 
 
 def q8_0_blocks(rng, n_blocks, sigma=0.02):
