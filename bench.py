@@ -530,6 +530,13 @@ def run_case(pkg, name):
         c = g.DeviceBuffer(M * N * 2)
         for i in range(6):
             g.check(lib.greta_cuda_gemm(None, g.FMT_Q4_0, a.ptr, 1, w[i][0].ptr, w[i][1].ptr, c.ptr, 1, M, N, K, None))
+    elif name == "gemm_small":       # a prefill chunk of 128 tokens: 128 x 4096 -> 11008, fp16 in / out (dequantisation-bound)
+        M, N, K = 128, 11008, 4096
+        w = planes(N, K, 6)
+        a = g.DeviceBuffer.from_numpy(rng.normal(0, 1, (M, K)).astype(np.float16).view(np.uint16))
+        c = g.DeviceBuffer(M * N * 2)
+        for i in range(6):
+            g.check(lib.greta_cuda_gemm(None, g.FMT_Q4_0, a.ptr, 1, w[i][0].ptr, w[i][1].ptr, c.ptr, 1, M, N, K, None))
     elif name == "attn_decode":      # 32 heads x 128, 2049 keys, fp16 cache, 6 distinct caches (201 MB)
         H, Dh, L, S = 32, 128, 2049, 2304
         kv = rng.normal(0, 1, H * S * Dh).astype(np.float16).view(np.uint16)
@@ -594,7 +601,7 @@ def main():
                          "workload; --prompt-len 4096 --steps 256 for its full size); c5-batch1: the 70B shape at batch 1")
     ap.add_argument("--exchange", choices=["fused", "nccl"], default="fused",
                     help="tensor-parallel exchange of the decode step: fused into the GEMV kernels over peer memory, or NCCL all-reduce")
-    ap.add_argument("--case", default=None, help="run a small single-kernel case (gemv_swiglu, gemv_plain, gemm_c2, attn_decode, decode_step) and exit; "
+    ap.add_argument("--case", default=None, help="run a small single-kernel case (gemv_swiglu, gemv_plain, gemm_c2, gemm_small, attn_decode, decode_step, gemv_batch, attn_batch) and exit; "
                          "gemv_shapes prints the GEMV bandwidth of every projection shape")
     args = ap.parse_args()
     pkg = load_pkg()

@@ -48,6 +48,13 @@ __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// Arrival on a barrier of the pair's even CTA.  CTA-scope release on purpose: what the arrival publishes are this
+// thread's shared-memory stores, already fenced towards the async proxy, and the tensor core of this SM is what reads
+// them; a cluster-scope release would also wait for the thread's outstanding cp.async prefetches (about one DRAM
+// latency per stage: measured, it doubled the kernel's time).
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
@@ -69,12 +76,12 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volat
   const long long t0 = clock64();
   for (;;) {
     uint32_t ok;
-    asm volatile(
+    asm volatile(  // with a time hint the thread sleeps in hardware until the phase completes instead of spinning through issue slots
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(20000u)
         : "memory");
     if (ok) return true;
     if (*abort_flag) return false;
@@ -208,6 +215,7 @@ struct Cfg {
   static constexpr int AU = RT == 2 ? (TN == 256 ? (Q4 ? 4 : 3) : 6) : (TN == 128 ? 6 : (TN == 512 && Q4 ? 5 : 4));
   static constexpr int BS = RT == 2 ? (TN == 256 || !Q4 ? 2 : 3) : ((TN == 256 && !Q4) || TN == 512 ? 3 : 4);
   static constexpr int RS = RT == 2 ? 3 : (TN == 512 ? 3 : (TN == 256 ? (Q4 ? 6 : 4) : (Q4 ? 8 : 6)));
+  static constexpr int U = (RT == 1 && TN <= 256 && BS >= 3 && RS >= 4) ? 2 : 1;  // stages per pass of the dequant loop
   static constexpr int NBARS = 2 * AU + 2 * BS + 1;
   static constexpr size_t SMEM = (size_t)AU * UNIT_BYTES + (size_t)BS * B_STAGE + (size_t)RS * RAW_STAGE + 1024 + 256;
   static_assert(RT * TN <= 512, "accumulators exceed tensor memory");
@@ -274,6 +282,81 @@ __device__ __forceinline__ void dequant_block(const uint8_t *stage, int row, int
   }
 }
 
+// The dequant warps' share of the K loop, common to the one-CTA and the two-CTA kernel.  Stages 0 .. RS-1 of
+// the raw ring have been requested, one commit group each.  A pass of the loop takes U consecutive stages: the
+// dependent chain of one stage (shared-memory load -> half2 math -> wait for the slot -> stores -> proxy fence ->
+// arrival) is about 950 cycles at 128 tokens, several times its issue time, and every warp works on every stage,
+// so one stage per pass makes that chain the stage period whenever the token tile is short; U stages per pass
+// interleave U chains and share the fence.  U <= BS and U <= RS.
+// b_full_remote0 != 0: arrivals go to the barrier array at that cluster-window address (the pair's even CTA).
+template <class C, int U>
+__device__ __forceinline__ bool dequant_stages(uint8_t *raw, uint8_t *b_tiles, uint64_t *b_empty, uint64_t *b_full, uint32_t b_full_remote0, int row,
+                                               int hb, uint32_t row_off, const uint8_t *qs_row, const __half *d_row, uint32_t KT, uint32_t nb,
+                                               volatile int *abort_flag, int lane) {
+  constexpr int BS = C::BS, RS = C::RS, RAW_STAGE = C::RAW_STAGE, B_STAGE = C::B_STAGE;
+  static_assert(U >= 1 && U <= BS && U <= RS, "stages per pass");
+  bool ok = true;
+  uint32_t s = 0, sph = 1, rs_use = 0;  // a fresh barrier passes a wait on parity 1
+  for (uint32_t kt = 0; kt < KT; kt += U) {
+    cp_async_wait<RS - U>();  // this thread's shares of stages kt .. kt+U-1 have landed (it reads only what it copied)
+    uint4 chunk[U][4];
+    uint32_t slot[U], par[U];
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+      uint32_t r = rs_use + j;
+      if (r >= (uint32_t)RS) r -= RS;
+      slot[j] = s + j;
+      par[j] = sph;
+      if (slot[j] >= (uint32_t)BS) {
+        slot[j] -= BS;
+        par[j] ^= 1;
+      }
+      if (kt + j < KT) dequant_block<C>(raw + r * RAW_STAGE, row, hb, 2 * (kt + j) + hb < nb, chunk[j]);  // the math does not wait for the slot
+    }
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+      if (kt + j < KT && ok) {
+        ok = mbar_wait(&b_empty[slot[j]], par[j], abort_flag, 400 + slot[j]);
+        if (ok) {
+          uint8_t *row_base = b_tiles + slot[j] * B_STAGE + row_off;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4 *>(row_base + (((4 * hb + c) ^ (row & 7)) << 4)) = chunk[j][c];
+        }
+      }
+    }
+    if (!ok) break;
+    fence_proxy_async();  // make the generic-proxy stores visible to the tensor core's reads
+    __syncwarp();
+    if (lane == 0) {
+#pragma unroll
+      for (int j = 0; j < U; ++j) {
+        if (kt + j < KT) {
+          if (b_full_remote0)
+            mbar_arrive_remote(b_full_remote0 + slot[j] * 8);
+          else
+            mbar_arrive(&b_full[slot[j]]);
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < U; ++j) {  // refill the raw slots just read
+      uint32_t r = rs_use + j;
+      if (r >= (uint32_t)RS) r -= RS;
+      if (kt + j + RS < KT) raw_issue<C>(raw + r * RAW_STAGE, row, hb, qs_row, d_row, kt + j + RS, nb);
+      cp_async_commit();
+    }
+    s += U;
+    if (s >= (uint32_t)BS) {
+      s -= BS;
+      sph ^= 1;
+    }
+    rs_use += U;
+    if (rs_use >= (uint32_t)RS) rs_use -= RS;
+  }
+  cp_async_wait<0>();
+  return ok;
+}
+
 template <int FMT, int TN, int RT, bool OUT_F16>
 __global__ void __launch_bounds__(Cfg<FMT, TN, RT>::THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t *__restrict__ qs, const __half *__restrict__ dsc, void *__restrict__ Cout,
@@ -328,7 +411,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t *__rest
   const __half *d_row = dsc + (size_t)n_row * d_row_stride(nb);
   if (warp >= 2) {
 #pragma unroll
-    for (int j = 0; j < RS - 1; ++j) {
+    for (int j = 0; j < RS; ++j) {
       if ((uint32_t)j < KT) raw_issue<C>(raw + j * RAW_STAGE, row, hb, qs_row, d_row, j, nb);
       cp_async_commit();
     }
@@ -404,30 +487,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t *__rest
     // ---------------- dequant warps, then epilogue ----------------
     // this thread's half (64 bytes) of its row in the swizzled tile of its 128-row group
     const uint32_t row_off = (row >> 7) * (TILE_N * BK * 2) + (row & 127) * 128;
-    bool ok = true;
-    uint32_t s = 0, sph = 1, rs_load = RS - 1, rs_use = 0;
-    for (uint32_t kt = 0; kt < KT; ++kt) {
-      if (kt + RS - 1 < KT) raw_issue<C>(raw + rs_load * RAW_STAGE, row, hb, qs_row, d_row, kt + RS - 1, nb);
-      cp_async_commit();
-      cp_async_wait<RS - 1>();  // this thread's share of stage kt has landed (it reads only what it copied)
-      uint4 chunk[4];
-      dequant_block<C>(raw + rs_use * RAW_STAGE, row, hb, 2 * kt + hb < nb, chunk);  // the math does not wait for the slot
-      ok = mbar_wait(&b_empty[s], sph, abort_flag, 400 + s);
-      if (!ok) break;
-      uint8_t *row_base = b_tiles + s * B_STAGE + row_off;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4 *>(row_base + (((4 * hb + c) ^ (row & 7)) << 4)) = chunk[c];
-      fence_proxy_async();  // make the generic-proxy stores visible to the tensor core's reads
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&b_full[s]);
-      if (++s == BS) {
-        s = 0;
-        sph ^= 1;
-      }
-      if (++rs_load == RS) rs_load = 0;
-      if (++rs_use == RS) rs_use = 0;
-    }
-    cp_async_wait<0>();
+    bool ok = dequant_stages<C, C::U>(raw, b_tiles, b_empty, b_full, 0u, row, hb, row_off, qs_row, d_row, KT, nb, abort_flag, lane);
     // epilogue: accumulator rows = weight rows (TMEM lanes), columns = tokens.  A warp may only touch TMEM
     // lanes 32 * (warp % 4) .. +31; the 2 * RT warps of a lane quadrant split row tiles and token halves.
     if (ok) ok = mbar_wait(acc_full, 0, abort_flag, 500);
@@ -484,6 +544,256 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t *__rest
   }
 }
 
+// ---- two-CTA form ------------------------------------------------------------------------------
+// A cluster of two CTAs owns 256 weight rows (128 each) and 256 * UPS tokens.  One tcgen05.mma with
+// cta_group::2 (M = 256, N = 256), issued by a thread of the even CTA, multiplies both CTAs' weight
+// tiles with a 256-token unit of which each CTA has staged 128 tokens: per 64-K stage a CTA writes, and
+// its tensor core reads, half the token bytes of the one-CTA form, whose pace shared-memory bandwidth
+// set.  Each CTA's accumulator (its 128 rows x all tokens) stays in its own tensor memory, so the
+// epilogue is the one-CTA one.  The "full" barriers that the issuing thread waits on live in the even
+// CTA: the odd CTA's TMA loads complete their bytes there and its dequant warps arrive there through
+// the cluster window.  The "empty" barriers and acc_full exist in both CTAs and one commit signals both.
+// No load is multicast; every mbarrier wait is bounded as in the one-CTA kernel, and both CTAs always
+// reach the closing cluster barrier, so neither leaves while the other may still address its memory.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+// TMA load of this CTA's half of a token unit; the bytes are counted on a barrier given by its address in
+// the cluster window (the even CTA's).
+__device__ __forceinline__ void tma_load_2d_pair(void *smem_dst, const CUtensorMap *map, int x, int y, uint32_t bar_cluster_addr) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(map), "r"(x), "r"(y), "r"(bar_cluster_addr)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t *smem_result, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint32_t desc_a_lo, uint32_t desc_b_lo, uint32_t desc_hi, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p;\n\t}" ::"r"(tmem_d),
+      "r"(desc_a_lo), "r"(desc_b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the barrier at this shared-memory offset in both CTAs of the pair once every MMA issued so far has completed.
+__device__ __forceinline__ void umma_commit_pair(uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(smem_u32(bar)),
+               "h"((uint16_t)3)
+               : "memory");
+}
+
+template <int FMT, int UPS_>
+struct PairCfg {
+  static constexpr int ROWS = TILE_N;  // weight rows per CTA
+  static constexpr int UPS = UPS_;     // 256-token units per stage
+  static constexpr int TN = 256 * UPS;
+  static constexpr int QV = (FMT == GRETA_FMT_Q4_0) ? 1 : 2;
+  static constexpr int DEQ_THREADS = 2 * ROWS;
+  static constexpr int THREADS = 64 + DEQ_THREADS;
+  static constexpr int RAW_SCALES = 2 * QV * ROWS * 16;
+  static constexpr int RAW_STAGE = RAW_SCALES + 2 * ROWS * 4;
+  static constexpr int B_STAGE = ROWS * BK * 2;
+  static constexpr int HALF_ROWS = 128;  // tokens of a unit that one CTA stages
+  static constexpr int HALF_BYTES = HALF_ROWS * BK * 2;
+  static constexpr bool Q4 = FMT == GRETA_FMT_Q4_0;
+  static constexpr int AU = Q4 ? 8 : 5;
+  static constexpr int BS = 4;
+  static constexpr int RS = 6;
+  static constexpr int U = 2;  // stages per pass of the dequant loop
+  static constexpr int NBARS = 2 * AU + 2 * BS + 1;
+  static constexpr size_t SMEM = (size_t)AU * HALF_BYTES + (size_t)BS * B_STAGE + (size_t)RS * RAW_STAGE + 1024 + 256;
+  static_assert((size_t)TN * ROWS * 2 <= (size_t)AU * HALF_BYTES + (size_t)BS * B_STAGE, "the fp16 output tile is staged in the idle rings");
+  static_assert(SMEM <= 232448, "tile configuration exceeds shared memory");
+};
+
+template <int FMT, int UPS, bool OUT_F16>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<FMT, UPS>::THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t *__restrict__ qs, const __half *__restrict__ dsc,
+                    void *__restrict__ Cout, uint32_t M, uint32_t N, uint32_t K) {
+  using C = PairCfg<FMT, UPS>;
+  constexpr int AU = C::AU, BS = C::BS, RS = C::RS, HALF_BYTES = C::HALF_BYTES;
+  constexpr int RAW_STAGE = C::RAW_STAGE, B_STAGE = C::B_STAGE, ROWS = C::ROWS, TN = C::TN, COLS = C::TN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t *a_units = smem;                       // [AU][128 tokens][128 B]   this CTA's half of each token unit (MMA operand B)
+  uint8_t *b_tiles = a_units + AU * HALF_BYTES;  // [BS][128 rows][128 B]     this CTA's weights (MMA operand A)
+  uint8_t *raw = b_tiles + BS * B_STAGE;         // [RS] raw quantised stages
+  uint64_t *bars = reinterpret_cast<uint64_t *>(raw + RS * RAW_STAGE);
+  uint64_t *a_full = bars, *a_empty = bars + AU, *b_full = bars + 2 * AU, *b_empty = bars + 2 * AU + BS, *acc_full = bars + 2 * AU + 2 * BS;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + C::NBARS);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0: the CTA whose thread issues the MMAs and whose "full" barriers are used
+  const uint32_t n0 = blockIdx.x * ROWS, m0 = blockIdx.y * TN;
+  const uint32_t KT = (K + BK - 1) / BK, nb = K / 32;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < AU; ++s) {
+      mbar_init(&a_full[s], 1);
+      mbar_init(&a_empty[s], 1);
+    }
+    for (int s = 0; s < BS; ++s) {
+      mbar_init(&b_full[s], 2 * (C::DEQ_THREADS / 32));  // the dequant warps of both CTAs
+      mbar_init(&b_empty[s], 1);
+    }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
+  }
+  if (warp == 1) {  // the same warp of both CTAs
+    tmem_alloc_pair(tmem_slot, COLS);
+    tmem_relinquish_pair();
+  }
+  const int t = (int)threadIdx.x - 64;
+  const int row = t >= 0 ? t % ROWS : 0, hb = t >= 0 ? t / ROWS : 0;
+  const uint32_t n_row = min(n0 + (uint32_t)row, N - 1);  // a CTA past the last row tile re-reads the last row and stores nothing
+  const uint8_t *qs_row = qs + (size_t)n_row * nb * (C::Q4 ? 16 : 32);
+  const __half *d_row = dsc + (size_t)n_row * d_row_stride(nb);
+  if (warp >= 2) {
+#pragma unroll
+    for (int j = 0; j < RS; ++j) {
+      if ((uint32_t)j < KT) raw_issue<C>(raw + j * RAW_STAGE, row, hb, qs_row, d_row, j, nb);
+      cp_async_commit();
+    }
+  }
+  tc_fence_before();
+  cluster_sync_all();  // barriers of both CTAs exist before anything arrives on them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs: tokens rank * 128 .. + 127 of every unit) ----------------
+    if (lane == 0) {
+      const uint32_t full0 = map_to_cta(smem_u32(a_full), 0);
+      uint32_t u = 0, ph = 1;  // a fresh barrier passes a wait on parity 1: the first round needs no release
+      for (uint32_t g = 0; g < KT * UPS; ++g) {
+        if (!mbar_wait(&a_empty[u], ph, abort_flag, 100 + u)) break;
+        if (rank == 0) mbar_arrive_expect_tx(&a_full[u], 2 * HALF_BYTES);
+        tma_load_2d_pair(a_units + u * HALF_BYTES, &tmap_a, (int)((g / UPS) * BK), (int)(m0 + (g % UPS) * 256 + rank * C::HALF_ROWS), full0 + u * 8);
+        if (++u == AU) {
+          u = 0;
+          ph ^= 1;
+        }
+      }
+      if (*abort_flag) {  // copies may still be in flight: leave them time to land before the closing barrier
+        const long long t0 = clock64();
+        while (clock64() - t0 < 20000000ll) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (even CTA only) ----------------
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = instr_desc_f16(2 * TILE_N, 256);
+      const uint32_t w_lo0 = smem_desc_lo(smem_u32(b_tiles)), a_lo0 = smem_desc_lo(smem_u32(a_units));
+      bool ok = true;
+      uint32_t s = 0, sph = 0, u = 0, uph = 0, acc = 0;
+      for (uint32_t kt = 0; kt < KT && ok; ++kt) {
+        ok = mbar_wait(&b_full[s], sph, abort_flag, 300 + s);
+        if (!ok) break;
+        const uint32_t w_lo = w_lo0 + s * (B_STAGE >> 4);
+#pragma unroll
+        for (int h = 0; h < UPS; ++h) {
+          ok = mbar_wait(&a_full[u], uph, abort_flag, 200 + u);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_lo = a_lo0 + u * (HALF_BYTES >> 4);
+#pragma unroll
+          for (int k16 = 0; k16 < BK / 16; ++k16)
+            umma_f16_pair(tmem_base + h * 256, w_lo + k16 * 2, a_lo + k16 * 2, SMEM_DESC_HI_SW128, idesc, k16 == 0 ? acc : 1u);
+          umma_commit_pair(&a_empty[u]);
+          if (++u == AU) {
+            u = 0;
+            uph ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit_pair(&b_empty[s]);
+        acc = 1;
+        if (++s == BS) {
+          s = 0;
+          sph ^= 1;
+        }
+      }
+      if (ok) umma_commit_pair(acc_full);
+    }
+  } else {
+    // ---------------- dequant warps, then epilogue ----------------
+    const uint32_t bfull0 = map_to_cta(smem_u32(b_full), 0);
+    const uint32_t row_off = row * 128;
+    bool ok = dequant_stages<C, C::U>(raw, b_tiles, b_empty, b_full, bfull0, row, hb, row_off, qs_row, d_row, KT, nb, abort_flag, lane);
+    if (ok) ok = mbar_wait(acc_full, 0, abort_flag, 500);
+    // epilogue: as in the one-CTA kernel; the two warps of a lane quadrant take one half of the tokens each
+    const int quad = warp & 3, half = (warp - 2) >> 2;
+    const bool staged = OUT_F16 && n0 + ROWS <= N && N % 8 == 0;
+    if (ok) {
+      tc_fence_after();
+      const uint32_t orow = n0 + quad * 32 + lane;
+      for (int c = half * (TN / 2); c < (half + 1) * (TN / 2); c += 32) {
+        if (m0 + c >= M) break;
+        uint32_t v[32];
+        tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + c, v);
+        tmem_ld_wait();
+        if (staged) {
+          __half *tile = reinterpret_cast<__half *>(smem) + (size_t)c * ROWS + quad * 32 + lane;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) tile[(size_t)j * ROWS] = __float2half_rn(__uint_as_float(v[j]));
+        } else if (orow < N) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const uint32_t m = m0 + c + j;
+            if (m < M) {
+              if (OUT_F16)
+                reinterpret_cast<__half *>(Cout)[(size_t)m * N + orow] = __float2half_rn(__uint_as_float(v[j]));
+              else
+                reinterpret_cast<float *>(Cout)[(size_t)m * N + orow] = __uint_as_float(v[j]);
+            }
+          }
+        }
+      }
+    }
+    if (staged) {
+      asm volatile("bar.sync 1, %0;" ::"n"(C::DEQ_THREADS) : "memory");
+      if (ok) {
+        constexpr uint32_t PIECES_PER_TOKEN = ROWS / 8;
+        const uint32_t tokens = min((uint32_t)TN, M - m0);
+        for (uint32_t piece = t; piece < tokens * PIECES_PER_TOKEN; piece += C::DEQ_THREADS) {
+          const uint32_t tok = piece / PIECES_PER_TOKEN, off = piece % PIECES_PER_TOKEN;
+          const uint4 val = *reinterpret_cast<const uint4 *>(smem + ((size_t)tok * ROWS + off * 8) * 2);
+          *reinterpret_cast<uint4 *>(reinterpret_cast<__half *>(Cout) + (size_t)(m0 + tok) * N + n0 + off * 8) = val;
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  cluster_sync_all();  // both CTAs are done with each other's barriers and with their tensor memory
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, COLS);
+  }
+}
+
 // ---- host side ---------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
@@ -514,6 +824,22 @@ int launch_tc(cudaStream_t stream, const CUtensorMap &map, const void *qs, const
   dim3 grid((N + Cf::ROWS - 1) / Cf::ROWS, (M + TN - 1) / TN);
   gemm_tc_kernel<FMT, TN, RT, OUT_F16><<<grid, Cf::THREADS, Cf::SMEM, stream>>>(map, (const uint8_t *)qs, (const __half *)d, C, M, N, K);
   return launched("gemm_tc_kernel");
+}
+
+template <int FMT, int UPS, bool OUT_F16>
+int launch_pair(cudaStream_t stream, const CUtensorMap &map, const void *qs, const void *d, void *C, uint32_t M, uint32_t N, uint32_t K) {
+  using Cf = PairCfg<FMT, UPS>;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    GRETA_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_pair_kernel<FMT, UPS, OUT_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cf::SMEM));
+    attr_set[dev] = true;
+  }
+  const uint32_t row_tiles = (N + TILE_N - 1) / TILE_N;
+  dim3 grid((row_tiles + 1) / 2 * 2, (M + Cf::TN - 1) / Cf::TN);  // whole pairs
+  gemm_tc_pair_kernel<FMT, UPS, OUT_F16><<<grid, Cf::THREADS, Cf::SMEM, stream>>>(map, (const uint8_t *)qs, (const __half *)d, C, M, N, K);
+  return launched("gemm_tc_pair_kernel");
 }
 
 template <int FMT, bool OUT_F16>
@@ -586,16 +912,23 @@ int greta_cuda_gemm(greta_stream_t stream, int fmt, const void *A, int a_is_f16,
   }
   int tn = 128, rt = 1;
   pick_tile(M, N, &tn, &rt);
-  CUtensorMap map;
+  // 512-token tiles run as CTA pairs unless a tile shape is forced or the switch is off (2: always, whatever the shape)
+  const bool pair = tuning().gemm_pair == 2 || (tuning().gemm_pair == 1 && tn == 512 && rt == 1 && tuning().gemm_tile_tokens == 0);
   const cuuint64_t dims[2] = {K, M};
+  CUtensorMap map;
   const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-  const cuuint32_t box[2] = {BK, tn >= 256 ? 256u : 128u};
+  const cuuint32_t box[2] = {BK, (tn >= 256 && !pair) ? 256u : 128u};
   const cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(a16), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     set_error("gemm: cuTensorMapEncodeTiled failed with code %d", (int)r);
     return GRETA_ERR_INVALID_ARGS;
+  }
+  if (pair) {
+    if (fmt == GRETA_FMT_Q4_0)
+      return c_is_f16 ? launch_pair<GRETA_FMT_Q4_0, 2, true>(s, map, qs, d, Cout, M, N, K) : launch_pair<GRETA_FMT_Q4_0, 2, false>(s, map, qs, d, Cout, M, N, K);
+    return c_is_f16 ? launch_pair<GRETA_FMT_Q8_0, 2, true>(s, map, qs, d, Cout, M, N, K) : launch_pair<GRETA_FMT_Q8_0, 2, false>(s, map, qs, d, Cout, M, N, K);
   }
   if (fmt == GRETA_FMT_Q4_0)
     return c_is_f16 ? dispatch_tile<GRETA_FMT_Q4_0, true>(s, map, tn, rt, qs, d, Cout, M, N, K) : dispatch_tile<GRETA_FMT_Q4_0, false>(s, map, tn, rt, qs, d, Cout, M, N, K);

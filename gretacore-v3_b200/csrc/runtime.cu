@@ -73,6 +73,8 @@ Tuning &tuning() {
     v.peer_two_level_min_tp = e ? atoi(e) : 4;
     e = getenv("GRETA_SKINNY_MAX_ROWS");
     v.skinny_max_rows = e ? atoi(e) : 32;
+    e = getenv("GRETA_GEMM_PAIR");
+    v.gemm_pair = (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 0;
     return v;
   }();
   return t;
@@ -127,6 +129,9 @@ int greta_cuda_set_tuning(const char *name, long long value) {
   } else if (!strcmp(name, "skinny_max_rows")) {
     GRETA_REQUIRE(value >= 1 && value <= 32, "set_tuning: skinny_max_rows=%lld outside 1..32", value);
     t.skinny_max_rows = (int)value;
+  } else if (!strcmp(name, "gemm_pair")) {
+    GRETA_REQUIRE(value >= 0 && value <= 2, "set_tuning: gemm_pair=%lld outside 0..2", value);
+    t.gemm_pair = (int)value;
   } else {
     set_error("set_tuning: unknown switch '%s'", name);
     return GRETA_ERR_INVALID_ARGS;

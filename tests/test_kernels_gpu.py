@@ -622,6 +622,46 @@ def test_gemm_every_tile_shape(g, tuning, name, M, N, K, tile):
     assert np.isfinite(got).all() and err < 1e-4, err
 
 
+@pytest.mark.parametrize("name,M,N,K,c_f16", [("q4_0", 600, 300, 1376, False), ("q8_0", 515, 260, 2048, False), ("q4_0", 100, 128, 4096, False),
+                                              ("q4_0", 257, 1000, 1024, True), ("q8_0", 512, 384, 4096, True), ("q4_0", 1024, 2048, 544, True)])
+def test_gemm_cta_pairs(g, tuning, name, M, N, K, c_f16):
+    """The two-CTA form (one tcgen05.mma of cta_group::2 per pair, each CTA staging half of the tokens) gives the
+    one-CTA product: odd number of row tiles (a CTA with nothing to store), ragged token and row tiles, a second
+    token unit that is all padding, odd number of blocks in K, more K stages than the rings are deep, both outputs."""
+    tuning("gemm_pair", 2, restore=0)
+    ofmt, gfmt = FMTS[name]
+    rng = np.random.default_rng(1200 + M + N)
+    blk = make_blocks(rng, ofmt, N, K)
+    a16 = rng.normal(0, 1, (M, K)).astype(np.float16).view(np.uint16)
+    w = g.Weight(blk, gfmt, N, K)
+    c = g.DeviceBuffer(M * N * (2 if c_f16 else 4))
+    _KEEP.append(c)
+    c.fill(0xFF)
+    g.check(g.cuda().greta_cuda_gemm(None, gfmt, _dev(g, a16).ptr, 1, w.qs.ptr, w.d.ptr, c.ptr, int(c_f16), M, N, K, None))
+    g.check(g.cuda().greta_cuda_device_synchronize())
+    assert _gemm_status(g) == 0
+    if c_f16:
+        got = O.f16_bits_to_f32(c.download(np.uint16)).reshape(M, N)
+        want = O.f16_bits_to_f32(O.gemm(a16, blk, ofmt, N, K, out_f16=True))
+        bar = 1.5e-3
+    else:
+        got = c.download(np.float32).reshape(M, N)
+        want = O.gemm(a16, blk, ofmt, N, K)
+        bar = 1e-4
+    assert np.isfinite(got).all()
+    err = max_abs_rel(got, want)
+    assert err < bar, err
+    # and bit for bit what the one-CTA kernel stores (same products, same accumulation order inside the tensor core)
+    tuning("gemm_pair", 0, restore=0)
+    c1 = g.DeviceBuffer(M * N * (2 if c_f16 else 4))
+    _KEEP.append(c1)
+    g.check(g.cuda().greta_cuda_gemm(None, gfmt, _dev(g, a16).ptr, 1, w.qs.ptr, w.d.ptr, c1.ptr, int(c_f16), M, N, K, None))
+    g.check(g.cuda().greta_cuda_device_synchronize())
+    one = c1.download(np.uint16 if c_f16 else np.float32).reshape(M, N)
+    two = c.download(np.uint16 if c_f16 else np.float32).reshape(M, N)
+    assert max_abs_rel(O.f16_bits_to_f32(two) if c_f16 else two, O.f16_bits_to_f32(one) if c_f16 else one) < 1e-6
+
+
 def test_gemm_rejects_what_it_cannot_do(g):
     lib = g.cuda()
     buf = g.DeviceBuffer(1 << 16)
