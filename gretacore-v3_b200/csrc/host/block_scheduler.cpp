@@ -230,6 +230,56 @@ bool BlockScheduler::set_layer_tensor(size_t layer, LayerTensor which, const voi
   return upload_blocks(c.weight_type, local.data(), s.rows, s.cols, *p.qs, *p.d, staging, err);
 }
 
+// K-quant rows [row0, row0 + rows) of a [grows x gcols] tensor -> Q8_0 planes of the column range [col0, col0 + cols).
+// Whole rows are converted on the device (a column range need not be whole super-blocks), then the range is copied out.
+static bool upload_kquant(int ggml_type, const uint8_t *host, uint32_t gcols, uint32_t row0, uint32_t rows, uint32_t col0, uint32_t cols, Buffer &qs,
+                          Buffer &d, std::string *err) {
+  if (gcols % 256) return fail(err, "K-quant tensor: row length is not a multiple of the super-block size 256");
+  const size_t row_b = greta_cuda_kquant_bytes(ggml_type, gcols);
+  if (row_b == 0) return fail(err, "K-quant tensor: GGML type is not Q4_K or Q6_K");
+  Buffer staging, fq, fd;
+  if (!staging.allocate(rows * row_b, BufferUsage::DeviceOnly, GretaDataType::INT8, err)) return false;
+  GRETA_TRY(greta_cuda_memcpy_h2d_sync(staging.data(), host + (size_t)row0 * row_b, rows * row_b), "weight upload");
+  if (cols == gcols) {
+    GRETA_TRY(greta_cuda_kquant_to_q8_0(nullptr, ggml_type, staging.data(), qs.data(), d.data(), rows, cols), "kquant_to_q8_0");
+    GRETA_TRY(greta_cuda_device_synchronize(), "kquant_to_q8_0");
+    return true;
+  }
+  const int f = GRETA_FMT_Q8_0;
+  if (!fq.allocate(greta_cuda_qs_bytes(f, rows, gcols), BufferUsage::DeviceOnly, GretaDataType::INT8, err)) return false;
+  if (!fd.allocate(greta_cuda_d_bytes(f, rows, gcols), BufferUsage::DeviceOnly, GretaDataType::FP16, err)) return false;
+  GRETA_TRY(greta_cuda_kquant_to_q8_0(nullptr, ggml_type, staging.data(), fq.data(), fd.data(), rows, gcols), "kquant_to_q8_0");
+  GRETA_TRY(greta_cuda_memcpy_2d_d2d(qs.data(), (size_t)cols, static_cast<const uint8_t *>(fq.data()) + col0, (size_t)gcols, (size_t)cols, rows, nullptr),
+            "shard copy");
+  GRETA_TRY(greta_cuda_memset(d.data(), 0, greta_cuda_d_bytes(f, rows, cols), nullptr), "shard copy");  // row padding of the scale plane
+  GRETA_TRY(greta_cuda_memcpy_2d_d2d(d.data(), greta_cuda_d_bytes(f, 1, cols), static_cast<const uint8_t *>(fd.data()) + (size_t)(col0 / 32) * 2,
+                                     greta_cuda_d_bytes(f, 1, gcols), (size_t)(cols / 32) * 2, rows, nullptr),
+            "shard copy");
+  GRETA_TRY(greta_cuda_device_synchronize(), "shard copy");
+  return true;
+}
+
+bool BlockScheduler::set_layer_tensor_kquant(size_t layer, LayerTensor which, int ggml_type, const void *host, size_t bytes, std::string *err) {
+  if (layer >= blocks_.size()) return fail(err, "set_layer_tensor_kquant: layer out of range (allocate_weights first)");
+  if (which == LayerTensor::ATTN_NORM || which == LayerTensor::FFN_NORM) return fail(err, "set_layer_tensor_kquant: norm weights are plain floats");
+  const ModelConfig &c = config_;
+  if (c.weight_type != GretaDataType::Q8_0) return fail(err, "set_layer_tensor_kquant: K-quant tensors are re-stored as Q8_0; initialise the scheduler with weight_type Q8_0");
+  Shape s = shard_of(c, which);
+  if (bytes != (size_t)s.grows * greta_cuda_kquant_bytes(ggml_type, s.gcols) || bytes == 0)
+    return fail(err, "set_layer_tensor_kquant: byte size does not match the global tensor shape");
+  PlanePair p = planes(blocks_[layer], which);
+  return upload_kquant(ggml_type, static_cast<const uint8_t *>(host), s.gcols, s.row0, s.rows, s.col0, s.cols, *p.qs, *p.d, err);
+}
+
+bool BlockScheduler::set_global_tensor_kquant(GlobalTensor which, int ggml_type, const void *host, size_t bytes, std::string *err) {
+  const ModelConfig &c = config_;
+  if (which != GlobalTensor::OUT_WEIGHT) return fail(err, "set_global_tensor_kquant: only the LM head is kept quantised");
+  if (c.lm_head_type != GretaDataType::Q8_0) return fail(err, "set_global_tensor_kquant: a K-quant LM head is re-stored as Q8_0; set lm_head_type to Q8_0");
+  if (bytes != (size_t)c.vocab_size * greta_cuda_kquant_bytes(ggml_type, c.dim) || bytes == 0)
+    return fail(err, "set_global_tensor_kquant: LM head size mismatch");
+  return upload_kquant(ggml_type, static_cast<const uint8_t *>(host), c.dim, c.tp_rank * vocab_l_, vocab_l_, 0, c.dim, output_weight_, s_output_weight_, err);
+}
+
 bool BlockScheduler::set_global_tensor(GlobalTensor which, const void *host, size_t bytes, std::string *err) {
   const ModelConfig &c = config_;
   if (which == GlobalTensor::TOK_EMBD) {

@@ -25,7 +25,8 @@ using gcore::rt::GretaDataType;
 
 namespace {
 
-enum GgmlType : uint32_t { GGML_F32 = 0, GGML_F16 = 1, GGML_Q4_0 = 2, GGML_Q8_0 = 8 };
+enum GgmlType : uint32_t { GGML_F32 = 0, GGML_F16 = 1, GGML_Q4_0 = 2, GGML_Q8_0 = 8, GGML_Q4_K = GRETA_GGML_Q4_K, GGML_Q6_K = GRETA_GGML_Q6_K };
+inline bool is_kquant(uint32_t t) { return t == GGML_Q4_K || t == GGML_Q6_K; }
 
 const char *ggml_name(uint32_t t) {
   switch (t) {
@@ -45,6 +46,8 @@ size_t ggml_bytes(uint32_t t, size_t elems) {
     case GGML_F16: return elems * 2;
     case GGML_Q4_0: return elems / 32 * 18;
     case GGML_Q8_0: return elems / 32 * 34;
+    case GGML_Q4_K:
+    case GGML_Q6_K: return greta_cuda_kquant_bytes((int)t, elems);
     default: return 0;
   }
 }
@@ -278,14 +281,17 @@ bool GGUFLoader::open(const std::string &path, std::string *err) {
   // Storage format of the projections: what the first layer's query projection is stored as.
   if (const Impl::Entry *wq = im.find("blk.0.attn_q.weight")) {
     if (wq->ggml_type == GGML_Q4_0) cfg.weight_type = GretaDataType::Q4_0;
-    else if (wq->ggml_type == GGML_Q8_0) cfg.weight_type = GretaDataType::Q8_0;
+    else if (wq->ggml_type == GGML_Q8_0 || is_kquant(wq->ggml_type)) cfg.weight_type = GretaDataType::Q8_0;  // K-quants are re-stored as Q8_0
   }
   if (const Impl::Entry *emb = im.find("token_embd.weight"))
     if (cfg.vocab_size == 0 && emb->info.shape.size() == 2) cfg.vocab_size = (uint32_t)emb->info.shape[0];
   if (cfg.vocab_size == 0) cfg.vocab_size = ModelConfig{}.vocab_size;
   const Impl::Entry *out = im.find("output.weight");
   if (!out) out = im.find("token_embd.weight");  // tied embeddings
-  if (out) cfg.lm_head_type = out->ggml_type == GGML_Q4_0 ? GretaDataType::Q4_0 : out->ggml_type == GGML_Q8_0 ? GretaDataType::Q8_0 : GretaDataType::FP16;
+  if (out)
+    cfg.lm_head_type = out->ggml_type == GGML_Q4_0 ? GretaDataType::Q4_0
+                       : (out->ggml_type == GGML_Q8_0 || is_kquant(out->ggml_type)) ? GretaDataType::Q8_0
+                                                                                    : GretaDataType::FP16;
   return true;
 }
 
@@ -306,10 +312,19 @@ bool GGUFLoader::tensor_data(const std::string &name, const void **data, size_t 
   return true;
 }
 
-// F32 / F16 tensor -> fp32 on the device (norm weights).
+// F32 / F16 / Q4_K / Q6_K tensor -> fp32 on the device (norm weights; any tensor a caller wants as plain floats).
 bool GGUFLoader::load_tensor(const std::string &name, gcore::rt::cuda::Buffer &buffer, std::string *err) {
   const Impl::Entry *e = impl_->find(name);
   if (!e) return fail(err, "GGUF: tensor not found: " + name);
+  if (is_kquant(e->ggml_type)) {  // decoded on the device, as GGUFLoader::load_tensor of the reference decodes them on the host (weight_loader.cpp:551-565)
+    gcore::rt::cuda::Buffer raw;
+    if (!raw.allocate(e->info.size_bytes, gcore::rt::cuda::BufferUsage::DeviceOnly, GretaDataType::INT8, err)) return false;
+    if (!raw.copy_to_device(impl_->data(*e), e->info.size_bytes, err)) return false;
+    if (buffer.size() < e->elems * 4 && !buffer.allocate(e->elems * 4, gcore::rt::cuda::BufferUsage::DeviceOnly, GretaDataType::FP32, err)) return false;
+    if (greta_cuda_kquant_dequant(nullptr, (int)e->ggml_type, raw.data(), e->elems, buffer.data(), 0) != GRETA_OK || greta_cuda_device_synchronize() != GRETA_OK)
+      return fail(err, std::string("GGUF: decoding ") + name + ": " + greta_cuda_last_error());
+    return true;
+  }
   std::vector<float> tmp(e->elems);
   if (e->ggml_type == GGML_F32) {
     std::memcpy(tmp.data(), impl_->data(*e), e->elems * 4);
@@ -323,7 +338,7 @@ bool GGUFLoader::load_tensor(const std::string &name, gcore::rt::cuda::Buffer &b
   return buffer.copy_to_device(tmp.data(), e->elems * 4, err);
 }
 
-// F16 / F32 / Q4_0 / Q8_0 tensor -> fp16 values in host memory (embedding table, fp16 LM head).
+// F16 / F32 / Q4_0 / Q8_0 / Q4_K / Q6_K tensor -> fp16 values in host memory (embedding table, fp16 LM head).
 bool GGUFLoader::read_as_fp16(const std::string &name, std::vector<uint16_t> *out, std::string *err) const {
   const Impl::Entry *e = impl_->find(name);
   if (!e) return fail(err, "GGUF: tensor not found: " + name);
@@ -347,6 +362,14 @@ bool GGUFLoader::read_as_fp16(const std::string &name, std::vector<uint16_t> *ou
         (*out)[b * 32 + j] = float_to_half_bits((float)q * d);
       }
     }
+  } else if (is_kquant(e->ggml_type)) {  // decoded and rounded to fp16 on the device
+    gcore::rt::cuda::Buffer raw, half;
+    if (!raw.allocate(e->info.size_bytes, gcore::rt::cuda::BufferUsage::DeviceOnly, GretaDataType::INT8, err)) return false;
+    if (!half.allocate(e->elems * 2, gcore::rt::cuda::BufferUsage::DeviceOnly, GretaDataType::FP16, err)) return false;
+    if (!raw.copy_to_device(p, e->info.size_bytes, err)) return false;
+    if (greta_cuda_kquant_dequant(nullptr, (int)e->ggml_type, raw.data(), e->elems, half.data(), 1) != GRETA_OK ||
+        greta_cuda_memcpy_d2h_sync(out->data(), half.data(), e->elems * 2) != GRETA_OK)
+      return fail(err, std::string("GGUF: decoding ") + name + ": " + greta_cuda_last_error());
   } else {
     return fail(err, "GGUF: " + name + " has storage type " + e->info.dtype + ", which this path does not read");
   }
@@ -396,6 +419,10 @@ bool BlockScheduler::load_weights(WeightLoader &loader, std::string *err) {
       std::string dtype;
       const std::string name = prefix + kNames[t] + ".weight";
       if (!gguf->tensor_data(name, &data, &bytes, &dtype, err)) return false;
+      if (dtype == "Q4_K" || dtype == "Q6_K") {  // re-stored as Q8_0 on the device
+        if (!set_layer_tensor_kquant(l, (LayerTensor)t, dtype == "Q4_K" ? GRETA_GGML_Q4_K : GRETA_GGML_Q6_K, data, bytes, err)) return false;
+        continue;
+      }
       if (dtype != want) return fail(err, "load_weights: " + name + " is stored as " + dtype + ", the scheduler was initialised for " + want);
       if (!set_layer_tensor(l, (LayerTensor)t, data, bytes, err)) return false;
     }
@@ -418,6 +445,7 @@ bool BlockScheduler::load_weights(WeightLoader &loader, std::string *err) {
   size_t bytes;
   std::string dtype;
   if (!gguf->tensor_data(head, &data, &bytes, &dtype, err)) return false;
+  if (dtype == "Q4_K" || dtype == "Q6_K") return set_global_tensor_kquant(GlobalTensor::OUT_WEIGHT, dtype == "Q4_K" ? GRETA_GGML_Q4_K : GRETA_GGML_Q6_K, data, bytes, err);
   if (dtype != (c.lm_head_type == GretaDataType::Q4_0 ? "Q4_0" : "Q8_0")) return fail(err, "load_weights: " + head + " is stored as " + dtype + ", not as the configured LM-head type");
   return set_global_tensor(GlobalTensor::OUT_WEIGHT, data, bytes, err);
 }

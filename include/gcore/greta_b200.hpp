@@ -480,6 +480,11 @@ public:
   // One tensor from host memory: GGUF blocks for the projections, fp32 for the norms, fp16 for embedding / LM head.
   bool set_layer_tensor(size_t layer, LayerTensor which, const void *host, size_t bytes, std::string *err);
   bool set_global_tensor(GlobalTensor which, const void *host, size_t bytes, std::string *err);
+  // The same for a tensor stored as K-quant super-blocks (ggml_type GRETA_GGML_Q4_K / GRETA_GGML_Q6_K): the global tensor is
+  // decoded on the device with the reference loader's arithmetic and re-stored as Q8_0 blocks, so weight_type (or lm_head_type
+  // for OUT_WEIGHT) must be Q8_0.  The reference re-quantises such tensors as well (to its INT4: weight_loader.cpp:920-957).
+  bool set_layer_tensor_kquant(size_t layer, LayerTensor which, int ggml_type, const void *host, size_t bytes, std::string *err);
+  bool set_global_tensor_kquant(GlobalTensor which, int ggml_type, const void *host, size_t bytes, std::string *err);
 
   bool execute_layer(size_t layer_idx, size_t seq_start, size_t seq_len, const int32_t *tokens, std::string *err);
   // Runs seq_len tokens starting at seq_start; logits of the last position are left in get_logits().

@@ -130,6 +130,18 @@ GRETA_API uint64_t greta_cuda_launch_count(void);
 /* Bytes of the qs plane and of the d plane of an [N x K] weight. */
 GRETA_API size_t greta_cuda_qs_bytes(int fmt, uint32_t N, uint32_t K);
 GRETA_API size_t greta_cuda_d_bytes(int fmt, uint32_t N, uint32_t K);
+/* K-quant super-blocks (256 weights; GGML type codes as in a GGUF file).  Decoding follows the reference loader
+ * (src/inference/src/weight_loader.cpp:125-177) bit for bit, including its own reading of the two layouts. */
+#define GRETA_GGML_Q4_K 12 /* 144 bytes: fp16 d, fp16 dmin, 12 bytes of 6-bit scales and mins, 128 payload bytes */
+#define GRETA_GGML_Q6_K 14 /* 210 bytes: 128 low-nibble bytes, 64 high-bit bytes, 16 int8 scales, fp16 d */
+/* Bytes of n_elems weights stored as that type; 0 for another type or a count that is not whole super-blocks. */
+GRETA_API size_t greta_cuda_kquant_bytes(int ggml_type, size_t n_elems);
+/* blocks (device, as in the file) -> n_elems fp32 or fp16 values (GGUFLoader::load_tensor, weight_loader.cpp:551-565). */
+GRETA_API int greta_cuda_kquant_dequant(greta_stream_t stream, int ggml_type, const void *blocks, size_t n_elems, void *out, int out_is_f16);
+/* blocks of an [N x K] weight -> the qs and d planes of GRETA_FMT_Q8_0 (sizes from greta_cuda_qs_bytes / greta_cuda_d_bytes):
+ * each group of 32 decoded values becomes one Q8_0 block, d = amax / 127 rounded to fp16, q = round(x / d).  The reference
+ * re-quantises K-quant tensors too, to its INT4 storage (weight_loader.cpp:920-957). */
+GRETA_API int greta_cuda_kquant_to_q8_0(greta_stream_t stream, int ggml_type, const void *blocks, void *qs, void *d, uint32_t N, uint32_t K);
 /* Device-side split of raw GGUF blocks (18 B Q4_0 / 34 B Q8_0, as stored in a GGUF
  * file: src/inference/src/weight_loader.cpp:60-75 sizes, :703-712 Q8_0 split) into
  * the two planes. */

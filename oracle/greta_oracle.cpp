@@ -268,6 +268,74 @@ OAPI void oracle_dequant(const uint8_t *blocks, int fmt, size_t n_blocks, float 
   }
 }
 
+// K-quant super-blocks of 256 weights, decoded the way the reference decodes them
+// (src/inference/src/weight_loader.cpp:125-156 for Q4_K, :158-177 for Q6_K).  The reference's reading of these
+// two layouts is its own: for Q4_K byte l of sub-block j holds elements 2l (low nibble) and 2l+1 (high nibble)
+// of that sub-block, and the eight 6-bit scales and mins are unpacked as written below; for Q6_K element i takes
+// its low four bits from nibble i of ql, its high two bits from bit pair i of qh and its scale from entry i / 16.
+// (Upstream ggml orders the nibbles and packs the scales differently; the reference's results are what counts
+// here.)  fp32 arithmetic in the reference's order, no fused multiply-add.
+// Q4_K block: fp16 d, fp16 dmin, 12 scale bytes, 128 payload bytes (144 bytes).
+OAPI void oracle_dequant_q4_k(const uint8_t *blocks, size_t n_super, float *out) {
+#pragma omp parallel for if (n_super > 1024)
+  for (size_t b = 0; b < n_super; ++b) {
+    const uint8_t *blk = blocks + b * 144, *sc = blk + 4, *qs = blk + 16;
+    uint16_t dh, mh;
+    std::memcpy(&dh, blk, 2);
+    std::memcpy(&mh, blk + 2, 2);
+    const float d = h2f(dh), dmin = h2f(mh);
+    uint8_t s8[8], m8[8];
+    for (int j = 0; j < 4; ++j) {
+      s8[j] = sc[j] & 0x3F;
+      m8[j] = sc[6 + j] & 0x3F;
+    }
+    for (int j = 0; j < 4; ++j) {  // entry 4 + j: top two bits of byte j, and a nibble of byte 4 + j / 2 shifted up by two
+      const uint8_t ns = (j & 1) ? (sc[4 + j / 2] >> 4) : (sc[4 + j / 2] & 0x0F);
+      const uint8_t nm = (j & 1) ? (sc[10 + j / 2] >> 4) : (sc[10 + j / 2] & 0x0F);
+      s8[4 + j] = (uint8_t)((sc[j] >> 6) | (ns << 2));
+      m8[4 + j] = (uint8_t)((sc[6 + j] >> 6) | (nm << 2));
+    }
+    for (int j = 0; j < 8; ++j) {
+      const float scale = d * (float)s8[j], minv = dmin * (float)m8[j];
+      for (int l = 0; l < 16; ++l) {
+        const uint8_t q = qs[j * 16 + l];
+        out[b * 256 + j * 32 + 2 * l] = scale * (float)(q & 0x0F) - minv;
+        out[b * 256 + j * 32 + 2 * l + 1] = scale * (float)(q >> 4) - minv;
+      }
+    }
+  }
+}
+// Q6_K block: ql[128], qh[64], int8 scales[16], fp16 d (210 bytes).
+OAPI void oracle_dequant_q6_k(const uint8_t *blocks, size_t n_super, float *out) {
+#pragma omp parallel for if (n_super > 1024)
+  for (size_t b = 0; b < n_super; ++b) {
+    const uint8_t *blk = blocks + b * 210, *ql = blk, *qh = blk + 128;
+    const int8_t *sc = reinterpret_cast<const int8_t *>(blk + 192);
+    uint16_t dh;
+    std::memcpy(&dh, blk + 208, 2);
+    const float d = h2f(dh);
+    for (int i = 0; i < 256; ++i) {
+      const int lo = (ql[i / 2] >> ((i % 2) * 4)) & 0x0F, hi = (qh[i / 4] >> ((i % 4) * 2)) & 0x03;
+      const int q = (lo | (hi << 4)) - 32;
+      out[b * 256 + i] = (d * (float)q) * (float)sc[i / 16];
+    }
+  }
+}
+// fp32 values -> GGUF Q8_0 blocks (fp16 d, 32 int8), the round-to-nearest quantiser published with the format
+// (ggml, quantize_row_q8_0 reference form; ggml is not part of the reference checkout): d = amax / 127,
+// q = roundf(x / d) with the reciprocal taken in fp32 before d is rounded to fp16 for storage.
+OAPI void oracle_quantize_q8_0(const float *x, size_t n_blocks, uint8_t *blocks) {
+#pragma omp parallel for if (n_blocks > 4096)
+  for (size_t b = 0; b < n_blocks; ++b) {
+    float amax = 0.f;
+    for (int j = 0; j < 32; ++j) amax = std::max(amax, std::fabs(x[b * 32 + j]));
+    const float d = amax / 127.0f, id = d != 0.f ? 1.0f / d : 0.f;
+    const uint16_t dh = f2h(d);
+    std::memcpy(blocks + b * 34, &dh, 2);
+    for (int j = 0; j < 32; ++j) blocks[b * 34 + 2 + j] = (uint8_t)(int8_t)std::roundf(x[b * 32 + j] * id);
+  }
+}
+
 // The reference's own INT4 storage: uint8 w[n/2], element 2j in the low nibble
 // and 2j+1 in the high nibble, two's complement, fp32 scale per group of
 // group_size along the flat index (gemm_kernels.hip:784-797;

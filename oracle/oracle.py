@@ -115,6 +115,33 @@ def dequant_ref_int8(w, scales, group_size=32):
     return out
 
 
+def dequant_q4_k(blocks):
+    """Q4_K super-blocks (144 bytes per 256 weights) -> fp32, in the reference's decoding."""
+    blocks = np.ascontiguousarray(blocks, np.uint8)
+    n = blocks.size // 144
+    out = np.empty(n * 256, np.float32)
+    lib().oracle_dequant_q4_k(_p(blocks), C.c_size_t(n), _p(out))
+    return out
+
+
+def dequant_q6_k(blocks):
+    """Q6_K super-blocks (210 bytes per 256 weights) -> fp32, in the reference's decoding."""
+    blocks = np.ascontiguousarray(blocks, np.uint8)
+    n = blocks.size // 210
+    out = np.empty(n * 256, np.float32)
+    lib().oracle_dequant_q6_k(_p(blocks), C.c_size_t(n), _p(out))
+    return out
+
+
+def quantize_q8_0(x):
+    """fp32 values (a multiple of 32) -> GGUF Q8_0 blocks."""
+    x = np.ascontiguousarray(x, np.float32)
+    nb = x.size // 32
+    out = np.empty(nb * 34, np.uint8)
+    lib().oracle_quantize_q8_0(_p(x), C.c_size_t(nb), _p(out))
+    return out
+
+
 def q4_0_to_ref_int4(blocks):
     blocks = np.ascontiguousarray(blocks, np.uint8)
     nb = blocks.size // 18

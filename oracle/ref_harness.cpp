@@ -55,6 +55,18 @@ RAPI int ref_gguf_load_int4(const char *path, const char *name, uint8_t *packed,
   return 0;
 }
 
+// GGUFLoader::load_tensor: F32 / F16 / Q4_K / Q6_K tensor -> fp32 (weight_loader.cpp:520-570).
+RAPI int ref_gguf_load_fp32(const char *path, const char *name, float *out, size_t cap) {
+  std::string err;
+  gcore::inference::GGUFLoader ld;
+  if (!ld.open(path, &err)) return 1;
+  gcore::rt::hip::Buffer b;
+  if (!ld.load_tensor(name, b, &err)) return 2;
+  if (b.size() > cap * 4) return 3;
+  std::memcpy(out, b.data(), b.size());
+  return 0;
+}
+
 // GGUFLoader::get_config after open(): the model shape the reference parses.
 RAPI int ref_gguf_config(const char *path, uint32_t *out10) {
   std::string err;

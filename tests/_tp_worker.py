@@ -1,7 +1,8 @@
 """One rank of the tensor-parallel check (launched by test_tp_gpu.py under torch.distributed.run).
 Each rank holds its shard of a small Llama-shaped model and runs prefill + greedy decode twice: with the NCCL
 all-reduce, and with the exchange fused into the GEMV kernels over peer memory; then a batch of five sequences
-decoding in step; rank 0 compares all ids with the CPU oracle's and reads the exchange's time-out status."""
+decoding in step, then a model loaded from a K-quant file; rank 0 compares all ids with the CPU oracle's and reads the
+exchange's time-out status."""
 import ctypes as C
 import json
 import os
@@ -63,8 +64,24 @@ def main():
     out["batch"] = m.generate_batch(bprompts, n_new).tolist()
     ranks.barrier()
     m.close()
+    # a K-quant file under tensor parallelism: every rank decodes its rows on the device, re-stores them as Q8_0 and keeps its
+    # column range (the down-projection's 384 columns per rank are not whole super-blocks)
+    import tempfile
+    import test_kquant as KQ
+    with tempfile.TemporaryDirectory() as td:
+        kpath = os.path.join(td, "kq.gguf")
+        kweights = KQ._kquant_model_file(kpath, np.random.default_rng(6), "f16")        # the same file on every rank
+        m = pkg.model.Model(KQ.CFG, tp_rank=ranks.rank, tp_size=ranks.world, weight_fmt=g.FMT_Q8_0)
+        m.set_comm(comm)
+        m.load_gguf(kpath)
+        kprompt = pkg.model.synth_tokens(5, 20, KQ.CFG["vocab"])
+        out["kquant"] = m.generate(kprompt, 12)[0]
+        ranks.barrier()
+        m.close()
     if ranks.rank == 0:
         from oracle import oracle as O
+        want, gaps = O.Model(KQ.CFG, kweights, O.FMT_Q8_0).generate(kprompt, 12)
+        out["kquant_ok"] = out["kquant"] == want and min(gaps) > 1e-6
         weights = pkg.model.synth_weights(CFG, seed)
         ok = True
         for plen in (12, 40):
@@ -75,7 +92,7 @@ def main():
         for b in range(B):
             want, gaps = O.Model(CFG, weights).generate(bprompts[b], n_new)
             ok = ok and out["batch"][b] == want and min(gaps) > 1e-6
-        out["ok"] = bool(ok) and out.get("peer_status") == 0 and not out.get("repeat_mismatch")
+        out["ok"] = bool(ok) and out.get("peer_status") == 0 and not out.get("repeat_mismatch") and out["kquant_ok"]
         print("TP_RESULT " + json.dumps(out), flush=True)
     g.check(lib.greta_cuda_comm_destroy(comm))
 

@@ -35,6 +35,23 @@ def q8_0_blocks(rng, n_blocks, sigma=0.02):
     return blk
 
 
+def kquant_blocks(rng, ggml_type, n):
+    """Random K-quant super-blocks: every payload, scale and min bit pattern, fp16 super-scales of model-like size
+    (one of them subnormal, one zero)."""
+    if ggml_type == 12:   # Q4_K: d, dmin, scales[12], qs[128]
+        blk = rng.integers(0, 256, (n, 144), dtype=np.uint8)
+        d = (np.abs(rng.normal(0, 0.01, (n, 2))) / 16).astype(np.float16)
+        d[1, 0] = np.float16(3e-7)
+        d[2, 1] = np.float16(0)
+        blk[:, :4] = d.view(np.uint8).reshape(n, 4)
+    else:                 # Q6_K: ql[128], qh[64], scales[16], d
+        blk = rng.integers(0, 256, (n, 210), dtype=np.uint8)
+        d = (np.abs(rng.normal(0, 0.01, n)) / 1024).astype(np.float16)
+        d[1] = np.float16(2e-7)
+        blk[:, 208:] = d.view(np.uint8).reshape(n, 2)
+    return blk
+
+
 def main():
     ref = oracle.ref()
     if ref is None:
@@ -153,6 +170,32 @@ def main():
     g["rwv_int8_down"] = read_weights(3, g["int8_down_w"], g["int8_down_scales"], g["int8_down_w"].size)
     g["rwv_f16_bits"] = allh[::97].copy()
     g["rwv_f16"] = read_weights(1, g["rwv_f16_bits"], None, g["rwv_f16_bits"].size)
+
+    # 8. K-quant tensors through the reference's loader: GGUFLoader::load_tensor (fp32, weight_loader.cpp:520-570 with
+    # the block decoders at :125-177) and GGUFLoader::load_tensor_int4 (decode, then the INT4 re-quantiser, :825-957).
+    q4k, q6k = kquant_blocks(rng, 12, 8), kquant_blocks(rng, 14, 8)   # 8 super-blocks each: tensors [4 x 512]
+    with tempfile.TemporaryDirectory() as td:
+        path = os.path.join(td, "kq.gguf")
+        write_gguf(path,
+                   [("llama.embedding_length", 512), ("llama.attention.head_count", 4),
+                    ("llama.attention.head_count_kv", 4), ("llama.block_count", 1),
+                    ("llama.feed_forward_length", 4), ("llama.context_length", 64)],
+                   [("llama.rope.freq_base", 10000.0), ("llama.norm_eps", 1e-5)],
+                   [("blk.0.ffn_gate.weight", [4, 512], 12, q4k.tobytes()),
+                    ("blk.0.ffn_up.weight", [4, 512], 14, q6k.tobytes())])
+        for tag, name, blk in (("q4k", b"blk.0.ffn_gate.weight", q4k), ("q6k", b"blk.0.ffn_up.weight", q6k)):
+            f = np.empty(2048, np.float32)
+            rc = ref.ref_gguf_load_fp32(path.encode(), name, f.ctypes.data_as(C.c_void_p), C.c_size_t(f.size))
+            assert rc == 0, rc
+            pk = np.empty(1024, np.uint8)
+            sc = np.empty(64, np.float32)
+            hs = np.zeros(4, np.float32)
+            nh = C.c_uint32(0)
+            rc = ref.ref_gguf_load_int4(path.encode(), name, pk.ctypes.data_as(C.c_void_p), C.c_size_t(pk.size),
+                                        sc.ctypes.data_as(C.c_void_p), C.c_size_t(sc.size),
+                                        hs.ctypes.data_as(C.c_void_p), C.c_size_t(hs.size), C.byref(nh))
+            assert rc == 0, rc
+            g[tag + "_blocks"], g[tag + "_f32"], g[tag + "_int4_packed"], g[tag + "_int4_scales"] = blk, f, pk, sc
 
     out = os.path.join(HERE, "ref_golden.npz")
     np.savez_compressed(out, **g)

@@ -200,3 +200,34 @@ def test_gemv_accumulation_orders_agree():
         scale = np.abs(y64).max()
         assert np.abs(yref - y64).max() / scale < 1e-5
         assert np.abs(yfast - y64).max() / scale < 1e-5
+
+
+@pytest.mark.parametrize("tag", ["q4k", "q6k"])
+def test_kquant_decoders_match_the_reference_loader(golden, tag):
+    """Q4_K / Q6_K super-blocks decode to the fp32 values GGUFLoader::load_tensor produces, bit for bit
+    (weight_loader.cpp:125-177, 520-570), and the decode -> INT4 re-quantisation chain of load_tensor_int4
+    (:825-957) gives the reference's packed nibbles and group scales."""
+    dec = O.dequant_q4_k if tag == "q4k" else O.dequant_q6_k
+    got = dec(golden[tag + "_blocks"])
+    assert np.array_equal(got.view(np.uint32), golden[tag + "_f32"].view(np.uint32))
+    packed, scales = O.quantize_ref_int4(got)
+    assert np.array_equal(packed, golden[tag + "_int4_packed"])
+    assert np.array_equal(scales.view(np.uint32), golden[tag + "_int4_scales"].view(np.uint32))
+
+
+def test_q8_0_quantiser_round_trip():
+    """The Q8_0 quantiser K-quant tensors are re-stored with: d = amax / 127 in fp16, |q| <= 127, the largest magnitude
+    of a block maps to +-127, and decoding stays within half a step of the input (plus the fp16 rounding of d)."""
+    rng = np.random.default_rng(5)
+    x = rng.normal(0, 0.03, 64 * 32).astype(np.float32)
+    x[32:64] = 0.0                                       # an all-zero block
+    blk = O.quantize_q8_0(x).reshape(-1, 34)
+    q = blk[:, 2:].view(np.int8).astype(np.int32)
+    d = O.f16_bits_to_f32(blk[:, :2].copy().view(np.uint16).reshape(-1))
+    xb = x.reshape(-1, 32)
+    amax = np.abs(xb).max(axis=1)
+    assert np.abs(q).max() <= 127 and (q[1] == 0).all() and d[1] == 0
+    assert (np.abs(q).max(axis=1)[amax > 0] == 127).all()
+    assert np.array_equal(O.f32_to_f16_bits(amax / np.float32(127.0)), blk[:, :2].copy().view(np.uint16).reshape(-1))
+    back = O.dequant(blk, O.FMT_Q8_0).reshape(-1, 32)
+    assert (np.abs(back - xb) <= (0.5 + 127 * 2.0 ** -11) * d[:, None] + 1e-12).all()
