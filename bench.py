@@ -260,13 +260,15 @@ def time_dominant_kernel(pkg, cfg, tp, batch=1, reps=4):
     return us, alg_bytes, name
 
 
-def time_prefill_gemm(pkg, reps=5):
+def time_prefill_gemm(pkg, reps=5, split_k=False):
     """The prefill GEMM benchmark shape: fp16 activations [512 x 4096] x Q4_0 weights [11008 x 4096] -> fp16 [512 x 11008] on
     the tcgen05 kernel, 6 distinct weight copies (152 MB, beyond L2) captured in one graph, CUDA events; fraction of the
-    measured dense bf16 tensor peak (fp16 runs at the same rate)."""
+    measured dense bf16 tensor peak (fp16 runs at the same rate).  split_k: with the tuning switch that lets SMs share a
+    tile's K loop (off by default: it changes the fp32 summation order of the prefill)."""
     import ctypes as C
     g = pkg.ffi
     lib = g.cuda()
+    g.check(lib.greta_cuda_set_tuning(b"gemm_splitk", 1 if split_k else 0))   # off is the library's default
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
             peak, src = float(json.load(f)["bf16_tflops"]), "measured"
@@ -280,12 +282,13 @@ def time_prefill_gemm(pkg, reps=5):
     w = [(g.DeviceBuffer.from_numpy(qs_h), g.DeviceBuffer.from_numpy(d_h)) for _ in range(6)]
     a = g.DeviceBuffer.from_numpy(rng.normal(0, 1, (M, K)).astype(np.float16).view(np.uint16))
     c = g.DeviceBuffer(M * N * 2)
+    ws = g.DeviceBuffer(lib.greta_cuda_gemm_workspace_bytes(M, K))      # with a workspace the K loop of a tile may be shared between SMs
     stream, graph, ex, e0, e1 = C.c_void_p(), C.c_void_p(), C.c_void_p(), C.c_void_p(), C.c_void_p()
     g.check(lib.greta_cuda_stream_create(C.byref(stream)))
 
     def one_pass():
         for qs, d in w:
-            g.check(lib.greta_cuda_gemm(stream, g.FMT_Q4_0, a.ptr, 1, qs.ptr, d.ptr, c.ptr, 1, M, N, K, None))
+            g.check(lib.greta_cuda_gemm(stream, g.FMT_Q4_0, a.ptr, 1, qs.ptr, d.ptr, c.ptr, 1, M, N, K, ws.ptr))
 
     one_pass()
     g.check(lib.greta_cuda_stream_synchronize(stream))
@@ -311,9 +314,12 @@ def time_prefill_gemm(pkg, reps=5):
         d.free()
     a.free()
     c.free()
+    ws.free()
+    g.check(lib.greta_cuda_set_tuning(b"gemm_splitk", 0))
     tflops = 2.0 * M * N * K / us / 1e6
     return {"shape": "fp16 [512 x 4096] x Q4_0 [11008 x 4096] -> fp16 [512 x 11008]", "us_per_launch": us, "tflops": tflops, "peak_tflops": peak,
-            "frac": tflops / peak, "peak_source": f"of {src}", "bound": "tensor"}
+            "frac": tflops / peak, "peak_source": f"of {src}", "bound": "tensor",
+            "kernel": "gemm_tc_splitk_kernel (tuning switch gemm_splitk = 1: K loops shared between SMs)" if split_k else "gemm_tc_kernel (default)"}
 
 
 # ----------------------------------------------------------------------------- GEMV bandwidth per projection shape
@@ -733,6 +739,7 @@ def main():
     }
     if tp == 1:                                              # reported at N=1 only
         out["prefill_gemm"] = time_prefill_gemm(pkg)         # the tensor-bound half of the path: the prefill dequant-GEMM
+        out["prefill_gemm_split_k"] = time_prefill_gemm(pkg, split_k=True)   # the same product with the opt-in split over K
     if not args.no_cpu_baseline and tp == 1:
         out["cpu_baseline"] = cpu_baseline(pkg, cfg, context, B)
     print(json.dumps(out))

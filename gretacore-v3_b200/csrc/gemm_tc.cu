@@ -26,6 +26,8 @@
 
 #include <cstdio>
 #include <cstdlib>
+#include <atomic>
+#include <chrono>
 #include <mutex>
 
 #include "greta_common.cuh"
@@ -794,6 +796,319 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t *_
   }
 }
 
+// ---- split over K ------------------------------------------------------------------------------
+// Fixed tiles leave SMs idle when there are fewer tiles than SMs, or not a multiple of them (11008 rows x 512
+// tokens: 86 tiles on 148 SMs).  Here the work is counted in K stages of 128-row x 512-token tiles and cut into
+// one contiguous share per CTA, shares being at most one tile's K loop long, so a CTA runs at most two
+// "segments": the end of one tile's K range, then the beginning of the next tile's.  A segment that does not
+// start at stage 0 is a contribution: its fp32 accumulator goes to the CTA's slot of a workspace, followed by a
+// flag.  The segment that starts a tile owns it: after its own stages it waits (bounded) for the flags of the
+// CTAs that hold the rest of the tile's K range, adds their partial sums in ascending K order (so the result
+// does not depend on timing) and stores the tile.  The owner's segment is the last thing its CTA does and
+// the contributions it needs are the first thing their CTAs do, so it hardly ever waits; the grid is launched
+// cooperatively (all CTAs resident), so it cannot wait for a CTA that has not started.
+// Flags carry a launch number that is unique in the process: nothing has to be cleared between launches.
+struct SplitPlan {
+  uint32_t share;        // K stages per CTA (<= KT)
+  uint32_t KT;           // K stages per tile
+  uint32_t units;        // tiles * KT
+  uint32_t token_tiles;  // tiles along the tokens (tile index = row tile * token_tiles + token tile)
+  unsigned long long epoch;
+  float *partials;               // [CTAs][512 / 32 token chunks][4 lane quadrants][8 pieces][32 lanes][4] fp32
+  unsigned long long *flags;     // [CTAs]
+};
+constexpr size_t SPLIT_PARTIAL_FLOATS = (size_t)TILE_N * 512;
+
+template <int FMT, bool OUT_F16>
+__global__ void __launch_bounds__(Cfg<FMT, 512, 1>::THREADS, 1)
+gemm_tc_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const uint8_t *__restrict__ qs, const __half *__restrict__ dsc,
+                      void *__restrict__ Cout, uint32_t M, uint32_t N, uint32_t K, const SplitPlan plan) {
+  using C = Cfg<FMT, 512, 1>;
+  constexpr int AU = C::AU, BS = C::BS, RS = C::RS, UPS = C::UPS, UNIT_BYTES = C::UNIT_BYTES, UNIT_ROWS = C::UNIT_ROWS;
+  constexpr int RAW_STAGE = C::RAW_STAGE, B_STAGE = C::B_STAGE, ROWS = C::ROWS, TN = 512;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t *a_units = smem;
+  uint8_t *b_tiles = a_units + AU * UNIT_BYTES;
+  uint8_t *raw = b_tiles + BS * B_STAGE;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(raw + RS * RAW_STAGE);
+  uint64_t *a_full = bars, *a_empty = bars + AU, *b_full = bars + 2 * AU, *b_empty = bars + 2 * AU + BS;
+  uint64_t *acc_full = bars + 2 * AU + 2 * BS, *acc_empty = bars + C::NBARS;  // one barrier more than the tiled kernel: the accumulator handed back
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + C::NBARS + 1);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t KT = plan.KT, nb = K / 32;
+  // this CTA's share [u0, u1) of the stage units, as at most two segments
+  const uint32_t u0 = min(blockIdx.x * plan.share, plan.units), u1 = min(u0 + plan.share, plan.units);
+  uint32_t seg_tile[2], seg_k0[2], seg_k1[2], nseg = 0;
+  for (uint32_t u = u0; u < u1;) {
+    const uint32_t tile = u / KT, k0 = u - tile * KT, k1 = min(KT, k0 + (u1 - u));
+    seg_tile[nseg] = tile;
+    seg_k0[nseg] = k0;
+    seg_k1[nseg] = k1;
+    ++nseg;
+    u += k1 - k0;
+  }
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < AU; ++s) {
+      mbar_init(&a_full[s], 1);
+      mbar_init(&a_empty[s], 1);
+    }
+    for (int s = 0; s < BS; ++s) {
+      mbar_init(&b_full[s], C::DEQ_THREADS / 32);
+      mbar_init(&b_empty[s], 1);
+    }
+    mbar_init(acc_full, 1);
+    mbar_init(acc_empty, C::DEQ_THREADS / 32);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      uint32_t u = 0, ph = 1, issued = 0;  // a fresh barrier passes a wait on parity 1
+      bool ok = true;
+      for (uint32_t sg = 0; sg < nseg && ok; ++sg) {
+        const uint32_t m0 = (seg_tile[sg] % plan.token_tiles) * TN;
+        for (uint32_t kt = seg_k0[sg]; kt < seg_k1[sg] && ok; ++kt) {
+#pragma unroll
+          for (int h = 0; h < UPS; ++h) {
+            ok = mbar_wait(&a_empty[u], ph, abort_flag, 100 + u);
+            if (!ok) break;
+            mbar_arrive_expect_tx(&a_full[u], UNIT_BYTES);
+            tma_load_2d(a_units + u * UNIT_BYTES, &tmap_a, (int)(kt * BK), (int)(m0 + h * UNIT_ROWS), &a_full[u]);
+            ++issued;
+            if (++u == AU) {
+              u = 0;
+              ph ^= 1;
+            }
+          }
+        }
+      }
+      if (*abort_flag) {  // give the copies still in flight a bounded chance to land before the CTA exits
+        for (uint32_t j = issued > (uint32_t)AU ? issued - AU : 0; j < issued; ++j) {
+          const long long t0 = clock64();
+          while (!mbar_try_wait(&a_full[j % AU], (j / AU) & 1) && clock64() - t0 < 20000000ll) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc_f16(TILE_N, UNIT_ROWS);
+      const uint32_t w_lo0 = smem_desc_lo(smem_u32(b_tiles)), a_lo0 = smem_desc_lo(smem_u32(a_units));
+      bool ok = true;
+      uint32_t s = 0, sph = 0, u = 0, uph = 0;
+      for (uint32_t sg = 0; sg < nseg && ok; ++sg) {
+        if (sg > 0) {  // the accumulator of the segment before has been read out
+          ok = mbar_wait(acc_empty, (sg - 1) & 1, abort_flag, 600);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        uint32_t acc = 0;
+        for (uint32_t kt = seg_k0[sg]; kt < seg_k1[sg] && ok; ++kt) {
+          ok = mbar_wait(&b_full[s], sph, abort_flag, 300 + s);
+          if (!ok) break;
+          const uint32_t w_lo = w_lo0 + s * (B_STAGE >> 4);
+#pragma unroll
+          for (int h = 0; h < UPS; ++h) {
+            ok = mbar_wait(&a_full[u], uph, abort_flag, 200 + u);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t a_lo = a_lo0 + u * (UNIT_BYTES >> 4);
+#pragma unroll
+            for (int k16 = 0; k16 < BK / 16; ++k16)
+              umma_f16(tmem_base + h * UNIT_ROWS, w_lo + k16 * 2, a_lo + k16 * 2, SMEM_DESC_HI_SW128, idesc, k16 == 0 ? acc : 1u);
+            umma_commit(&a_empty[u]);
+            if (++u == AU) {
+              u = 0;
+              uph ^= 1;
+            }
+          }
+          if (!ok) break;
+          umma_commit(&b_empty[s]);
+          acc = 1;
+          if (++s == BS) {
+            s = 0;
+            sph ^= 1;
+          }
+        }
+        if (ok) umma_commit(acc_full);
+      }
+    }
+  } else {
+    // ---------------- dequant warps; after each segment's stages, its epilogue ----------------
+    const int t = (int)threadIdx.x - 64;
+    const int row = t % ROWS, hb = t / ROWS;
+    const uint32_t row_off = row * 128;
+    const int quad = warp & 3, half = (warp - 2) >> 2;
+    bool ok = true;
+    uint32_t s = 0, sph = 1;
+    auto prologue = [&](uint32_t sg) {  // requests the first RS - 1 raw stages of segment sg
+      const uint32_t nr = min((seg_tile[sg] / plan.token_tiles) * ROWS + (uint32_t)row, N - 1);
+      const uint8_t *qr = qs + (size_t)nr * nb * (C::Q4 ? 16 : 32);
+      const __half *dr = dsc + (size_t)nr * d_row_stride(nb);
+#pragma unroll
+      for (int j = 0; j < RS - 1; ++j) {
+        if (seg_k0[sg] + j < seg_k1[sg]) raw_issue<C>(raw + j * RAW_STAGE, row, hb, qr, dr, seg_k0[sg] + j, nb);
+        cp_async_commit();
+      }
+    };
+    for (uint32_t sg = 0; sg < nseg && ok; ++sg) {
+      const uint32_t tile = seg_tile[sg], k0 = seg_k0[sg], k1 = seg_k1[sg];
+      const uint32_t n0 = (tile / plan.token_tiles) * ROWS, m0 = (tile % plan.token_tiles) * TN;
+      const uint32_t n_row = min(n0 + (uint32_t)row, N - 1);
+      const uint8_t *qs_row = qs + (size_t)n_row * nb * (C::Q4 ? 16 : 32);
+      const __half *d_row = dsc + (size_t)n_row * d_row_stride(nb);
+      if (sg == 0) prologue(0);  // a later segment's first stages were requested before the epilogue of the one before
+      uint32_t rs_load = RS - 1, rs_use = 0;
+      for (uint32_t kt = k0; kt < k1; ++kt) {
+        if (kt + RS - 1 < k1) raw_issue<C>(raw + rs_load * RAW_STAGE, row, hb, qs_row, d_row, kt + RS - 1, nb);
+        cp_async_commit();
+        cp_async_wait<RS - 1>();
+        uint4 chunk[4];
+        dequant_block<C>(raw + rs_use * RAW_STAGE, row, hb, 2 * kt + hb < nb, chunk);
+        ok = mbar_wait(&b_empty[s], sph, abort_flag, 400 + s);
+        if (!ok) break;
+        uint8_t *row_base = b_tiles + s * B_STAGE + row_off;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4 *>(row_base + (((4 * hb + c) ^ (row & 7)) << 4)) = chunk[c];
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&b_full[s]);
+        if (++s == BS) {
+          s = 0;
+          sph ^= 1;
+        }
+        if (++rs_load == RS) rs_load = 0;
+        if (++rs_use == RS) rs_use = 0;
+      }
+      cp_async_wait<0>();
+      if (!ok) break;
+      if (sg + 1 < nseg) prologue(sg + 1);  // travels while this segment's accumulator is read out
+      ok = mbar_wait(acc_full, sg & 1, abort_flag, 500);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t orow = n0 + quad * 32 + lane;
+      if (k0 > 0) {
+        // ---- contribution: the fp32 accumulator goes to this CTA's slot, then the flag
+        float *slot = plan.partials + (size_t)blockIdx.x * SPLIT_PARTIAL_FLOATS;
+        for (int c = half * (TN / 2); c < (half + 1) * (TN / 2); c += 32) {
+          if (m0 + c >= M) break;
+          uint32_t v[32];
+          tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + c, v);
+          tmem_ld_wait();
+          // piece j of lane l at 16-byte index j * 32 + l of the warp's 4 KB: every store instruction writes 512 contiguous bytes
+          uint4 *dst = reinterpret_cast<uint4 *>(slot + ((size_t)(c >> 5) * ROWS + quad * 32) * 32) + lane;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) dst[j * 32] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        }
+        __threadfence();
+        asm volatile("bar.sync 1, %0;" ::"n"(C::DEQ_THREADS) : "memory");
+        if (t == 0) {
+          asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(plan.flags + blockIdx.x), "l"(plan.epoch) : "memory");
+        }
+      } else {
+        // ---- this CTA stores the tile; when its stages end before the tile's K does, the rest comes from the CTAs after it
+        const bool staged = OUT_F16 && n0 + ROWS <= N && N % 8 == 0;
+        uint32_t first_c = 0, n_contrib = 0;  // contributors are CTAs blockIdx.x + 1 .. + n_contrib
+        if (k1 < KT) {
+          first_c = blockIdx.x + 1;
+          n_contrib = (KT - k1 + plan.share - 1) / plan.share;
+          if (t < (int)n_contrib) {  // one thread per contributor waits for its flag
+            const unsigned long long *f = plan.flags + first_c + t;
+            const long long t0 = clock64();
+            for (;;) {
+              unsigned long long got;
+              asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(got) : "l"(f) : "memory");
+              if (got == plan.epoch) break;
+              if (*abort_flag) break;
+              if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+                *abort_flag = 700;
+                atomicCAS(&g_gemm_error, 0, 700);
+                break;
+              }
+              __nanosleep(200);
+            }
+          }
+          asm volatile("bar.sync 1, %0;" ::"n"(C::DEQ_THREADS) : "memory");
+          if (*abort_flag) ok = false;
+        }
+        if (ok) {
+          for (int c = half * (TN / 2); c < (half + 1) * (TN / 2); c += 32) {
+            if (m0 + c >= M) break;
+            uint32_t v[32];
+            tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + c, v);
+            tmem_ld_wait();
+            for (uint32_t ci = 0; ci < n_contrib; ++ci) {  // ascending K order
+              const float4 *src = reinterpret_cast<const float4 *>(plan.partials + (size_t)(first_c + ci) * SPLIT_PARTIAL_FLOATS +
+                                                                   ((size_t)(c >> 5) * ROWS + quad * 32) * 32) + lane;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float4 a = __ldcg(src + j * 32);
+                v[4 * j] = __float_as_uint(__uint_as_float(v[4 * j]) + a.x);
+                v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + a.y);
+                v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + a.z);
+                v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + a.w);
+              }
+            }
+            if (staged) {
+              __half *tile_h = reinterpret_cast<__half *>(smem) + (size_t)c * ROWS + quad * 32 + lane;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) tile_h[(size_t)j * ROWS] = __float2half_rn(__uint_as_float(v[j]));
+            } else if (orow < N) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const uint32_t m = m0 + c + j;
+                if (m < M) {
+                  if (OUT_F16)
+                    reinterpret_cast<__half *>(Cout)[(size_t)m * N + orow] = __float2half_rn(__uint_as_float(v[j]));
+                  else
+                    reinterpret_cast<float *>(Cout)[(size_t)m * N + orow] = __uint_as_float(v[j]);
+                }
+              }
+            }
+          }
+        }
+        if (staged) {  // the segment that stores a tile is the CTA's last: the rings are idle
+          asm volatile("bar.sync 1, %0;" ::"n"(C::DEQ_THREADS) : "memory");
+          if (ok) {
+            constexpr uint32_t PIECES_PER_TOKEN = ROWS / 8;
+            const uint32_t tokens = min((uint32_t)TN, M - m0);
+            for (uint32_t piece = t; piece < tokens * PIECES_PER_TOKEN; piece += C::DEQ_THREADS) {
+              const uint32_t tok = piece / PIECES_PER_TOKEN, off = piece % PIECES_PER_TOKEN;
+              const uint4 val = *reinterpret_cast<const uint4 *>(smem + ((size_t)tok * ROWS + off * 8) * 2);
+              *reinterpret_cast<uint4 *>(reinterpret_cast<__half *>(Cout) + (size_t)(m0 + tok) * N + n0 + off * 8) = val;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TN);
+  }
+}
+
 // ---- host side ---------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
@@ -824,6 +1139,68 @@ int launch_tc(cudaStream_t stream, const CUtensorMap &map, const void *qs, const
   dim3 grid((N + Cf::ROWS - 1) / Cf::ROWS, (M + TN - 1) / TN);
   gemm_tc_kernel<FMT, TN, RT, OUT_F16><<<grid, Cf::THREADS, Cf::SMEM, stream>>>(map, (const uint8_t *)qs, (const __half *)d, C, M, N, K);
   return launched("gemm_tc_kernel");
+}
+
+void pick_tile(uint32_t M, uint32_t N, int *tn, int *rt);
+
+size_t split_scratch_bytes() {
+  const size_t ctas = (size_t)sm_count();
+  return (ctas * SPLIT_PARTIAL_FLOATS * 4 + ctas * 8 + 255) / 256 * 256;
+}
+unsigned long long next_split_epoch() {
+  static std::atomic<unsigned long long> counter{0};
+  static const unsigned long long base = ((unsigned long long)std::chrono::steady_clock::now().time_since_epoch().count() << 16) | 1ull;
+  return base + counter.fetch_add(1);
+}
+
+// Whether the split over K pays for this shape, and the plan if so: 512-token tiles, fewer tiles than SMs (or not many
+// more: above that the tiled kernel's waves are full enough), shares of at least 8 stages.
+bool plan_splitk(uint32_t M, uint32_t N, uint32_t K, SplitPlan *pl, uint32_t *ctas) {
+  const uint32_t row_tiles = (N + TILE_N - 1) / TILE_N, token_tiles = (M + 511) / 512, tiles = row_tiles * token_tiles;
+  const uint32_t KT = (K + BK - 1) / BK, sms = (uint32_t)sm_count();
+  if (M <= 256 || M % 512 > 0 && M % 512 <= 256) return false;  // a token tile that is mostly padding
+  if (tiles >= sms || (uint64_t)tiles * KT >= (1ull << 31)) return false;
+  const uint32_t units = tiles * KT;
+  uint32_t share = (units + sms - 1) / sms;
+  if (share < 8) share = 8;
+  if (share > KT) return false;
+  // Worth it?  In units of one 512-token stage: the tiled kernel needs waves * KT stages of its tile width (a 256-token
+  // stage costs about 0.8 of a 512-token one, a 128-token stage 0.66: the issuing thread, not the tensor core, sets
+  // their pace), the split needs one share plus about 24 stages' worth of partial sums, flags and a second pipeline start
+  // (measured: 11008 x 4096 at 512 tokens 48.7 vs 50.3 us, 4096 x 11008 55 vs 83, 12288 x 4096 52.1 vs 51.1).
+  int tn = 128, rt = 1;
+  pick_tile(M, N, &tn, &rt);
+  const uint32_t tile_ctas = ((N + TILE_N * rt - 1) / (TILE_N * rt)) * ((M + tn - 1) / tn);
+  const double per_stage = tn == 512 ? 1.0 : (tn == 256 ? 0.8 : 0.66);
+  if (share + 24.0 >= (double)((tile_ctas + sms - 1) / sms) * KT * per_stage * rt) return false;
+  pl->share = share;
+  pl->KT = KT;
+  pl->units = units;
+  pl->token_tiles = token_tiles;
+  *ctas = (units + share - 1) / share;
+  return *ctas <= sms;
+}
+
+template <int FMT, bool OUT_F16>
+int launch_splitk(cudaStream_t stream, const CUtensorMap &map, const void *qs, const void *d, void *C, uint32_t M, uint32_t N, uint32_t K,
+                  SplitPlan plan, uint32_t ctas, void *scratch) {
+  using Cf = Cfg<FMT, 512, 1>;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    GRETA_CUDA_TRY(cudaFuncSetAttribute(gemm_tc_splitk_kernel<FMT, OUT_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cf::SMEM));
+    attr_set[dev] = true;
+  }
+  plan.partials = static_cast<float *>(scratch);
+  plan.flags = reinterpret_cast<unsigned long long *>(static_cast<uint8_t *>(scratch) + (size_t)sm_count() * SPLIT_PARTIAL_FLOATS * 4);
+  plan.epoch = next_split_epoch();
+  const uint8_t *qs8 = static_cast<const uint8_t *>(qs);
+  const __half *d16 = static_cast<const __half *>(d);
+  void *args[] = {(void *)&map, (void *)&qs8, (void *)&d16, (void *)&C, (void *)&M, (void *)&N, (void *)&K, (void *)&plan};
+  // cooperative: every CTA is resident, so a tile's owner never waits for a CTA that has not started
+  GRETA_CUDA_TRY(cudaLaunchCooperativeKernel((const void *)gemm_tc_splitk_kernel<FMT, OUT_F16>, dim3(ctas), dim3(Cf::THREADS), args, Cf::SMEM, stream));
+  return launched("gemm_tc_splitk_kernel");
 }
 
 template <int FMT, int UPS, bool OUT_F16>
@@ -883,7 +1260,7 @@ void pick_tile(uint32_t M, uint32_t N, int *tn, int *rt) {
 
 extern "C" {
 
-size_t greta_cuda_gemm_workspace_bytes(uint32_t M, uint32_t K) { return ((size_t)M * K * 2 + 255) / 256 * 256; }
+size_t greta_cuda_gemm_workspace_bytes(uint32_t M, uint32_t K) { return split_scratch_bytes() + ((size_t)M * K * 2 + 255) / 256 * 256; }
 
 int greta_cuda_gemm_status(int *code) {
   GRETA_REQUIRE(code, "gemm_status: null out pointer");
@@ -902,8 +1279,9 @@ int greta_cuda_gemm(greta_stream_t stream, int fmt, const void *A, int a_is_f16,
   const void *a16 = A;
   if (!a_is_f16) {
     GRETA_REQUIRE(workspace && aligned16(workspace), "gemm: fp32 activations need a workspace of greta_cuda_gemm_workspace_bytes(M, K)");
-    if (int rc = greta_cuda_f32_to_f16(stream, static_cast<const float *>(A), workspace, (size_t)M * K)) return rc;
-    a16 = workspace;
+    void *a_area = static_cast<uint8_t *>(workspace) + split_scratch_bytes();  // the front of the workspace is the split-K scratch
+    if (int rc = greta_cuda_f32_to_f16(stream, static_cast<const float *>(A), a_area, (size_t)M * K)) return rc;
+    a16 = a_area;
   }
   EncodeTiledFn enc = encode_tiled();
   if (!enc) {
@@ -914,16 +1292,27 @@ int greta_cuda_gemm(greta_stream_t stream, int fmt, const void *A, int a_is_f16,
   pick_tile(M, N, &tn, &rt);
   // 512-token tiles run as CTA pairs unless a tile shape is forced or the switch is off (2: always, whatever the shape)
   const bool pair = tuning().gemm_pair == 2 || (tuning().gemm_pair == 1 && tn == 512 && rt == 1 && tuning().gemm_tile_tokens == 0);
+  SplitPlan splan;
+  uint32_t split_ctas = 0;
+  const bool split = tuning().gemm_splitk && !pair && workspace && aligned16(workspace) && tuning().gemm_tile_tokens == 0 &&
+                     plan_splitk(M, N, K, &splan, &split_ctas);
   const cuuint64_t dims[2] = {K, M};
   CUtensorMap map;
   const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-  const cuuint32_t box[2] = {BK, (tn >= 256 && !pair) ? 256u : 128u};
+  const cuuint32_t box[2] = {BK, ((tn >= 256 && !pair) || split) ? 256u : 128u};
   const cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(a16), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     set_error("gemm: cuTensorMapEncodeTiled failed with code %d", (int)r);
     return GRETA_ERR_INVALID_ARGS;
+  }
+  if (split) {
+    if (fmt == GRETA_FMT_Q4_0)
+      return c_is_f16 ? launch_splitk<GRETA_FMT_Q4_0, true>(s, map, qs, d, Cout, M, N, K, splan, split_ctas, workspace)
+                      : launch_splitk<GRETA_FMT_Q4_0, false>(s, map, qs, d, Cout, M, N, K, splan, split_ctas, workspace);
+    return c_is_f16 ? launch_splitk<GRETA_FMT_Q8_0, true>(s, map, qs, d, Cout, M, N, K, splan, split_ctas, workspace)
+                    : launch_splitk<GRETA_FMT_Q8_0, false>(s, map, qs, d, Cout, M, N, K, splan, split_ctas, workspace);
   }
   if (pair) {
     if (fmt == GRETA_FMT_Q4_0)

@@ -73,6 +73,8 @@ Tuning &tuning() {
     v.peer_two_level_min_tp = e ? atoi(e) : 4;
     e = getenv("GRETA_SKINNY_MAX_ROWS");
     v.skinny_max_rows = e ? atoi(e) : 32;
+    e = getenv("GRETA_GEMM_SPLITK");
+    v.gemm_splitk = (e && e[0] == '1') ? 1 : 0;
     e = getenv("GRETA_GEMM_PAIR");
     v.gemm_pair = (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 0;
     return v;
@@ -129,6 +131,8 @@ int greta_cuda_set_tuning(const char *name, long long value) {
   } else if (!strcmp(name, "skinny_max_rows")) {
     GRETA_REQUIRE(value >= 1 && value <= 32, "set_tuning: skinny_max_rows=%lld outside 1..32", value);
     t.skinny_max_rows = (int)value;
+  } else if (!strcmp(name, "gemm_splitk")) {
+    t.gemm_splitk = value != 0;
   } else if (!strcmp(name, "gemm_pair")) {
     GRETA_REQUIRE(value >= 0 && value <= 2, "set_tuning: gemm_pair=%lld outside 0..2", value);
     t.gemm_pair = (int)value;

@@ -120,7 +120,9 @@ GRETA_API int greta_cuda_set_pdl(int on);
  *   consumer spends on one missing partial before it gives up, default 2^22), "attn_mma" (GRETA_ATTN_MMA, 0/1: prefill and grouped-query batched decode
  *   attention on the tensor cores), "peer_two_level_min_tp"
  *   (GRETA_PEER_TWO_LEVEL_MIN_TP: ranks from which an exchange consumer gathers in two levels, default 4), "skinny_max_rows"
- *   (GRETA_SKINNY_MAX_ROWS, 1..32), "gemm_pair" (GRETA_GEMM_PAIR: 1 = prefill GEMMs that take 512-token tiles
+ *   (GRETA_SKINNY_MAX_ROWS, 1..32), "gemm_splitk" (GRETA_GEMM_SPLITK, 0/1, default 0: a prefill GEMM with fewer 512-token tiles than
+ *   SMs shares each tile's K loop between CTAs where that is predicted to pay; needs the workspace; the partial sums change the
+ *   fp32 summation order, deterministically), "gemm_pair" (GRETA_GEMM_PAIR: 1 = prefill GEMMs that take 512-token tiles
  *   run as pairs of CTAs sharing one two-CTA tensor-core instruction, 2 = every GEMM does, 0 = none). */
 GRETA_API int greta_cuda_set_tuning(const char *name, long long value);
 /* Number of kernel launches this library has issued on the calling process (all threads). */
@@ -282,8 +284,11 @@ GRETA_API int greta_cuda_decode_trace(const void *plan, long long *out25);
  * tensor cores (tcgen05, TMEM accumulators); A fp32 or fp16, C fp32 or fp16.
  * Replaces the M > 32 route: gemm_mfma_int4_wt_kernel / gemm_mfma_int8_wt_kernel
  * (gemm_kernels.hip:820-908, 640-740) with the row-major contraction.
- * workspace: device scratch of greta_cuda_gemm_workspace_bytes(M, K) bytes, used
- * for the fp16 copy of A when A is fp32 (may be NULL when a_is_f16). */
+ * workspace: device scratch of greta_cuda_gemm_workspace_bytes(M, K) bytes: room for the partial sums of a K loop
+ * shared between CTAs (one 128 x 512 fp32 tile per SM, used when the product has fewer 512-token tiles than the GPU has
+ * SMs) followed by the fp16 copy of A when A is fp32.  May be NULL when a_is_f16: the product is then computed with
+ * fixed tiles only.  Its contents need not be initialised or kept; two products that may run at the same time
+ * (different streams) need a workspace each. */
 GRETA_API size_t greta_cuda_gemm_workspace_bytes(uint32_t M, uint32_t K);
 /* Every wait inside the GEMM kernel is bounded; if one ever gives up the kernel drains, frees its tensor
  * memory and records a non-zero code (100 * role + stage) that this call returns in *code (0 = none).

@@ -662,6 +662,44 @@ def test_gemm_cta_pairs(g, tuning, name, M, N, K, c_f16):
     assert max_abs_rel(O.f16_bits_to_f32(two) if c_f16 else two, O.f16_bits_to_f32(one) if c_f16 else one) < 1e-6
 
 
+@pytest.mark.parametrize("name,M,N,K,a_f16,c_f16", [("q4_0", 512, 1280, 4096, True, True), ("q8_0", 512, 384, 1376, True, False),
+                                                    ("q4_0", 1024, 256, 8192, False, False), ("q4_0", 900, 640, 2048, True, True),
+                                                    ("q8_0", 512, 1000, 1024, False, True), ("q4_0", 600, 300, 2048, True, False)])
+def test_gemm_split_over_k(g, tuning, name, M, N, K, a_f16, c_f16):
+    """With fewer 512-token tiles than SMs the K loop of a tile is shared between CTAs: partial sums through the workspace,
+    added in ascending K order by the CTA that owns the tile.  Tiles cut into up to eight parts, two token tiles, ragged rows and
+    tokens, an odd number of blocks in K, fp32 activations converted into the same workspace, and a shape the plan declines
+    (600 tokens: the second token tile would be mostly padding), which must still come out right through the tiled kernel."""
+    tuning("gemm_splitk", 1, restore=0)
+    ofmt, gfmt = FMTS[name]
+    rng = np.random.default_rng(1400 + M + N)
+    blk = make_blocks(rng, ofmt, N, K)
+    a = rng.normal(0, 1, (M, K)).astype(np.float32)
+    a_in = a.astype(np.float16).view(np.uint16) if a_f16 else a
+    w = g.Weight(blk, gfmt, N, K)
+    ws = g.DeviceBuffer(g.cuda().greta_cuda_gemm_workspace_bytes(M, K))
+    _KEEP.append(ws)
+    ws.fill(0xEE)                                   # stale bytes in the partial slots and flags must not matter
+    c = g.DeviceBuffer(M * N * (2 if c_f16 else 4))
+    _KEEP.append(c)
+    for rep in range(2):                            # the second launch meets the first launch's flags
+        c.fill(0xFF)
+        g.check(g.cuda().greta_cuda_gemm(None, gfmt, _dev(g, a_in).ptr, int(a_f16), w.qs.ptr, w.d.ptr, c.ptr, int(c_f16), M, N, K, ws.ptr))
+        g.check(g.cuda().greta_cuda_device_synchronize())
+        assert _gemm_status(g) == 0
+        if c_f16:
+            got = O.f16_bits_to_f32(c.download(np.uint16)).reshape(M, N)
+            want = O.f16_bits_to_f32(O.gemm(a_in, blk, ofmt, N, K, out_f16=True))
+            bar = 1.5e-3
+        else:
+            got = c.download(np.float32).reshape(M, N)
+            want = O.gemm(a_in, blk, ofmt, N, K)
+            bar = 1e-4
+        assert np.isfinite(got).all()
+        err = max_abs_rel(got, want)
+        assert err < bar, (rep, err)
+
+
 def test_gemm_rejects_what_it_cannot_do(g):
     lib = g.cuda()
     buf = g.DeviceBuffer(1 << 16)
