@@ -657,12 +657,12 @@ def main():
         idbuf = C.create_string_buffer(raw, 128)
         g.check(lib.greta_cuda_comm_init(C.byref(comm), idbuf, tp, ranks.rank), "comm_init")
         model.set_comm(comm)
-        if B > 1:
-            args.exchange = "nccl (a batch uses the all-reduce)"
-        elif args.exchange == "fused":
-            peer_keep = pkg.rendezvous.install_peer_exchange(model, ranks, cfg["dim"])
+        if args.exchange == "fused":
+            peer_keep = pkg.rendezvous.install_peer_exchange(model, ranks, cfg["dim"], batch=B)
             if peer_keep is None:
                 args.exchange = "nccl (peer memory could not be mapped)"
+            elif B > 1:
+                args.exchange = "all-reduce over peer memory (one kernel per rank)"
     model.load_synthetic(SEED if args.workload == "c4" else 4)
     seed = SEED if args.workload == "c4" else 4
     prompts = [pkg.model.synth_tokens(seed, args.prompt_len, cfg["vocab"], stream=(1 << 40) + b) for b in range(B)]

@@ -476,6 +476,78 @@ int dispatch_peer(cudaStream_t stream, int fmt, const GemvParams &p, uint64_t to
   return GRETA_ERR_INVALID_ARGS;
 }
 
+// ---- all-reduce over peer memory (a batch of sequences) ---------------------------------------------
+// In-place sum over the ranks of `count` floats, as one kernel per rank and no collective launch.  Three phases
+// over {value, tag} words in the ranks' slot buffers (the tag travels with the value: no flag, no fence):
+//   A  every rank stores slice j of its vector into region A of rank j's buffer (row `rank` of [tp][count / tp]);
+//   B  every rank sums the tp rows of its own slice in rank order (bounded waits on the tags) and stores the sums
+//      into region B ([count]) of every rank's buffer: all ranks receive the same bits;
+//   C  every rank waits for the count words of its region B and writes the values back to x.
+// Two sets of regions alternate with the parity of exch_idx, which is enough: a rank can be at most one all-reduce
+// ahead of another, because it cannot finish one without every rank's contribution to it.  The tag is
+// ((*d_pos + 1) << 8) | exch_idx, read on the device, so a captured decode step replays with fresh tags.
+struct PeerArParams {
+  float *x;
+  uint32_t count, tp, rank, exch_idx;
+  const uint32_t *d_pos;
+  uint2 *slots[MAX_TP];
+  unsigned poll_limit;
+};
+
+__device__ __forceinline__ uint2 wait_tagged(const uint2 *src, uint32_t tag, uint32_t budget) {
+  uint2 w = ld_peer8(src);
+  uint32_t polls = 0;
+  while (w.y != tag) {
+    if (++polls > budget || ((polls & 255u) == 0 && peer_failed())) {
+      g_peer_error = 1;
+      break;
+    }
+    w = ld_peer8(src);
+  }
+  return w;
+}
+
+__global__ void __launch_bounds__(256) peer_allreduce_kernel(const PeerArParams p) {
+  pdl_launch_dependents();
+  pdl_wait();  // x comes from the kernel in front
+  const uint32_t tag = ((__ldcg(p.d_pos) + 1u) << 8) | p.exch_idx;
+  const uint32_t slice = p.count / p.tp, nthreads = gridDim.x * blockDim.x, gtid = blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t set = (size_t)(p.exch_idx & 1u) * 2u * p.count;  // words: region A, then region B
+  const uint32_t budget = peer_failed() ? 0u : p.poll_limit;
+  // A: scatter the slices
+  for (uint32_t i = gtid; i < p.count; i += nthreads) {
+    const uint32_t owner = i / slice, e = i - owner * slice;
+    st_peer(p.slots[owner] + set + (size_t)p.rank * slice + e, make_uint2(__float_as_uint(__ldcg(p.x + i)), tag));
+  }
+  // B: sum this rank's slice, publish it everywhere
+  const uint2 *mine = p.slots[p.rank] + set;
+  for (uint32_t e = gtid; e < slice; e += nthreads) {
+    uint2 w[MAX_TP];
+#pragma unroll
+    for (int r = 0; r < MAX_TP; ++r)
+      if ((uint32_t)r < p.tp) w[r] = ld_peer8(mine + (size_t)r * slice + e);  // all rows in flight before any tag is looked at
+    float v = 0.f;
+#pragma unroll
+    for (int r = 0; r < MAX_TP; ++r) {
+      if ((uint32_t)r < p.tp) {
+        if (w[r].y != tag) w[r] = wait_tagged(mine + (size_t)r * slice + e, tag, budget);
+        v += __uint_as_float(w[r].x);
+      }
+    }
+    const uint2 out = make_uint2(__float_as_uint(v), tag);
+#pragma unroll
+    for (int j = 0; j < MAX_TP; ++j)
+      if ((uint32_t)j < p.tp) st_peer(p.slots[j] + set + p.count + (size_t)p.rank * slice + e, out);
+  }
+  // C: collect
+  const uint2 *sums = mine + p.count;
+  for (uint32_t i = gtid; i < p.count; i += nthreads) {
+    uint2 w = ld_peer8(sums + i);
+    if (w.y != tag) w = wait_tagged(sums + i, tag, budget);
+    p.x[i] = __uint_as_float(w.x);
+  }
+}
+
 int fill_exchange(GemvParams &p, const greta_peer_exchange *ex, uint32_t exch_idx, const uint32_t *d_pos, uint32_t dim, bool as_producer) {
   GRETA_REQUIRE(ex && d_pos, "tensor-parallel exchange: null exchange descriptor or position");
   GRETA_REQUIRE(ex->tp >= 1 && ex->tp <= (uint32_t)MAX_TP && ex->rank < ex->tp, "tensor-parallel exchange: rank %u of %u", ex->rank, ex->tp);
@@ -745,6 +817,34 @@ int greta_cuda_fused_ffn_front_peer(greta_stream_t stream, int fmt, const float 
   p.y = y;
   if (int rc = fill_exchange(p, ex, exch_idx, d_pos, D, false)) return rc;
   return dispatch_peer<EPI_SWIGLU, true>((cudaStream_t)stream, fmt, p, (uint64_t)2 * F);
+}
+
+size_t greta_cuda_peer_allreduce_slot_bytes(size_t max_count) { return (size_t)4 * max_count * sizeof(uint2); }
+
+int greta_cuda_peer_allreduce_f32(greta_stream_t stream, float *x, size_t count, const greta_peer_exchange *ex, uint32_t exch_idx,
+                                  const uint32_t *d_pos) {
+  GRETA_REQUIRE(ex && d_pos && x, "peer_allreduce: null pointer");
+  GRETA_REQUIRE(ex->tp >= 1 && ex->tp <= (uint32_t)MAX_TP && ex->rank < ex->tp, "peer_allreduce: rank %u of %u", ex->rank, ex->tp);
+  GRETA_REQUIRE(exch_idx < 256, "peer_allreduce: index %u out of range (256 per step)", exch_idx);
+  GRETA_REQUIRE(count > 0 && count % ex->tp == 0 && count < (1u << 28), "peer_allreduce: %zu values do not split over %u ranks", count, ex->tp);
+  GRETA_REQUIRE(ex->slot_bytes >= greta_cuda_peer_allreduce_slot_bytes(count), "peer_allreduce: slot buffers of %zu bytes are too small for %zu values",
+                (size_t)ex->slot_bytes, count);
+  PeerArParams p{};
+  p.x = x;
+  p.count = (uint32_t)count;
+  p.tp = ex->tp;
+  p.rank = ex->rank;
+  p.exch_idx = exch_idx;
+  p.d_pos = d_pos;
+  for (uint32_t j = 0; j < ex->tp; ++j) {
+    GRETA_REQUIRE(ex->slots[j] && aligned16(ex->slots[j]), "peer_allreduce: slot buffer %u is null or misaligned", j);
+    p.slots[j] = static_cast<uint2 *>(ex->slots[j]);
+  }
+  p.poll_limit = tuning().peer_poll_limit;
+  // enough threads to have every word of a phase in flight at once, not more CTAs than SMs
+  const unsigned ctas = (unsigned)std::min<size_t>((count / ex->tp + 255) / 256, (size_t)sm_count());
+  GRETA_CUDA_TRY(launch_pdl(peer_allreduce_kernel, dim3(ctas ? ctas : 1), dim3(256), 0, (cudaStream_t)stream, p));
+  return launched("peer_allreduce_kernel");
 }
 
 }  // extern "C"

@@ -375,7 +375,10 @@ bool BlockScheduler::set_peer_exchange(const greta_peer_exchange &ex, std::strin
   if (c.dim > 8192 || 2 * c.num_layers > 256) return fail(err, "set_peer_exchange: model too large for the exchange tags");
   if (!all_reduce_) return fail(err, "set_peer_exchange: install the all-reduce hook first (barriers, last layer, logits)");
   if (!x_alt_.allocate((size_t)c.dim * 4, BufferUsage::DeviceOnly, GretaDataType::FP32, err)) return false;
+  const size_t least = greta_cuda_peer_slot_bytes(ex.tp, c.dim);
+  if (ex.slot_bytes != 0 && ex.slot_bytes < least) return fail(err, "set_peer_exchange: slot buffers are smaller than greta_cuda_peer_slot_bytes(tp, dim)");
   peer_ = ex;
+  if (peer_.slot_bytes == 0) peer_.slot_bytes = least;
   invalidate_graph();  // a captured step holds the old exchange's pointers
   return true;
 }
@@ -505,6 +508,9 @@ bool BlockScheduler::decode_layers_batch(std::string *err) {
   float *gate = static_cast<float *>(a.mlp_gate.data());
   const bool tp = c.tp_size > 1, fold = !tp || c.tp_rank == 0;  // one rank folds the residual in, the others contribute bare partials
   void *ws = batch_ws_.data();  // prepared activations of the operator in flight (one buffer serves them all: stream order)
+  // With slot buffers large enough for [batch x dim] the sums over the ranks go through peer memory (one kernel per rank);
+  // the logits gather and the prefill keep the all-reduce hook, which also separates one step's exchanges from the next's.
+  const bool peer_ar = tp && peer_.tp == c.tp_size && peer_.slot_bytes >= greta_cuda_peer_allreduce_slot_bytes((size_t)B * D) && 2 * c.num_layers <= 256;
   for (uint32_t l = 0; l < c.num_layers; ++l) {
     BlockBuffers &b = blocks_[l];
     uint16_t *kc = static_cast<uint16_t *>(a.kv_cache_k.data()) + l * cache_l;
@@ -517,12 +523,20 @@ bool BlockScheduler::decode_layers_batch(std::string *err) {
                                            a.attn_scratch.size()),
               "attention decode (batch)");
     GRETA_TRY(greta_cuda_gemv_batch(s, fmt, att, nullptr, 0.f, b.wo.data(), b.s_wo.data(), fold ? x : nullptr, x, B, D, ql, 0, ws), "wo (batch)");
-    if (tp && all_reduce_(x, (size_t)B * D, s) != 0) return fail(err, "all-reduce after the O-projection failed");
+    if (peer_ar) {
+      GRETA_TRY(greta_cuda_peer_allreduce_f32(s, x, (size_t)B * D, &peer_, 2 * l, dpos), "exchange after the O-projection");
+    } else if (tp && all_reduce_(x, (size_t)B * D, s) != 0) {
+      return fail(err, "all-reduce after the O-projection failed");
+    }
     GRETA_TRY(greta_cuda_fused_ffn_front_batch(s, fmt, x, static_cast<const float *>(b.ffn_norm.data()), c.rms_eps, b.w1.data(), b.s_w1.data(),
                                                b.w3.data(), b.s_w3.data(), gate, B, D, hidden_l_, ws),
               "ffn front (batch)");
     GRETA_TRY(greta_cuda_gemv_batch(s, fmt, gate, nullptr, 0.f, b.w2.data(), b.s_w2.data(), fold ? x : nullptr, x, B, D, hidden_l_, 0, ws), "w2 (batch)");
-    if (tp && all_reduce_(x, (size_t)B * D, s) != 0) return fail(err, "all-reduce after the down-projection failed");
+    if (peer_ar) {
+      GRETA_TRY(greta_cuda_peer_allreduce_f32(s, x, (size_t)B * D, &peer_, 2 * l + 1, dpos), "exchange after the down-projection");
+    } else if (tp && all_reduce_(x, (size_t)B * D, s) != 0) {
+      return fail(err, "all-reduce after the down-projection failed");
+    }
   }
   return true;
 }
@@ -705,7 +719,7 @@ bool BlockScheduler::begin_decode_batch(const int32_t *first_tokens, const uint3
     // Exchange tags grow with the position: a session that restarts earlier must not meet the tags of the
     // last one.  Every rank clears its slots, then a collective keeps anyone from storing into a buffer
     // that is still being cleared.
-    GRETA_TRY(greta_cuda_memset(peer_.slots[peer_.rank], 0, greta_cuda_peer_slot_bytes(peer_.tp, config_.dim), s), "exchange reset");
+    GRETA_TRY(greta_cuda_memset(peer_.slots[peer_.rank], 0, (size_t)peer_.slot_bytes, s), "exchange reset");
     if (all_reduce_(static_cast<float *>(logits_.data()), 1, s) != 0) return fail(err, "begin_decode: barrier failed");
     GRETA_TRY(greta_cuda_stream_synchronize(s), "begin_decode");
   }
@@ -725,7 +739,6 @@ bool BlockScheduler::begin_decode_batch(const int32_t *first_tokens, const uint3
     bool ok;
     const float *x_last = static_cast<const float *>(a.x.data());
     if (batch_ > 1) {
-      if (peer_.tp > 1) return fail(err, "begin_decode: the fused exchange serves one sequence; a batch uses the all-reduce hook");
       ok = greta_cuda_embedding(s, static_cast<const int32_t *>(a.d_next.data()), token_embd_.data(), 1, static_cast<float *>(a.x.data()), batch_,
                                 c.dim, c.vocab_size) == GRETA_OK;
       if (ok && c.tp_size > 1) ok = greta_cuda_memset(logits_.data(), 0, logits_.size(), s) == GRETA_OK;

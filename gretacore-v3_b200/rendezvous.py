@@ -91,7 +91,7 @@ class Ranks:
         return [blob[i * n:(i + 1) * n] for i in range(self.world)]
 
 
-def install_peer_exchange(mdl, ranks, dim):
+def install_peer_exchange(mdl, ranks, dim, batch=1):
     """Sets up the fused tensor-parallel exchange: every rank allocates its slot buffer, the processes swap the
     64-byte IPC handles over the rendezvous sockets, map each other's buffers and hand the table to the model.
     Returns the objects that must stay alive (local buffer, descriptor, mapped pointers), or None - on every rank
@@ -101,7 +101,10 @@ def install_peer_exchange(mdl, ranks, dim):
     lib = g.cuda()
     local, handle, ok = None, C.create_string_buffer(64), True
     try:
-        local = g.DeviceBuffer(lib.greta_cuda_peer_slot_bytes(ranks.world, dim), zero=True)
+        nbytes = lib.greta_cuda_peer_slot_bytes(ranks.world, dim)
+        if batch > 1:                                                 # room for the all-reduce of [batch x dim] through peer memory
+            nbytes = max(nbytes, lib.greta_cuda_peer_allreduce_slot_bytes(batch * dim))
+        local = g.DeviceBuffer(nbytes, zero=True)
         g.check(lib.greta_cuda_ipc_export(local.ptr, handle), "ipc_export")
     except Exception as e:                                            # noqa: BLE001 - reported, then agreed on by all ranks
         print(f"rank {ranks.rank}: peer exchange unavailable: {e}", file=sys.stderr)
@@ -110,7 +113,7 @@ def install_peer_exchange(mdl, ranks, dim):
     if not all(h[64:] == b"\1" for h in got):
         return None
     ex = model.PeerExchange()
-    ex.tp, ex.rank = ranks.world, ranks.rank
+    ex.tp, ex.rank, ex.slot_bytes = ranks.world, ranks.rank, nbytes
     mapped = []
     try:
         for r, h in enumerate(got):

@@ -437,13 +437,23 @@ GRETA_API int greta_cuda_comm_allreduce_f32(void *comm, float *buf, size_t count
  * a collective.  A wait that gives up sets a status word (greta_cuda_peer_status) and uses what it has.
  * Slot buffers are plain device allocations shared between the processes with the ipc calls below. */
 typedef struct greta_peer_exchange {
-  uint32_t tp, rank; /* ranks of the group (<= 8), this rank */
-  void *slots[8];    /* slot buffer of every rank, greta_cuda_peer_slot_bytes(tp, dim) each; slots[rank] is local */
+  uint32_t tp, rank;   /* ranks of the group (<= 8), this rank */
+  void *slots[8];      /* slot buffer of every rank, the same size on all; slots[rank] is local */
+  uint64_t slot_bytes; /* size of each slot buffer: at least greta_cuda_peer_slot_bytes(tp, dim); greta_cuda_peer_allreduce_f32
+                          wants greta_cuda_peer_allreduce_slot_bytes(count).  0 is read as greta_cuda_peer_slot_bytes(tp, dim). */
 } greta_peer_exchange;
 GRETA_API size_t greta_cuda_peer_slot_bytes(uint32_t tp, uint32_t dim);
 GRETA_API int greta_cuda_peer_status(int *code);
 /* Clears the status word (on `stream`): after a time-out every later wait gives up at once until this is called. */
 GRETA_API int greta_cuda_peer_reset(greta_stream_t stream);
+/* In-place sum of `count` floats over the ranks through the slot buffers: one kernel per rank, no collective launch
+ * (scatter of slices, sum in rank order by the slice's owner, gather; every rank receives the same bits).  Meant for
+ * the [batch x dim] partial products of a batch of sequences, where the exchange cannot ride in a GEMV epilogue; count must
+ * divide by tp.  Tags and the alternation of exch_idx parity as above; d_pos points at the first sequence's position.
+ * Waits are bounded like those of the fused exchange (greta_cuda_peer_status). */
+GRETA_API size_t greta_cuda_peer_allreduce_slot_bytes(size_t max_count);
+GRETA_API int greta_cuda_peer_allreduce_f32(greta_stream_t stream, float *x, size_t count, const greta_peer_exchange *ex, uint32_t exch_idx,
+                                            const uint32_t *d_pos);
 GRETA_API int greta_cuda_ipc_export(void *device_ptr, void *handle64);         /* 64-byte handle of a greta_cuda_malloc block */
 GRETA_API int greta_cuda_ipc_open(const void *handle64, void **device_ptr);    /* maps another process's block */
 GRETA_API int greta_cuda_ipc_close(void *device_ptr);

@@ -1,7 +1,7 @@
 """One rank of the tensor-parallel check (launched by test_tp_gpu.py under torch.distributed.run).
 Each rank holds its shard of a small Llama-shaped model and runs prefill + greedy decode twice: with the NCCL
 all-reduce, and with the exchange fused into the GEMV kernels over peer memory; then a batch of five sequences
-decoding in step, then a model loaded from a K-quant file; rank 0 compares all ids with the CPU oracle's and reads the
+decoding in step (NCCL all-reduce, then the all-reduce through peer memory), then a model loaded from a K-quant file; rank 0 compares all ids with the CPU oracle's and reads the
 exchange's time-out status."""
 import ctypes as C
 import json
@@ -58,12 +58,25 @@ def main():
     # a batch of sequences under tensor parallelism (batched kernels, all-reduce over [batch x dim], logits gathered per rank slice)
     B, blen = 5, 14
     bprompts = np.stack([pkg.model.synth_tokens(seed, blen, CFG["vocab"], stream=(1 << 40) + b) for b in range(B)])
-    m = pkg.model.Model(CFG, tp_rank=ranks.rank, tp_size=ranks.world, batch=B)
-    m.set_comm(comm)
-    m.load_synthetic(seed)
-    out["batch"] = m.generate_batch(bprompts, n_new).tolist()
-    ranks.barrier()
-    m.close()
+    for mode in ("batch", "batch_peer"):           # NCCL all-reduce, then the all-reduce through peer memory
+        m = pkg.model.Model(CFG, tp_rank=ranks.rank, tp_size=ranks.world, batch=B)
+        m.set_comm(comm)
+        keep = pkg.rendezvous.install_peer_exchange(m, ranks, CFG["dim"], batch=B) if mode == "batch_peer" else None
+        m.load_synthetic(seed)
+        out[mode] = m.generate_batch(bprompts, n_new).tolist()
+        out[mode + "_again"] = m.generate_batch(bprompts, n_new).tolist()      # a second session restarts at the earlier positions
+        ranks.barrier()
+        m.close()
+        if mode == "batch_peer" and keep is None:
+            out["peer_setup_failed"] = True
+        if keep:
+            code = C.c_int(-1)
+            g.check(lib.greta_cuda_peer_status(C.byref(code)))
+            out["peer_status_batch"] = code.value
+            for ptr in keep[2]:
+                g.check(lib.greta_cuda_ipc_close(ptr))
+            ranks.barrier()
+            keep[0].free()
     # a K-quant file under tensor parallelism: every rank decodes its rows on the device, re-stores them as Q8_0 and keeps its
     # column range (the down-projection's 384 columns per rank are not whole super-blocks)
     import tempfile
@@ -91,8 +104,9 @@ def main():
             out["want" + str(plen)] = want
         for b in range(B):
             want, gaps = O.Model(CFG, weights).generate(bprompts[b], n_new)
-            ok = ok and out["batch"][b] == want and min(gaps) > 1e-6
-        out["ok"] = bool(ok) and out.get("peer_status") == 0 and not out.get("repeat_mismatch") and out["kquant_ok"]
+            ok = ok and min(gaps) > 1e-6 and all(out[k][b] == want for k in ("batch", "batch_again", "batch_peer", "batch_peer_again"))
+        out["ok"] = (bool(ok) and out.get("peer_status") == 0 and out.get("peer_status_batch") == 0 and not out.get("repeat_mismatch")
+                     and not out.get("peer_setup_failed") and out["kquant_ok"])
         print("TP_RESULT " + json.dumps(out), flush=True)
     g.check(lib.greta_cuda_comm_destroy(comm))
 

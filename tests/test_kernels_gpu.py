@@ -367,6 +367,74 @@ def test_fused_exchange_rejects_bad_descriptors(g):
                                                buf.ptr, buf.ptr, buf.ptr, 64, 64) == 4                         # x_out aliases x_in
 
 
+def test_peer_allreduce_protocol_on_one_gpu(g, tuning):
+    """greta_cuda_peer_allreduce_f32 as rank 0 of 2, the other rank played by the host: with nothing from rank 1 the bounded
+    waits run out, the status word says so and the call returns; after a reset and with rank 1's tagged words in place
+    (its partial of slice 0 in region A, its sums of slice 1 in region B, written by the host with the tag the kernel
+    derives from the position) the vector comes back as the sum over both ranks, and rank 0's own words sit where rank 1
+    would look for them.  With one rank the call is the identity."""
+    import time
+    from gretacore_v3_b200.model import PeerExchange
+    lib = g.cuda()
+    rng = np.random.default_rng(91)
+    count, tp, pos, idx = 5 * 512, 2, 7, 3
+    slice_ = count // tp
+    nbytes = lib.greta_cuda_peer_allreduce_slot_bytes(count)
+    assert nbytes == 4 * count * 8
+    slots = [g.DeviceBuffer(nbytes, zero=True) for _ in range(tp)]
+    _KEEP.extend(slots)
+    ex = PeerExchange()
+    ex.tp, ex.rank, ex.slot_bytes = tp, 0, nbytes
+    for j, b in enumerate(slots):
+        ex.slots[j] = b.ptr
+    dpos = _dev(g, np.array([pos], np.uint32))
+    x0, x1 = rng.normal(0, 1, count).astype(np.float32), rng.normal(0, 1, count).astype(np.float32)
+    tag = ((pos + 1) << 8) | idx
+    set_off = (idx & 1) * 2 * count
+
+    def run(xbuf):
+        g.check(lib.greta_cuda_peer_allreduce_f32(None, xbuf.ptr, count, C.byref(ex), idx, dpos.ptr))
+        g.check(lib.greta_cuda_device_synchronize())
+        code = C.c_int(-1)
+        g.check(lib.greta_cuda_peer_status(C.byref(code)))
+        return code.value
+
+    tuning("peer_poll_limit", 2000, restore=1 << 22)
+    g.check(lib.greta_cuda_peer_reset(None))
+    xd = _dev(g, x0)
+    t0 = time.time()
+    assert run(xd) != 0 and time.time() - t0 < 5.0              # rank 1 never wrote: the waits gave up by themselves
+    # rank 1's part, written by the host into rank 0's buffer
+    g.check(lib.greta_cuda_peer_reset(None))
+    words = np.zeros((4 * count, 2), np.uint32)
+    words[set_off + 1 * slice_: set_off + 2 * slice_, 0] = x1[:slice_].view(np.uint32)             # region A, row 1: rank 1's slice 0
+    words[set_off + 1 * slice_: set_off + 2 * slice_, 1] = tag
+    total = x0 + x1                                                                                 # rank order: rank 0 first
+    words[set_off + count + slice_: set_off + 2 * count, 0] = total[slice_:].view(np.uint32)       # region B, slice 1: summed by rank 1
+    words[set_off + count + slice_: set_off + 2 * count, 1] = tag
+    slots[0].upload(words.reshape(-1))
+    xd = _dev(g, x0)
+    assert run(xd) == 0
+    assert np.array_equal(xd.download(np.float32), total)
+    theirs = slots[1].download(np.uint32).reshape(-1, 2)                                            # what rank 1 would read
+    assert np.array_equal(theirs[set_off: set_off + slice_, 0].view(np.float32), x0[slice_:]) and (theirs[set_off: set_off + slice_, 1] == tag).all()
+    assert np.array_equal(theirs[set_off + count: set_off + count + slice_, 0].view(np.float32), total[:slice_])
+    # one rank: identity, whatever the parity
+    ex1 = PeerExchange()
+    ex1.tp, ex1.rank, ex1.slot_bytes = 1, 0, nbytes
+    ex1.slots[0] = slots[1].ptr
+    for i in (0, 1, 2):
+        xd = _dev(g, x1)
+        g.check(lib.greta_cuda_peer_allreduce_f32(None, xd.ptr, count, C.byref(ex1), i, dpos.ptr))
+        g.check(lib.greta_cuda_device_synchronize())
+        assert np.array_equal(xd.download(np.float32), x1)
+    # refused: slot buffers too small for the count, a count that does not split over the ranks
+    ex.slot_bytes = nbytes - 8
+    assert lib.greta_cuda_peer_allreduce_f32(None, xd.ptr, count, C.byref(ex), 0, dpos.ptr) != 0
+    ex.slot_bytes = nbytes
+    assert lib.greta_cuda_peer_allreduce_f32(None, xd.ptr, count - 1, C.byref(ex), 0, dpos.ptr) != 0
+
+
 def test_fused_exchange_wait_runs_out_and_recovers(g, tuning):
     """A consumer whose producers never ran: with a poll limit of a few thousand the wait gives up by itself, the
     kernel finishes on what it has, greta_cuda_peer_status reports it; after greta_cuda_peer_reset and with the
