@@ -587,7 +587,7 @@ template <int FMT>
 struct PFmt;  // warps per CTA, CTAs per SM the shared-memory plan aims at
 template <>
 struct PFmt<GRETA_FMT_Q4_0> {
-  static constexpr int NW = 8, CTAS_PER_SM = 2;
+  static constexpr int NW = 8, CTAS_PER_SM = 2;  // 3 (a two-stage weight ring) was measured: 28672 x 8192 gate/up 186 vs 210 us, but 8192 x 8192 41.5 vs 31.0 us
 };
 template <>
 struct PFmt<GRETA_FMT_Q8_0> {
@@ -604,8 +604,9 @@ struct PPlan {
   static constexpr int ROWB = CELL * PB + 16, STAGE = 16 * ROWB;
   static constexpr int ROWTAB = NW * 16 * (int)sizeof(RowSrc);
   static constexpr int room_in(int limit, int xcells) { return (limit - 2 * xcells * CELL * MT * 1024 - ROWTAB) / (NW * STAGE); }
-  static constexpr int CTAS = (PFmt<FMT>::CTAS_PER_SM == 2 && room_in(112 * 1024, 1) >= 2) ? 2 : 1;  // CTAs per SM this plan fits
-  static constexpr int LIMIT = CTAS == 2 ? 112 * 1024 : (int)BSMEM_LIMIT;
+  // CTAs per SM this plan fits: the most that the format aims at and that leaves a weight ring of at least two stages
+  static constexpr int CTAS = (PFmt<FMT>::CTAS_PER_SM >= 3 && room_in(74 * 1024, 1) >= 2) ? 3 : ((PFmt<FMT>::CTAS_PER_SM >= 2 && room_in(112 * 1024, 1) >= 2) ? 2 : 1);
+  static constexpr int LIMIT = CTAS == 3 ? 74 * 1024 : (CTAS == 2 ? 112 * 1024 : (int)BSMEM_LIMIT);
   // Two activation buffers of XCELLS cells each; a buffer is refilled XCELLS cells ahead, which the weight ring must
   // cover: XCELLS <= DEPTH - 1.  Two CTAs of 8 warps per SM (128 rows each) balance the SMs better than one of 16.
   static constexpr int room(int xcells) { return room_in(LIMIT, xcells); }

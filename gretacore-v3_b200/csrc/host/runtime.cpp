@@ -370,9 +370,25 @@ GretaResult GretaCompute::gemm(GretaStream *stream, GretaMemory *A, GretaMemory 
                                bool transpose_A, bool transpose_B, GretaDataType accum_type) {
   if (!A || !B || !C) return GretaResult::ERROR_INVALID_ARGS;
   if (transpose_A || transpose_B || accum_type != GretaDataType::FP32) return GretaResult::ERROR_NOT_IMPLEMENTED;
+  const bool a_f16 = A->data_type() == GretaDataType::FP16, c_f16 = C->data_type() == GretaDataType::FP16;
+  if (B->data_type() == GretaDataType::Q4_K) {
+    // Weights kept as Q4_K super-blocks exactly as in the file (the enum value the reference declares and never routes):
+    // the weight-only GEMV for M <= 32, fp32 activations and output.
+    if (a_f16 || c_f16 || M > 32) return GretaResult::ERROR_NOT_IMPLEMENTED;
+    g_audit = GemmAuditInfo{};
+    g_audit.op_label = g_label;
+    g_audit.route = "GEMV";
+    g_audit.quant_mode = "Q4_K";
+    g_audit.type_a = (int)A->data_type();
+    g_audit.type_b = (int)B->data_type();
+    g_audit.accum_type = (int)accum_type;
+    g_audit.m = M; g_audit.n = N; g_audit.k = K; g_audit.lda = K; g_audit.ldb = K; g_audit.ldc = N;
+    g_audit.a_ptr = (uintptr_t)A->data(); g_audit.b_ptr_base = (uintptr_t)B->data(); g_audit.c_ptr = (uintptr_t)C->data();
+    return static_cast<GretaResult>(greta_cuda_gemv_kquant(H(stream), GRETA_GGML_Q4_K, static_cast<const float *>(A->data()), B->data(),
+                                                           static_cast<float *>(C->data()), M, N, K));
+  }
   const int fmt = fmt_of(B->data_type());
   if (fmt < 0) return GretaResult::ERROR_NOT_IMPLEMENTED;
-  const bool a_f16 = A->data_type() == GretaDataType::FP16, c_f16 = C->data_type() == GretaDataType::FP16;
   const GretaQuantInfo qi = B->quant_info();
   if (fmt != GRETA_FMT_F16 && (qi.scales == nullptr || qi.group_size != 32)) return GretaResult::ERROR_INVALID_ARGS;
   const bool gguf = fmt == GRETA_FMT_Q4_0 || fmt == GRETA_FMT_Q8_0;

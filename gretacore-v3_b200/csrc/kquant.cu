@@ -10,6 +10,8 @@
 // The reference then re-quantises such tensors to its INT4 storage (weight_loader.cpp:920-957).  Here they are
 // re-stored as Q8_0 blocks instead (d = amax / 127, the quantiser published with the format), which the decode and
 // prefill kernels stream like any Q8_0 weight.
+#include <algorithm>
+
 #include "greta_common.cuh"
 
 using namespace greta;
@@ -104,6 +106,105 @@ __global__ void kquant_to_q8_0_kernel(const uint8_t *__restrict__ blocks, uint8_
   dpl[(sub / nb_row) * d_row_stride(nb_row) + sub % nb_row] = __float2half_rn(d);
 }
 
+// ---- GEMV straight from the super-blocks ----------------------------------------------------------
+// y[m][n] = sum_k x[m][k] * w[n][k] with w decoded as above, the weights read as they lie in the file (4.5 bits per
+// weight for Q4_K, 6.56 for Q6_K): nothing is re-quantised on this route.  A warp owns a row at a time; a lane owns one
+// group of weights that shares a scale (a Q4_K sub-block of 32, a Q6_K group of 16) and uses
+//   sum x (a q - b) = a sum(x q) - b sum(x),   a = d * sc, b = dmin * m   (Q4_K);    sum x (d q sc) = (d sc) sum(x q)   (Q6_K)
+// with sum(x) per group of 32 taken once per CTA when the activations are staged.  fp32 throughout; against the
+// double-accumulating oracle over the exactly decoded weights the difference is rounding (1e-6 relative).
+constexpr int KQ_WARPS = 8;
+
+template <int TYPE>
+__global__ void __launch_bounds__(KQ_WARPS * 32) kquant_gemv_kernel(const uint8_t *__restrict__ blocks, const float *__restrict__ x,
+                                                                     float *__restrict__ y, uint32_t N, uint32_t K) {
+  extern __shared__ __align__(16) float kq_smem[];
+  // activations of row blockIdx.y, 4 floats of padding after every 32 (a lane reads its own group of 32 with 128-bit
+  // loads: 36-float strides spread a quarter-warp over all banks), then their sums per group of 32
+  float *xs = kq_smem;
+  float *xsum = kq_smem + K + K / 8;
+  auto at = [](uint32_t k) { return k + 4 * (k >> 5); };
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const float *xrow = x + (size_t)blockIdx.y * K;
+  for (uint32_t i = tid * 4; i < K; i += KQ_WARPS * 32 * 4) *reinterpret_cast<float4 *>(xs + at(i)) = __ldg(reinterpret_cast<const float4 *>(xrow + i));
+  __syncthreads();
+  for (uint32_t g = tid; g < K / 32; g += KQ_WARPS * 32) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) t += xs[g * 36 + i];
+    xsum[g] = t;
+  }
+  __syncthreads();
+  constexpr int SB = TYPE == GRETA_GGML_Q4_K ? Q4_K_BYTES : Q6_K_BYTES;
+  const uint32_t nsuper = K / 256;
+  for (uint32_t row = blockIdx.x * KQ_WARPS + warp; row < N; row += gridDim.x * KQ_WARPS) {
+    const uint8_t *wrow = blocks + (size_t)row * nsuper * SB;
+    float acc = 0.f;
+    if (TYPE == GRETA_GGML_Q4_K) {
+      for (uint32_t sub = lane; sub < nsuper * 8; sub += 32) {  // one sub-block of 32 weights per lane
+        const uint8_t *blk = wrow + (size_t)(sub >> 3) * SB;
+        const int j = sub & 7;
+        const uint32_t dd = *reinterpret_cast<const uint32_t *>(blk);
+        const uint32_t *sc32 = reinterpret_cast<const uint32_t *>(blk + 4);
+        const uint32_t s0 = sc32[0], s1 = sc32[1], s2 = sc32[2];
+        auto byte_of = [&](int i) -> uint32_t { return ((i < 4 ? s0 : (i < 8 ? s1 : s2)) >> (8 * (i & 3))) & 0xFFu; };
+        uint32_t s6, m6;
+        if (j < 4) {
+          s6 = byte_of(j) & 0x3F;
+          m6 = byte_of(6 + j) & 0x3F;
+        } else {
+          const int i = j - 4;
+          const uint32_t ns = (i & 1) ? (byte_of(4 + i / 2) >> 4) : (byte_of(4 + i / 2) & 0x0F);
+          const uint32_t nm = (i & 1) ? (byte_of(10 + i / 2) >> 4) : (byte_of(10 + i / 2) & 0x0F);
+          s6 = (byte_of(i) >> 6) | (ns << 2);
+          m6 = (byte_of(6 + i) >> 6) | (nm << 2);
+        }
+        const float a = __half2float(__ushort_as_half((unsigned short)(dd & 0xFFFFu))) * (float)s6;
+        const float b = __half2float(__ushort_as_half((unsigned short)(dd >> 16))) * (float)m6;
+        const uint4 q = ld_stream(blk + 16 + j * 16);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+        const float *xb = xs + (size_t)sub * 36;
+        float dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {  // byte l of the sub-block: elements 2l (low nibble) and 2l + 1 (high nibble)
+          const float4 xa = *reinterpret_cast<const float4 *>(xb + 8 * i), xc = *reinterpret_cast<const float4 *>(xb + 8 * i + 4);
+          dot = fmaf((float)(w[i] & 15u), xa.x, dot);
+          dot = fmaf((float)((w[i] >> 4) & 15u), xa.y, dot);
+          dot = fmaf((float)((w[i] >> 8) & 15u), xa.z, dot);
+          dot = fmaf((float)((w[i] >> 12) & 15u), xa.w, dot);
+          dot = fmaf((float)((w[i] >> 16) & 15u), xc.x, dot);
+          dot = fmaf((float)((w[i] >> 20) & 15u), xc.y, dot);
+          dot = fmaf((float)((w[i] >> 24) & 15u), xc.z, dot);
+          dot = fmaf((float)(w[i] >> 28), xc.w, dot);
+        }
+        acc += a * dot - b * xsum[sub];
+      }
+    } else {
+      for (uint32_t grp = lane; grp < nsuper * 16; grp += 32) {  // one group of 16 weights (one scale) per lane
+        const uint8_t *blk = wrow + (size_t)(grp >> 4) * SB;
+        const int l = grp & 15;
+        const uint16_t *ql = reinterpret_cast<const uint16_t *>(blk + 8 * l);      // 8 bytes: the 16 low nibbles
+        const uint16_t *qh = reinterpret_cast<const uint16_t *>(blk + 128 + 4 * l);  // 4 bytes: the 16 high bit pairs
+        const uint32_t lo0 = (uint32_t)ql[0] | ((uint32_t)ql[1] << 16), lo1 = (uint32_t)ql[2] | ((uint32_t)ql[3] << 16);
+        const uint32_t hi = (uint32_t)qh[0] | ((uint32_t)qh[1] << 16);
+        const float sc = (float)reinterpret_cast<const int8_t *>(blk + 192)[l];
+        const float d = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short *>(blk + 208)));
+        const float *xb = xs + at(grp * 16);
+        float dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const uint32_t lo = ((i < 8 ? lo0 : lo1) >> (4 * (i & 7))) & 15u, h2 = (hi >> (2 * i)) & 3u;
+          dot = fmaf((float)((int)(lo | (h2 << 4)) - 32), xb[i], dot);
+        }
+        acc += (d * sc) * dot;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) y[(size_t)blockIdx.y * N + row] = acc;
+  }
+}
+
 inline cudaStream_t S(greta_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
 inline unsigned grid_for(size_t n, unsigned threads) { return (unsigned)((n + threads - 1) / threads); }
 
@@ -151,6 +252,34 @@ int greta_cuda_kquant_to_q8_0(greta_stream_t stream, int ggml_type, const void *
   else
     kquant_to_q8_0_kernel<GRETA_GGML_Q6_K><<<grid_for(n_sub, 128), 128, 0, S(stream)>>>(b, (uint8_t *)qs, (__half *)d, n_sub, K / 32);
   return launched("kquant_to_q8_0_kernel");
+}
+
+// The M <= 32 route of the reference's weight-only GEMV (gemm_kernels.hip:742-760: one pass over the weights per
+// activation row) on weights kept as K-quant super-blocks.
+int greta_cuda_gemv_kquant(greta_stream_t stream, int ggml_type, const float *x, const void *blocks, float *y, uint32_t M, uint32_t N, uint32_t K) {
+  GRETA_REQUIRE(ggml_type == GRETA_GGML_Q4_K || ggml_type == GRETA_GGML_Q6_K, "gemv_kquant: GGML type %d is not Q4_K (12) or Q6_K (14)", ggml_type);
+  GRETA_REQUIRE(K % 256 == 0 && K > 0, "gemv_kquant: K=%u is not a positive multiple of the super-block size 256", K);
+  GRETA_REQUIRE(M >= 1 && M <= 32, "gemv_kquant: M=%u outside 1..32", M);
+  if (N == 0) return GRETA_OK;
+  GRETA_REQUIRE(x && blocks && y && aligned16(x) && ((uintptr_t)blocks & (ggml_type == GRETA_GGML_Q4_K ? 15 : 1)) == 0, "gemv_kquant: null or misaligned pointer");
+  const size_t smem = ((size_t)K + K / 8 + K / 32) * sizeof(float);
+  GRETA_REQUIRE(smem <= 200 * 1024, "gemv_kquant: K=%u does not fit the activation staging (at most 44032)", K);
+  static bool attr_set[64][2] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const int ti = ggml_type == GRETA_GGML_Q4_K ? 0 : 1;
+  if (dev >= 0 && dev < 64 && !attr_set[dev][ti]) {
+    if (ti == 0) GRETA_CUDA_TRY(cudaFuncSetAttribute(kquant_gemv_kernel<GRETA_GGML_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    else GRETA_CUDA_TRY(cudaFuncSetAttribute(kquant_gemv_kernel<GRETA_GGML_Q6_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attr_set[dev][ti] = true;
+  }
+  const unsigned per_sm = smem <= 48 * 1024 ? 4u : (smem <= 100 * 1024 ? 2u : 1u);
+  const unsigned ctas = std::min<unsigned>((N + KQ_WARPS - 1) / KQ_WARPS, (unsigned)sm_count() * per_sm);
+  dim3 grid(ctas, M);
+  const uint8_t *b = static_cast<const uint8_t *>(blocks);
+  if (ti == 0) kquant_gemv_kernel<GRETA_GGML_Q4_K><<<grid, KQ_WARPS * 32, smem, S(stream)>>>(b, x, y, N, K);
+  else kquant_gemv_kernel<GRETA_GGML_Q6_K><<<grid, KQ_WARPS * 32, smem, S(stream)>>>(b, x, y, N, K);
+  return launched("kquant_gemv_kernel");
 }
 
 }  // extern "C"

@@ -144,6 +144,11 @@ GRETA_API int greta_cuda_kquant_dequant(greta_stream_t stream, int ggml_type, co
  * each group of 32 decoded values becomes one Q8_0 block, d = amax / 127 rounded to fp16, q = round(x / d).  The reference
  * re-quantises K-quant tensors too, to its INT4 storage (weight_loader.cpp:920-957). */
 GRETA_API int greta_cuda_kquant_to_q8_0(greta_stream_t stream, int ggml_type, const void *blocks, void *qs, void *d, uint32_t N, uint32_t K);
+/* y[M x N] = x[M x K] * W^T with W [N x K] kept as K-quant super-blocks exactly as in the file (nothing re-quantised): the
+ * weight-only GEMV of the reference's M <= 32 route (gemm_kernels.hip:742-760) for the block formats its models are shipped in.
+ * x, y fp32; 1 <= M <= 32 (the weights are streamed once per activation row, as the reference's grid(N, M) does). */
+GRETA_API int greta_cuda_gemv_kquant(greta_stream_t stream, int ggml_type, const float *x, const void *blocks, float *y, uint32_t M, uint32_t N,
+                                     uint32_t K);
 /* Device-side split of raw GGUF blocks (18 B Q4_0 / 34 B Q8_0, as stored in a GGUF
  * file: src/inference/src/weight_loader.cpp:60-75 sizes, :703-712 Q8_0 split) into
  * the two planes. */

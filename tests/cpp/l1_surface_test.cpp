@@ -160,6 +160,28 @@ int main(int argc, char **argv) {
   gemm_cases(stream.get(), "int4", GretaDataType::INT4, false);
   gemm_cases(stream.get(), "int8", GretaDataType::INT8, false);
   gemm_cases(stream.get(), "f16", GretaDataType::FP16, false);
+  {  // weights kept as Q4_K super-blocks: the GEMV route up to 32 rows, refused above
+    const uint32_t N = u32("gemm.N"), Kd = u32("gemm.K");
+    Buffer w;
+    upload(w, "gemm.q4_k.w", GretaDataType::Q4_K);
+    for (uint32_t M : {1u, 32u}) {
+      const std::string tag = "gemm.q4_k.M" + std::to_string(M);
+      Buffer a, c;
+      upload(a, "gemm.A" + std::to_string(M), GretaDataType::FP32);
+      device_out(c, (size_t)M * N * 4);
+      GretaCompute::set_op_label(tag.c_str());
+      GretaResult r = GretaCompute::gemm(stream.get(), &a, &w, &c, M, N, Kd);
+      auto got = download(c, (size_t)M * N);
+      double err = max_abs_rel(got.data(), f32("gemm.q4_k.want" + std::to_string(M)), (size_t)M * N);
+      report(tag + " result", r == GretaResult::SUCCESS && err < 2e-5, err);
+      auto audit = GretaCompute::get_last_gemm_audit();
+      report(tag + " route " + audit.route, audit.route == "GEMV" && audit.quant_mode == "Q4_K" && audit.op_label == tag);
+    }
+    Buffer a, c;
+    upload(a, "gemm.A33", GretaDataType::FP32);
+    device_out(c, (size_t)33 * N * 4);
+    report("gemm q4_k above 32 rows refused", GretaCompute::gemm(stream.get(), &a, &w, &c, 33, N, Kd) == GretaResult::ERROR_NOT_IMPLEMENTED);
+  }
   {  // FP16 output forces the tensor-core route even at M = 1; transposes and non-fp32 accumulation are refused
     Buffer w, sc, a, c;
     upload(w, "gemm.q4_0.w", GretaDataType::Q4_0);

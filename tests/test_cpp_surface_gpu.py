@@ -44,6 +44,12 @@ def _cases():
         t[f"gemm.int4.want{M}"] = O.gemv(a, b4, O.FMT_Q4_0, N, K)            # the same values in the reference's own storage
         t[f"gemm.int8.want{M}"] = O.gemv(a, b8, O.FMT_Q8_0, N, K)
         t[f"gemm.f16.want{M}"] = O.gemm_f16w(a, wf16.view(np.uint16), N, K)
+    import test_kquant as KQ                                                 # weights kept as Q4_K super-blocks (GretaDataType::Q4_K)
+    bk = KQ.kquant_blocks(rng, KQ.GGML_Q4_K, N * K // 256)
+    t["gemm.q4_k.w"] = bk
+    wk = O.dequant_q4_k(bk).reshape(N, K).astype(np.float64)
+    for M in (1, 32):
+        t[f"gemm.q4_k.want{M}"] = (t[f"gemm.A{M}"].astype(np.float64) @ wk.T).astype(np.float32)
     H, Hkv, Dh, L, S = 8, 2, 64, 200, 256
     q = rng.normal(0, 1, H * Dh).astype(np.float32)
     k = rng.normal(0, 1, (Hkv, S, Dh)).astype(np.float16)

@@ -87,6 +87,30 @@ def test_restoring_as_q8_0_gives_the_oracles_blocks_and_a_matching_gemv(g, ggml_
     assert lib.greta_cuda_kquant_to_q8_0(None, ggml_type, src.ptr, qs.ptr, d.ptr, N, 96) != 0           # K not whole super-blocks
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("ggml_type", [GGML_Q4_K, GGML_Q6_K])
+@pytest.mark.parametrize("M,N,K", [(1, 203, 2048), (3, 64, 7168), (1, 1024, 256)])
+def test_gemv_straight_from_super_blocks(g, ggml_type, M, N, K):
+    """greta_cuda_gemv_kquant reads the weights as they lie in the file (nothing re-quantised): against the product of the
+    activations with the oracle's decoded weights in double precision the difference is fp32 rounding."""
+    rng = np.random.default_rng(90 + ggml_type + N)
+    blk = kquant_blocks(rng, ggml_type, N * K // 256)
+    x = rng.normal(0, 1, (M, K)).astype(np.float32)
+    lib = g.cuda()
+    src, xd = g.DeviceBuffer.from_numpy(blk), g.DeviceBuffer.from_numpy(x)
+    y = g.DeviceBuffer(M * N * 4)
+    y.fill(0xFF)
+    g.check(lib.greta_cuda_gemv_kquant(None, ggml_type, xd.ptr, src.ptr, y.ptr, M, N, K))
+    got = y.download(np.float32).reshape(M, N)
+    want = x.astype(np.float64) @ decode(blk, ggml_type).reshape(N, K).astype(np.float64).T
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() <= 2e-5 * np.abs(want).max()
+    assert lib.greta_cuda_gemv_kquant(None, ggml_type, xd.ptr, src.ptr, y.ptr, M, N, 96) != 0       # K not whole super-blocks
+    assert lib.greta_cuda_gemv_kquant(None, ggml_type, xd.ptr, src.ptr, y.ptr, 33, N, K) != 0       # more rows than the route serves
+    for b in (src, xd, y):
+        b.free()
+
+
 def _kquant_model_file(path, rng, head):
     """A llama-style file as a Q4_K_M export lays it out: Q4_K projections with Q6_K for ffn_down and attn_v, a Q4_K
     embedding table, and an fp16 or Q6_K LM head.  Returns the oracle's weights: every K-quant tensor decoded and re-stored
