@@ -110,10 +110,38 @@ __global__ void kquant_to_q8_0_kernel(const uint8_t *__restrict__ blocks, uint8_
 // y[m][n] = sum_k x[m][k] * w[n][k] with w decoded as above, the weights read as they lie in the file (4.5 bits per
 // weight for Q4_K, 6.56 for Q6_K): nothing is re-quantised on this route.  A warp owns a row at a time; a lane owns one
 // group of weights that shares a scale (a Q4_K sub-block of 32, a Q6_K group of 16) and uses
-//   sum x (a q - b) = a sum(x q) - b sum(x),   a = d * sc, b = dmin * m   (Q4_K);    sum x (d q sc) = (d sc) sum(x q)   (Q6_K)
+//   sum x (a q - b) = a sum(x (q - 8)) + (8 a - b) sum(x),   a = d * sc, b = dmin * m   (Q4_K);    sum x (d q sc) = (d sc) sum(x q)   (Q6_K)
 // with sum(x) per group of 32 taken once per CTA when the activations are staged.  fp32 throughout; against the
 // double-accumulating oracle over the exactly decoded weights the difference is rounding (1e-6 relative).
 constexpr int KQ_WARPS = 8;
+
+__device__ __forceinline__ uint32_t kq_and_or(uint32_t a, uint32_t m, uint32_t o) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(m), "r"(o));  // (a & m) | o
+  return r;
+}
+__device__ __forceinline__ float2 kq_h2f2(uint32_t h2) { return __half22float2(*reinterpret_cast<__half2 *>(&h2)); }
+// sum x * (q - 8) over the 8 nibbles of one payload word.  The nibbles become exact fp16 integers through the 0x6400
+// exponent trick, two at a time; byte l of the word holds elements 2l (low) and 2l + 1 (high), so the pairs are
+// (e0, e4), (e2, e6), (e1, e5), (e3, e7) and x is staged in that order: xa = {x0, x4, x2, x6}, xb = {x1, x5, x3, x7}.
+__device__ __forceinline__ float2 kq_dot_nib8(uint32_t w, float4 xa, float4 xb, float2 s) {
+  const uint32_t MAGIC = 0x64006400u;
+  const __half2 c1032 = __halves2half2(__ushort_as_half(0x6408), __ushort_as_half(0x6408));
+  const __half2 sixteenth = __halves2half2(__ushort_as_half(0x2C00), __ushort_as_half(0x2C00));
+  const __half2 cm72 = __halves2half2(__ushort_as_half(0xD480), __ushort_as_half(0xD480));
+  const uint32_t w8 = w >> 8;
+  uint32_t lo = kq_and_or(w, 0x000F000Fu, MAGIC), hi = kq_and_or(w, 0x00F000F0u, MAGIC);
+  uint32_t lo2 = kq_and_or(w8, 0x000F000Fu, MAGIC), hi2 = kq_and_or(w8, 0x00F000F0u, MAGIC);
+  const float2 a = __half22float2(__hsub2(*reinterpret_cast<__half2 *>(&lo), c1032));
+  const float2 a2 = __half22float2(__hsub2(*reinterpret_cast<__half2 *>(&lo2), c1032));
+  const float2 b = __half22float2(__hfma2(*reinterpret_cast<__half2 *>(&hi), sixteenth, cm72));
+  const float2 b2 = __half22float2(__hfma2(*reinterpret_cast<__half2 *>(&hi2), sixteenth, cm72));
+  s = __ffma2_rn(make_float2(xa.x, xa.y), a, s);
+  s = __ffma2_rn(make_float2(xa.z, xa.w), a2, s);
+  s = __ffma2_rn(make_float2(xb.x, xb.y), b, s);
+  s = __ffma2_rn(make_float2(xb.z, xb.w), b2, s);
+  return s;
+}
 
 template <int TYPE>
 __global__ void __launch_bounds__(KQ_WARPS * 32) kquant_gemv_kernel(const uint8_t *__restrict__ blocks, const float *__restrict__ x,
@@ -126,7 +154,14 @@ __global__ void __launch_bounds__(KQ_WARPS * 32) kquant_gemv_kernel(const uint8_
   auto at = [](uint32_t k) { return k + 4 * (k >> 5); };
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float *xrow = x + (size_t)blockIdx.y * K;
-  for (uint32_t i = tid * 4; i < K; i += KQ_WARPS * 32 * 4) *reinterpret_cast<float4 *>(xs + at(i)) = __ldg(reinterpret_cast<const float4 *>(xrow + i));
+  if (TYPE == GRETA_GGML_Q4_K) {  // inside every group of 8 in the order e0, e4, e2, e6, e1, e5, e3, e7 (see kq_dot_nib8)
+    for (uint32_t i = tid; i < K; i += KQ_WARPS * 32) {
+      const uint32_t e = i & 7u;
+      xs[at((i & ~7u) | ((e & 1u) << 2) | (e & 2u) | (e >> 2))] = __ldg(xrow + i);
+    }
+  } else {
+    for (uint32_t i = tid * 4; i < K; i += KQ_WARPS * 32 * 4) *reinterpret_cast<float4 *>(xs + at(i)) = __ldg(reinterpret_cast<const float4 *>(xrow + i));
+  }
   __syncthreads();
   for (uint32_t g = tid; g < K / 32; g += KQ_WARPS * 32) {
     float t = 0.f;
@@ -141,7 +176,8 @@ __global__ void __launch_bounds__(KQ_WARPS * 32) kquant_gemv_kernel(const uint8_
     const uint8_t *wrow = blocks + (size_t)row * nsuper * SB;
     float acc = 0.f;
     if (TYPE == GRETA_GGML_Q4_K) {
-      for (uint32_t sub = lane; sub < nsuper * 8; sub += 32) {  // one sub-block of 32 weights per lane
+#pragma unroll 1
+      for (uint32_t sub = lane; sub < nsuper * 8; sub += 32) {  // one sub-block of 32 weights per lane (unrolling by 4 measured slower: 64 vs 56 us at 28672 x 8192)
         const uint8_t *blk = wrow + (size_t)(sub >> 3) * SB;
         const int j = sub & 7;
         const uint32_t dd = *reinterpret_cast<const uint32_t *>(blk);
@@ -164,22 +200,15 @@ __global__ void __launch_bounds__(KQ_WARPS * 32) kquant_gemv_kernel(const uint8_
         const uint4 q = ld_stream(blk + 16 + j * 16);
         const uint32_t w[4] = {q.x, q.y, q.z, q.w};
         const float *xb = xs + (size_t)sub * 36;
-        float dot = 0.f;
+        float2 d2 = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {  // byte l of the sub-block: elements 2l (low nibble) and 2l + 1 (high nibble)
-          const float4 xa = *reinterpret_cast<const float4 *>(xb + 8 * i), xc = *reinterpret_cast<const float4 *>(xb + 8 * i + 4);
-          dot = fmaf((float)(w[i] & 15u), xa.x, dot);
-          dot = fmaf((float)((w[i] >> 4) & 15u), xa.y, dot);
-          dot = fmaf((float)((w[i] >> 8) & 15u), xa.z, dot);
-          dot = fmaf((float)((w[i] >> 12) & 15u), xa.w, dot);
-          dot = fmaf((float)((w[i] >> 16) & 15u), xc.x, dot);
-          dot = fmaf((float)((w[i] >> 20) & 15u), xc.y, dot);
-          dot = fmaf((float)((w[i] >> 24) & 15u), xc.z, dot);
-          dot = fmaf((float)(w[i] >> 28), xc.w, dot);
-        }
-        acc += a * dot - b * xsum[sub];
+        for (int i = 0; i < 4; ++i)
+          d2 = kq_dot_nib8(w[i], *reinterpret_cast<const float4 *>(xb + 8 * i), *reinterpret_cast<const float4 *>(xb + 8 * i + 4), d2);
+        const float dot8 = d2.x + d2.y;  // sum x (q - 8)
+        acc += a * dot8 + (8.f * a - b) * xsum[sub];
       }
     } else {
+#pragma unroll 4
       for (uint32_t grp = lane; grp < nsuper * 16; grp += 32) {  // one group of 16 weights (one scale) per lane
         const uint8_t *blk = wrow + (size_t)(grp >> 4) * SB;
         const int l = grp & 15;
