@@ -110,3 +110,63 @@ def test_shards_tile_every_projection():
                 assert cols % 32 == 0 and c0 % 32 == 0
                 cover[r0:r0 + rows, c0 // 32:(c0 + cols) // 32] += 1
             assert (cover == 1).all()
+
+
+def test_peer_allreduce_protocol_model():
+    """A numpy model of greta_cuda_peer_allreduce_f32 (gemv.cu, peer_allreduce_kernel): per exchange, region A of a rank's
+    slot buffer holds [tp][count / tp] tagged words (row r: rank r's share of the slice this rank owns), region B holds
+    [count] tagged sums; two sets alternate with the exchange index.  The model runs tp ranks through scatter, sum in rank
+    order and gather for a sequence of exchanges in which one rank always races one exchange ahead of the others, and checks
+    that every rank ends with the same bits, that a set is never read while a rank may still write the next-but-one
+    exchange into it, and that the slot size the library reports holds both sets."""
+    rng = np.random.default_rng(3)
+    tp, count = 4, 4 * 96
+    slice_ = count // tp
+    words = 4 * count                                                     # greta_cuda_peer_allreduce_slot_bytes(count) / 8
+    vals = [np.zeros((tp, words), np.float32) for _ in range(1)][0]
+    tags = np.zeros((tp, words), np.int64)
+
+    def set_off(idx):
+        return (idx & 1) * 2 * count
+
+    def phase_a(rank, x, idx, tag):
+        for owner in range(tp):
+            dst = set_off(idx) + rank * slice_
+            vals[owner, dst:dst + slice_] = x[owner * slice_:(owner + 1) * slice_]
+            tags[owner, dst:dst + slice_] = tag
+
+    def phase_b(rank, idx, tag):
+        base = set_off(idx)
+        rows = np.stack([vals[rank, base + r * slice_: base + (r + 1) * slice_] for r in range(tp)])
+        assert all((tags[rank, base + r * slice_: base + (r + 1) * slice_] == tag).all() for r in range(tp)), "a row was not there yet"
+        v = np.zeros(slice_, np.float32)
+        for r in range(tp):                                               # rank order, fp32
+            v = v + rows[r]
+        for j in range(tp):
+            dst = base + count + rank * slice_
+            vals[j, dst:dst + slice_] = v
+            tags[j, dst:dst + slice_] = tag
+
+    def phase_c(rank, idx, tag):
+        base = set_off(idx) + count
+        assert (tags[rank, base:base + count] == tag).all()
+        return vals[rank, base:base + count].copy()
+
+    pos = 17
+    for idx in range(6):                                                   # consecutive exchanges of one decode step
+        tag = ((pos + 1) << 8) | idx
+        xs = [rng.normal(0, 1, count).astype(np.float32) for _ in range(tp)]
+        for r in range(tp):
+            phase_a(r, xs[r], idx, tag)
+        for r in range(tp):
+            phase_b(r, idx, tag)
+        # rank 0 races ahead: it finishes this exchange and scatters the next one before the others have collected
+        first = phase_c(0, idx, tag)
+        ahead = rng.normal(0, 1, count).astype(np.float32)
+        phase_a(0, ahead, idx + 1, ((pos + 1) << 8) | (idx + 1))           # goes into the other set
+        outs = [first] + [phase_c(r, idx, tag) for r in range(1, tp)]      # the set being read is untouched
+        want = np.zeros(count, np.float32)
+        for r in range(tp):
+            want = want + xs[r]
+        assert all(np.array_equal(o.view(np.uint32), want.view(np.uint32)) for o in outs)
+    assert 2 * (2 * count) <= words                                        # two sets of (region A + region B)
