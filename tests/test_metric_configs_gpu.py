@@ -4,6 +4,8 @@
     sampled weight rows (the oracle's cost is linear in the rows it is given);
   * one decoder layer of the 7B shape at batch 1 with the fp16 KV cache pre-filled to 2048 positions, seed 2:
     the five decode kernels against the oracle's layer arithmetic;
+  * the fused FFN front and the down projection of the 70B shape for 16 sequences, seed 5: sampled rows against the oracle,
+    all rows against the single-row kernels;
   * the full 7B-shaped model, 512-token prompt then 128 greedy steps, seed 3: ids against the oracle's ids
     stored in tests/golden/model_ids.npz (written by tests/golden/make_model_ids.py; the oracle needs minutes
     of host CPU for this, the comparison takes seconds).
@@ -62,6 +64,52 @@ def test_prefill_gemm_at_the_benchmark_shape(pkg):
     g.check(lib.greta_cuda_device_synchronize())
     assert max_abs_rel(got[t], y.download(np.float32)) < 1e-3
     for b in (ad, c, y, xd, w.qs, w.d):
+        b.free()
+
+
+def test_batched_ffn_at_the_70b_shape(pkg):
+    """The two matmuls that dominate the 70B-shaped batch-16 decode step, at full size: the fused RMSNorm -> gate/up -> SwiGLU
+    (2 x 28672 x 8192 weights) and the down projection with residual (8192 x 28672), 16 activation rows, on prepared
+    activations as the decode step runs them.  The oracle is given sampled output rows (its cost is linear in them); a
+    size-independent property covers all rows: the batched result of row m equals the single-row kernel's on row m."""
+    g = pkg.ffi
+    lib = g.cuda()
+    M, D, F = 16, 8192, 28672
+    rng = np.random.default_rng(5)
+    x = (rng.normal(0, 1, (M, D)) * rng.uniform(0.05, 20, (M, 1))).astype(np.float32)      # rows of different scale
+    gamma = rng.normal(1, 0.1, D).astype(np.float32)
+    b1, b3, b2 = q4_0_blocks(rng, F, D), q4_0_blocks(rng, F, D), q4_0_blocks(rng, D, F)
+    w1, w3, w2 = g.Weight(b1, g.FMT_Q4_0, F, D), g.Weight(b3, g.FMT_Q4_0, F, D), g.Weight(b2, g.FMT_Q4_0, D, F)
+    xd, gd = g.DeviceBuffer.from_numpy(x), g.DeviceBuffer.from_numpy(gamma)
+    act = g.DeviceBuffer(M * F * 4)
+    ws = g.DeviceBuffer(lib.greta_cuda_gemv_batch_workspace_bytes(M, F))
+    g.check(lib.greta_cuda_fused_ffn_front_batch(None, g.FMT_Q4_0, xd.ptr, gd.ptr, 1e-5, w1.qs.ptr, w1.d.ptr, w3.qs.ptr, w3.d.ptr, act.ptr, M, D, F,
+                                                 ws.ptr), "ffn_front_batch")
+    got_act = act.download(np.float32).reshape(M, F)
+    rows = np.unique(np.concatenate([rng.integers(0, F, 48), [0, 15, 16, F - 16, F - 1]]))
+    xn = O.rmsnorm(x, gamma, 1e-5)
+    sub = lambda blk, n, k, r: blk.reshape(n, k // 32 * 18)[r].reshape(-1)          # noqa: E731
+    want = O.silu_mul(O.gemv(xn, sub(b1, F, D, rows), O.FMT_Q4_0, len(rows), D), O.gemv(xn, sub(b3, F, D, rows), O.FMT_Q4_0, len(rows), D))
+    assert np.isfinite(got_act).all()
+    for m in range(M):
+        assert max_abs_rel(got_act[m, rows], want[m]) < 2e-5, m
+    # down projection + residual on the activations just produced
+    y = g.DeviceBuffer(M * D * 4)
+    g.check(lib.greta_cuda_gemv_batch(None, g.FMT_Q4_0, act.ptr, None, 0.0, w2.qs.ptr, w2.d.ptr, xd.ptr, y.ptr, M, D, F, 0, ws.ptr), "gemv_batch")
+    got = y.download(np.float32).reshape(M, D)
+    drows = np.unique(np.concatenate([rng.integers(0, D, 48), [0, D - 1]]))
+    wantd = x[:, drows] + O.gemv(got_act, sub(b2, D, F, drows), O.FMT_Q4_0, len(drows), F)
+    for m in range(M):
+        assert max_abs_rel(got[m, drows], wantd[m]) < 2e-5, m
+    # all rows: the single-row kernels on one sequence of the batch
+    m = int(rng.integers(0, M))
+    y1, a1 = g.DeviceBuffer(D * 4), g.DeviceBuffer(F * 4)
+    xm = g.DeviceBuffer.from_numpy(x[m])
+    g.check(lib.greta_cuda_fused_ffn_front(None, g.FMT_Q4_0, xm.ptr, gd.ptr, 1e-5, w1.qs.ptr, w1.d.ptr, w3.qs.ptr, w3.d.ptr, a1.ptr, D, F), "ffn_front")
+    assert max_abs_rel(got_act[m], a1.download(np.float32)) < 2e-5
+    g.check(lib.greta_cuda_gemv_residual(None, g.FMT_Q4_0, a1.ptr, w2.qs.ptr, w2.d.ptr, xm.ptr, y1.ptr, D, F), "gemv_residual")
+    assert max_abs_rel(got[m], y1.download(np.float32)) < 2e-5
+    for b in (xd, gd, act, ws, y, y1, a1, xm, w1.qs, w1.d, w3.qs, w3.d, w2.qs, w2.d):
         b.free()
 
 
