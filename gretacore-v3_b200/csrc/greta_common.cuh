@@ -59,6 +59,7 @@ struct Tuning {
   int attn_mma;              // GRETA_ATTN_MMA: 1 = prefill and grouped-query batched decode attention on the tensor cores
   int peer_two_level_min_tp; // GRETA_PEER_TWO_LEVEL_MIN_TP: ranks from which an exchange consumer gathers in two levels (see gemv_device.cuh)
   int skinny_max_rows;       // GRETA_SKINNY_MAX_ROWS: activation rows up to which the weights-read-once batched GEMV is used
+  int gemv_ring_stages;      // GRETA_GEMV_RING_STAGES: 3 or 5 = forced depth of the single-row GEMV's weight ring, 0 = automatic
   int gemm_splitk;           // GRETA_GEMM_SPLITK: 1 = prefill GEMMs with few 512-token tiles share each tile's K loop between SMs (needs the workspace; changes the fp32 summation order, so off by default)
   int gemm_pair;             // GRETA_GEMM_PAIR: 1 = prefill GEMMs with 512-token tiles run as CTA pairs (two-CTA MMA, each CTA stages half of the tokens), 2 = every GEMM, 0 = none
 };

@@ -73,6 +73,8 @@ Tuning &tuning() {
     v.peer_two_level_min_tp = e ? atoi(e) : 4;
     e = getenv("GRETA_SKINNY_MAX_ROWS");
     v.skinny_max_rows = e ? atoi(e) : 32;
+    e = getenv("GRETA_GEMV_RING_STAGES");
+    v.gemv_ring_stages = e ? atoi(e) : 0;
     e = getenv("GRETA_GEMM_SPLITK");
     v.gemm_splitk = (e && e[0] == '1') ? 1 : 0;
     e = getenv("GRETA_GEMM_PAIR");
@@ -131,6 +133,9 @@ int greta_cuda_set_tuning(const char *name, long long value) {
   } else if (!strcmp(name, "skinny_max_rows")) {
     GRETA_REQUIRE(value >= 1 && value <= 32, "set_tuning: skinny_max_rows=%lld outside 1..32", value);
     t.skinny_max_rows = (int)value;
+  } else if (!strcmp(name, "gemv_ring_stages")) {
+    GRETA_REQUIRE(value == 0 || value == 3 || value == 5, "set_tuning: gemv_ring_stages=%lld is not 0, 3 or 5", value);
+    t.gemv_ring_stages = (int)value;
   } else if (!strcmp(name, "gemm_splitk")) {
     t.gemm_splitk = value != 0;
   } else if (!strcmp(name, "gemm_pair")) {

@@ -120,7 +120,8 @@ GRETA_API int greta_cuda_set_pdl(int on);
  *   consumer spends on one missing partial before it gives up, default 2^22), "attn_mma" (GRETA_ATTN_MMA, 0/1: prefill and grouped-query batched decode
  *   attention on the tensor cores), "peer_two_level_min_tp"
  *   (GRETA_PEER_TWO_LEVEL_MIN_TP: ranks from which an exchange consumer gathers in two levels, default 4), "skinny_max_rows"
- *   (GRETA_SKINNY_MAX_ROWS, 1..32), "gemm_splitk" (GRETA_GEMM_SPLITK, 0/1, default 0: a prefill GEMM with fewer 512-token tiles than
+ *   (GRETA_SKINNY_MAX_ROWS, 1..32), "gemv_ring_stages" (GRETA_GEMV_RING_STAGES: 3 or 5 forces the depth of the single-row GEMV's weight ring,
+ *   0 = automatic), "gemm_splitk" (GRETA_GEMM_SPLITK, 0/1, default 0: a prefill GEMM with fewer 512-token tiles than
  *   SMs shares each tile's K loop between CTAs where that is predicted to pay; needs the workspace; the partial sums change the
  *   fp32 summation order, deterministically), "gemm_pair" (GRETA_GEMM_PAIR: 1 = prefill GEMMs that take 512-token tiles
  *   run as pairs of CTAs sharing one two-CTA tensor-core instruction, 2 = every GEMM does, 0 = none). */
