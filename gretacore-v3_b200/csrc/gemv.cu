@@ -433,10 +433,11 @@ int launch_pipe(cudaStream_t stream, GemvParams p) {
   const size_t room = (SMEM_LIMIT - xs_bytes - part_bytes) / (WARPS * stage_bytes);
   // Ring depth, fixed at compile time: 5 stages, or 3 where the smaller footprint pays more than the deeper prefetch:
   // kernels with 4-row cells (a 5-stage ring of those fills the SM, with 3 stages the next kernel's CTA fits beside it
-  // and starts its own weight prefetch early) and the residual projections (O, down) with 2-row cells.  Measured in the
-  // 7B-shape decode step: 632 -> 638 -> 645 tok/s; the fused QKV operator loses 5 % with 3 stages and keeps 5.
+  // and starts its own weight prefetch early) and the residual projections (O, down; their scattering form under tensor
+  // parallelism too) with 2-row cells.  Measured in the 7B-shape decode step: 632 -> 638 -> 645 tok/s (766 against 761 on
+  // two GPUs); the fused QKV operator loses 5 % with 3 stages and keeps 5.
   const int want = tuning().gemv_ring_stages;  // 0 = the rule above, 3 or 5 = forced
-  const bool shallow = want == 3 || (want != 5 && (R == 4 || EPI == EPI_RESIDUAL));
+  const bool shallow = want == 3 || (want != 5 && (R == 4 || EPI == EPI_RESIDUAL || EPI == EPI_PEER));
   if (F::INTEGER && room >= 5 && !shallow) return launch_pipe_fixed<FMT, EPI, R, PEER, F::INTEGER ? 5 : 0>(stream, p, grid, xs_bytes, stage_bytes, part_bytes);
   if (F::INTEGER && room >= 3) return launch_pipe_fixed<FMT, EPI, R, PEER, F::INTEGER ? 3 : 0>(stream, p, grid, xs_bytes, stage_bytes, part_bytes);
   p.stages = stages;
