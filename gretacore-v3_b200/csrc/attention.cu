@@ -151,6 +151,8 @@ int launch_attn_cluster(cudaStream_t stream, AttnParams p, uint32_t Dh, uint32_t
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
     GRETA_CUDA_TRY(cudaFuncSetAttribute(attn_cluster_kernel<KV, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)s16));
     GRETA_CUDA_TRY(cudaFuncSetAttribute(attn_cluster_kernel<KV, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)s8));
+    GRETA_CUDA_TRY(cudaFuncSetAttribute(attn_cluster_kernel<KV, 16>, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
+    GRETA_CUDA_TRY(cudaFuncSetAttribute(attn_cluster_kernel<KV, 8>, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
     cudaFuncSetAttribute(attn_cluster_kernel<KV, 16>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     cudaFuncSetAttribute(attn_cluster_kernel<KV, 8>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     attr_set[dev] = true;

@@ -371,6 +371,9 @@ int ensure_smem_attr(Kern kern, bool (&attr_set)[64]) {
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
     GRETA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_LIMIT));
+    // every kernel of the decode chain asks for the same (largest) shared-memory carve-out: an SM need not be
+    // reconfigured, and so drained, between two of them
+    GRETA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
     attr_set[dev] = true;
   }
   return GRETA_OK;
