@@ -330,6 +330,7 @@ int ensure_mma_smem(Kern kern, size_t smem, bool (&done)[64]) {
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !done[dev]) {
     GRETA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    GRETA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
     done[dev] = true;
   }
   return GRETA_OK;

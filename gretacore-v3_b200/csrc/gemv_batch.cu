@@ -858,6 +858,8 @@ int launch_batch_prepared(cudaStream_t stream, GemvParams p, void *workspace) {
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
     GRETA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P::SMEM));
+    GRETA_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
+    GRETA_CUDA_TRY(cudaFuncSetAttribute(prep, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared));
     attr_set[dev] = true;
   }
   GRETA_CUDA_TRY(launch_pdl(prep, dim3(8 * MT), dim3(PREP_THREADS), 0, stream, static_cast<const float *>(p.x), p.gamma, p.eps, p.M, p.K,
