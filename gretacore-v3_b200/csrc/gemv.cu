@@ -470,13 +470,14 @@ int launch_any(cudaStream_t stream, GemvParams p) {
 // switches earlier, at four: at the 7B shape (22016 rows x 4096) 4-row cells take 12.6 us against 13.4 and the
 // decode step gains 1.6 %; its half on two GPUs (11008 rows) gains 2 % (783 against 767 tok/s), its quarter on four
 // gains nothing.  The residual projections (O, down) take them from one cell per warp: with the 3-stage ring of
-// launch_pipe 654 -> 657 tok/s for the O projection (4096 x 4096) and 645 -> 654 for the down projection.  The
-// fused QKV operator of the same model loses 7 % with them.
+// launch_pipe 654 -> 657 tok/s for the O projection (4096 x 4096) and 645 -> 654 for the down projection; the plain
+// GEMV likewise (alone: 11008 x 4096 7.3 against 8.4 us, 22016 x 4096 11.5 against 12.7, 8192 x 8192 9.7 against 10.8).
+// The fused QKV operator of the same model loses 7 % with them.
 template <int FMT, int EPI, bool PEER = false>
 int launch_quant(cudaStream_t stream, const GemvParams &p, uint64_t total_rows) {
   const uint64_t cells4 = (total_rows / 4) * ((p.K / 32 + 31) / 32);
   if (EPI == EPI_QKV && (p.Dh / 2) % 2 != 0) return launch_any<FMT, EPI, 2, PEER>(stream, p);
-  const uint64_t r2_cells = tuning().gemv_r2_cells >= 0 ? (uint64_t)tuning().gemv_r2_cells : (uint64_t)sm_count() * WARPS * (EPI == EPI_SWIGLU ? 4 : (EPI == EPI_RESIDUAL ? 1 : 10));
+  const uint64_t r2_cells = tuning().gemv_r2_cells >= 0 ? (uint64_t)tuning().gemv_r2_cells : (uint64_t)sm_count() * WARPS * (EPI == EPI_SWIGLU ? 4 : ((EPI == EPI_RESIDUAL || EPI == EPI_PLAIN) ? 1 : 10));
   if (cells4 < r2_cells) return launch_any<FMT, EPI, 2, PEER>(stream, p);
   return launch_any<FMT, EPI, 4, PEER>(stream, p);
 }
