@@ -1172,7 +1172,7 @@ bool plan_splitk(uint32_t M, uint32_t N, uint32_t K, SplitPlan *pl, uint32_t *ct
   pick_tile(M, N, &tn, &rt);
   const uint32_t tile_ctas = ((N + TILE_N * rt - 1) / (TILE_N * rt)) * ((M + tn - 1) / tn);
   const double per_stage = tn == 512 ? 1.0 : (tn == 256 ? 0.8 : 0.66);
-  if (share + 24.0 >= (double)((tile_ctas + sms - 1) / sms) * KT * per_stage * rt) return false;
+  if (tuning().gemm_splitk != 2 && share + 24.0 >= (double)((tile_ctas + sms - 1) / sms) * KT * per_stage * rt) return false;  // 2: whenever feasible
   pl->share = share;
   pl->KT = KT;
   pl->units = units;
@@ -1261,6 +1261,37 @@ void pick_tile(uint32_t M, uint32_t N, int *tn, int *rt) {
 extern "C" {
 
 size_t greta_cuda_gemm_workspace_bytes(uint32_t M, uint32_t K) { return split_scratch_bytes() + ((size_t)M * K * 2 + 255) / 256 * 256; }
+
+// Which kernel greta_cuda_gemm would launch for this shape with the tuning switches as they stand, without launching it:
+// kind 0 = tiled (ctas = tiles of tile_tokens x 128 * row tiles), 1 = CTA pairs, 2 = split over K (ctas CTAs of `share` K
+// stages each).  Host arithmetic only.
+int greta_cuda_gemm_route(uint32_t M, uint32_t N, uint32_t K, int has_workspace, int *kind, uint32_t *ctas, uint32_t *share, uint32_t *tile_tokens) {
+  GRETA_REQUIRE(kind && ctas && share && tile_tokens, "gemm_route: null out pointer");
+  GRETA_REQUIRE(M && N && K && K % 32 == 0, "gemm_route: M=%u N=%u K=%u", M, N, K);
+  int tn = 128, rt = 1;
+  pick_tile(M, N, &tn, &rt);
+  const bool pair = tuning().gemm_pair == 2 || (tuning().gemm_pair == 1 && tn == 512 && rt == 1 && tuning().gemm_tile_tokens == 0);
+  SplitPlan sp{};
+  uint32_t sc = 0;
+  if (tuning().gemm_splitk && !pair && has_workspace && tuning().gemm_tile_tokens == 0 && plan_splitk(M, N, K, &sp, &sc)) {
+    *kind = 2;
+    *ctas = sc;
+    *share = sp.share;
+    *tile_tokens = 512;
+    return GRETA_OK;
+  }
+  *share = (K + BK - 1) / BK;
+  if (pair) {
+    *kind = 1;
+    *tile_tokens = 512;
+    *ctas = (((N + TILE_N - 1) / TILE_N + 1) / 2 * 2) * ((M + 511) / 512);
+    return GRETA_OK;
+  }
+  *kind = 0;
+  *tile_tokens = (uint32_t)tn;
+  *ctas = ((N + TILE_N * rt - 1) / (TILE_N * rt)) * ((M + tn - 1) / tn);
+  return GRETA_OK;
+}
 
 int greta_cuda_gemm_status(int *code) {
   GRETA_REQUIRE(code, "gemm_status: null out pointer");

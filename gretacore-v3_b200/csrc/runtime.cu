@@ -76,7 +76,7 @@ Tuning &tuning() {
     e = getenv("GRETA_GEMV_RING_STAGES");
     v.gemv_ring_stages = e ? atoi(e) : 0;
     e = getenv("GRETA_GEMM_SPLITK");
-    v.gemm_splitk = (e && e[0] == '1') ? 1 : 0;
+    v.gemm_splitk = (e && (e[0] == '1' || e[0] == '2')) ? e[0] - '0' : 0;
     e = getenv("GRETA_GEMM_PAIR");
     v.gemm_pair = (e && e[0] >= '0' && e[0] <= '2') ? e[0] - '0' : 0;
     return v;
@@ -137,7 +137,8 @@ int greta_cuda_set_tuning(const char *name, long long value) {
     GRETA_REQUIRE(value == 0 || value == 3 || value == 5, "set_tuning: gemv_ring_stages=%lld is not 0, 3 or 5", value);
     t.gemv_ring_stages = (int)value;
   } else if (!strcmp(name, "gemm_splitk")) {
-    t.gemm_splitk = value != 0;
+    GRETA_REQUIRE(value >= 0 && value <= 2, "set_tuning: gemm_splitk=%lld outside 0..2", value);
+    t.gemm_splitk = (int)value;
   } else if (!strcmp(name, "gemm_pair")) {
     GRETA_REQUIRE(value >= 0 && value <= 2, "set_tuning: gemm_pair=%lld outside 0..2", value);
     t.gemm_pair = (int)value;

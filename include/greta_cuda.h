@@ -121,8 +121,8 @@ GRETA_API int greta_cuda_set_pdl(int on);
  *   attention on the tensor cores), "peer_two_level_min_tp"
  *   (GRETA_PEER_TWO_LEVEL_MIN_TP: ranks from which an exchange consumer gathers in two levels, default 4), "skinny_max_rows"
  *   (GRETA_SKINNY_MAX_ROWS, 1..32), "gemv_ring_stages" (GRETA_GEMV_RING_STAGES: 3 or 5 forces the depth of the single-row GEMV's weight ring,
- *   0 = automatic), "gemm_splitk" (GRETA_GEMM_SPLITK, 0/1, default 0: a prefill GEMM with fewer 512-token tiles than
- *   SMs shares each tile's K loop between CTAs where that is predicted to pay; needs the workspace; the partial sums change the
+ *   0 = automatic), "gemm_splitk" (GRETA_GEMM_SPLITK, default 0: 1 = a prefill GEMM with fewer 512-token tiles than
+ *   SMs shares each tile's K loop between CTAs where that is predicted to pay, 2 = wherever it is feasible; needs the workspace; the partial sums change the
  *   fp32 summation order, deterministically), "gemm_pair" (GRETA_GEMM_PAIR: 1 = prefill GEMMs that take 512-token tiles
  *   run as pairs of CTAs sharing one two-CTA tensor-core instruction, 2 = every GEMM does, 0 = none). */
 GRETA_API int greta_cuda_set_tuning(const char *name, long long value);
@@ -296,6 +296,11 @@ GRETA_API int greta_cuda_decode_trace(const void *plan, long long *out25);
  * fixed tiles only.  Its contents need not be initialised or kept; two products that may run at the same time
  * (different streams) need a workspace each. */
 GRETA_API size_t greta_cuda_gemm_workspace_bytes(uint32_t M, uint32_t K);
+/* Which kernel greta_cuda_gemm would take for a shape under the tuning switches as they stand (nothing is launched):
+ * *kind 0 = fixed tiles of *tile_tokens tokens x 128 rows, 1 = CTA pairs, 2 = K loops shared between CTAs; *ctas = CTAs of the
+ * launch, *share = K stages (of 64) each CTA runs. */
+GRETA_API int greta_cuda_gemm_route(uint32_t M, uint32_t N, uint32_t K, int has_workspace, int *kind, uint32_t *ctas, uint32_t *share,
+                                    uint32_t *tile_tokens);
 /* Every wait inside the GEMM kernel is bounded; if one ever gives up the kernel drains, frees its tensor
  * memory and records a non-zero code (100 * role + stage) that this call returns in *code (0 = none).
  * Synchronises with the device. */

@@ -738,7 +738,7 @@ def test_gemm_split_over_k(g, tuning, name, M, N, K, a_f16, c_f16):
     added in ascending K order by the CTA that owns the tile.  Tiles cut into up to eight parts, two token tiles, ragged rows and
     tokens, an odd number of blocks in K, fp32 activations converted into the same workspace, and a shape the plan declines
     (600 tokens: the second token tile would be mostly padding), which must still come out right through the tiled kernel."""
-    tuning("gemm_splitk", 1, restore=0)
+    tuning("gemm_splitk", 2, restore=0)             # 2: wherever the plan is feasible, not only where it is predicted to pay
     ofmt, gfmt = FMTS[name]
     rng = np.random.default_rng(1400 + M + N)
     blk = make_blocks(rng, ofmt, N, K)
